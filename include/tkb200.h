@@ -1,0 +1,116 @@
+/* tkb200 — C ABI of the B200 (sm_100a) quantized-inference kernels.
+ *
+ * Drop-in replacements for the entry points that ThunderKittens exposes through its per-kernel
+ * pybind modules (`_C`).  Each function below names the reference entry it replaces (file:line in
+ * the ThunderKittens tree).  Conventions shared by every call:
+ *   - plain device pointers, sizes and a CUDA stream (cudaStream_t passed as void*; NULL = the
+ *     legacy default stream); no torch types, no allocation of user buffers, no synchronisation;
+ *   - the caller owns every input and output buffer, exactly as with the reference kernels
+ *     (include/pyutils/torchutils.cuh:97-115 checks and wraps caller tensors);
+ *   - return value: TKB_OK or an error code; tkb_last_error() gives the message of the calling
+ *     thread's last failure.  Nothing here throws, prints or exits (the reference TORCH_CHECKs,
+ *     throws std::runtime_error or exit()s: torchutils.cuh:35-83, common/util.cuh:412-431);
+ *   - layouts are the reference's: e2m1 codes two per byte with element 2i in the low nibble,
+ *     e4m3 / ue8m0 scales in 512-byte chunks of (128 rows x 4 K-blocks) with byte
+ *     (row%32)*16 + (row/32%4)*4 + kblock%4, chunks ordered [row/128][kblock/4]
+ *     (kernels/gemm/common.cuh:105-116), row-major bf16 outputs, both GEMM operands K-contiguous.
+ *   - every device-side wait is bounded; a launch that gave up records TKB_ERR_TIMEOUT, visible
+ *     through tkb_device_status().
+ */
+#ifndef TKB200_H
+#define TKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    TKB_OK = 0,
+    TKB_ERR_INVALID_ARG = 1,   /* null pointer, bad size or unsupported shape */
+    TKB_ERR_BAD_ALIGNMENT = 2, /* base pointers / leading dimensions must be 16-byte aligned */
+    TKB_ERR_CUDA = 3,          /* a CUDA runtime or driver call failed */
+    TKB_ERR_TIMEOUT = 4,       /* a bounded device-side wait ran out */
+    TKB_ERR_UNSUPPORTED = 5    /* not an sm_100 device / driver without tensor-map support */
+};
+
+/* NVFP4 quantizer arithmetic (see tkb_nvfp4_quantize) */
+enum {
+    TKB_NVFP4_SPEC = 0,        /* the reference's torch specification, IEEE fp32 (default) */
+    TKB_NVFP4_KERNEL_IEEE = 1, /* the reference kernel's operation order, IEEE fp32 */
+    TKB_NVFP4_KERNEL_FAST = 2  /* the reference kernel's operation order AND its --use_fast_math build */
+};
+
+/* GEMM tile configuration override for tkb_*_gemm_ex (0 = library default) */
+enum {
+    TKB_GEMM_DEFAULT = 0,
+    TKB_GEMM_PAIR_N256 = 1,    /* two-CTA 256 x 256 tiles */
+    TKB_GEMM_SINGLE_N256 = 2,  /* one-CTA 128 x 256 tiles */
+    TKB_GEMM_PAIR_N128 = 3,    /* two-CTA 256 x 128 tiles */
+    TKB_GEMM_SINGLE_N128 = 4   /* one-CTA 128 x 128 tiles */
+};
+
+int tkb_version(void);
+const char* tkb_last_error(void);
+
+/* Status word written by kernels of the current device (0 = no kernel reported a problem).
+ * Synchronises `stream`, returns the word through *status and clears it. */
+int tkb_device_status(void* stream, int* status);
+
+/* ---- quantize ----------------------------------------------------------------------------- */
+
+/* Replaces nvfp4_quantize(A_bf16, A_fp4x2, A_sc, A_sc_global, scale_2d)
+ * (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:772-794, kernels 356-545).
+ *   A_bf16 [M, K] bf16, leading dimension lda elements (0 = K); K % 64 == 0; any M >= 1
+ *   codes  [M, K/2] bytes; sc [ceil(M/128), K/64, 512] e4m3 (rows past M are written as 0);
+ *   sg     fp32[1] = per-tensor decode scale amax/2688
+ * One launch; the per-tensor amax pass is fused (cooperative grid). */
+int tkb_nvfp4_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int scale_2d,
+                       int arithmetic, void* stream);
+
+/* Same, with the per-tensor amax supplied by the caller as a device float (row-sharded tensors:
+ * reduce tkb_absmax_bf16 over the shards first so every shard quantizes like the full tensor). */
+int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M,
+                                 int K, int scale_2d, int arithmetic, void* stream);
+
+/* max |x| of a bf16 matrix into *amax (device float; overwritten).  Part of
+ * nvfp4_quantize::absmax_kernel (nvfp4_b200_gemm.cu:360-418) exposed for sharded tensors. */
+int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream);
+
+/* Replaces mxfp8_quantize(A_bf16, A_fp8, A_sc) (kernels/gemm/mxfp8_b200/mxfp8_b200_gemm.cu:605-619, kernel 328-430).
+ *   codes [M, K] e4m3; sc [ceil(M/128), K/128, 512] ue8m0; K % 128 == 0 */
+int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, int M, int K, void* stream);
+
+/* Replace fp32_to_fp4x2 / fp4x2_to_fp32 (nvfp4_b200_gemm.cu:796-826); the caller allocates the output. */
+int tkb_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, void* stream);
+int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream);
+
+/* ---- GEMM: D[M,N] bf16 = A[M,K] . B[N,K]^T ---------------------------------------------- */
+
+/* Replaces nvfp4_gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D) (nvfp4_b200_gemm.cu:748-770).
+ *   A [M, K/2] bytes, B [N, K/2] bytes (row pitch K/2); A_sc/B_sc swizzled e4m3 chunks with
+ *   ceil(rows/128) row blocks; A_sg/B_sg fp32[1]; D [M, N] bf16 with leading dimension ldd (0 = N).
+ *   K % 64 == 0, N % 8 == 0; any M, N (the reference needs M,N,K % 256 == 0). */
+int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
+                   void* D, int64_t ldd, int M, int N, int K, void* stream);
+int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
+                      void* D, int64_t ldd, int M, int N, int K, int config, void* stream);
+
+/* Replaces mxfp8_gemm(A, A_sc, B, B_sc, D) (mxfp8_b200_gemm.cu:585-603).  K % 128 == 0, N % 8 == 0. */
+int tkb_mxfp8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
+                   void* stream);
+int tkb_mxfp8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
+                      int config, void* stream);
+
+/* Replaces the standalone bf16 GEMM (kernels/gemm/bf16_b200/bf16_b200_gemm.cu:61-253, launched at
+ * l.300-330; it has no pybind entry).  lda/ldb in elements (0 = K); K % 8 == 0, N % 8 == 0. */
+int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream);
+int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
+                     int config, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TKB200_H */

@@ -1,0 +1,79 @@
+"""ctypes binding of libtkb200.so (the C ABI declared in include/tkb200.h).
+
+The library is built in-tree by `python -m thunderkittens_b200.build`.  There is no fallback: if the
+shared object is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtkb200.so")
+
+OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
+NVFP4_SPEC, NVFP4_KERNEL_IEEE, NVFP4_KERNEL_FAST = 0, 1, 2
+GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128 = range(5)
+
+
+class TkbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"tkb200 error {code}: {message}")
+        self.code = code
+
+
+_vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+_SIGNATURES = {
+    "tkb_version": ([], _i),
+    "tkb_last_error": ([], C.c_char_p),
+    "tkb_device_status": ([_vp, C.POINTER(_i)], _i),
+    "tkb_nvfp4_quantize": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
+    "tkb_nvfp4_quantize_with_amax": ([_vp, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
+    "tkb_absmax_bf16": ([_vp, _i64, _i, _i, _vp, _vp], _i),
+    "tkb_mxfp8_quantize": ([_vp, _i64, _vp, _vp, _i, _i, _vp], _i),
+    "tkb_fp32_to_fp4x2": ([_vp, _vp, _sz, _vp], _i),
+    "tkb_fp4x2_to_fp32": ([_vp, _vp, _sz, _vp], _i),
+    "tkb_nvfp4_gemm": ([_vp] * 7 + [_i64, _i, _i, _i, _vp], _i),
+    "tkb_nvfp4_gemm_ex": ([_vp] * 7 + [_i64, _i, _i, _i, _i, _vp], _i),
+    "tkb_mxfp8_gemm": ([_vp] * 5 + [_i64, _i, _i, _i, _vp], _i),
+    "tkb_mxfp8_gemm_ex": ([_vp] * 5 + [_i64, _i, _i, _i, _i, _vp], _i),
+    "tkb_bf16_gemm": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp], _i),
+    "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m thunderkittens_b200.build` (no CPU fallback exists)")
+        L = C.CDLL(LIB_PATH)
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            if not hasattr(L, name):
+                continue   # optional entry points are bound where they are declared
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _lib = L
+    return _lib
+
+
+def bind(name: str, argtypes, restype=_i):
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise TkbError(code, lib().tkb_last_error().decode())
+
+
+def device_status(stream: int = 0) -> int:
+    st = C.c_int(0)
+    check(lib().tkb_device_status(stream, C.byref(st)))
+    return st.value

@@ -1,0 +1,286 @@
+// C-ABI entry points of libtkb200: argument validation, per-device context (SM count, status word,
+// quantize scratch), TMA tensor-map construction, launches.  Declarations and the reference entry
+// each function replaces: include/tkb200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <atomic>
+
+#include "../../include/tkb200.h"
+#include "internal.h"
+#include "quantize_types.h"
+
+namespace tkb {
+
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+#define TKB_CUDA(expr)                                                                                   \
+    do {                                                                                                 \
+        cudaError_t _e = (expr);                                                                         \
+        if (_e != cudaSuccess) return fail(TKB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+// ------------------------------------------------------------------ per-device context -----
+constexpr int kMaxDevices = 64;
+constexpr int kQuantSlots = 256;
+
+struct DeviceCtx {
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status = nullptr;          // device int, zero when healthy
+    QuantWork* quant_ws = nullptr;  // kQuantSlots zeroed slots, each returned to zero by the kernel that used it
+    std::atomic<unsigned> next_slot{0};
+};
+static DeviceCtx g_ctx[kMaxDevices];
+static std::mutex g_ctx_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_ctx(DeviceCtx** out) {
+    int dev = 0;
+    TKB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TKB_ERR_INVALID_ARG, "device ordinal %d out of range", dev);
+    DeviceCtx& c = g_ctx[dev];
+    if (!c.ready) {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        if (!c.ready) {
+            cudaDeviceProp prop;
+            TKB_CUDA(cudaGetDeviceProperties(&prop, dev));
+            if (prop.major != 10) return fail(TKB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+            c.sm_count = prop.multiProcessorCount;
+            c.cc_major = prop.major;
+            TKB_CUDA(cudaMalloc(&c.status, sizeof(int)));
+            TKB_CUDA(cudaMemset(c.status, 0, sizeof(int)));
+            TKB_CUDA(cudaMalloc(&c.quant_ws, sizeof(QuantWork) * kQuantSlots));
+            TKB_CUDA(cudaMemset(c.quant_ws, 0, sizeof(QuantWork) * kQuantSlots));
+            if (!g_encode) {
+                void* fn = nullptr;
+                cudaDriverEntryPointQueryResult q;
+                TKB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+                if (!fn || q != cudaDriverEntryPointSuccess) return fail(TKB_ERR_UNSUPPORTED, "driver does not export cuTensorMapEncodeTiled");
+                g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            }
+            TKB_CUDA(cudaDeviceSynchronize());
+            c.ready = true;
+        }
+    }
+    *out = &c;
+    return TKB_OK;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 2-D K-major operand map: inner dimension = K in `elem_bytes`-sized elements, 128-byte swizzle,
+// box = 128 bytes of K x box_rows rows.  Out-of-range rows / K are zero-filled by the TMA unit.
+static int make_operand_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner_elems,
+                            uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows) {
+    cuuint64_t dims[2] = {inner_elems, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {uint32_t(128 / elem_bytes), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed with CUresult %d", int(r));
+    return TKB_OK;
+}
+// 3-D scale map over [row_blocks][k_chunks][128 x int32] (512-byte chunks), box = chunks_per_stage chunks.
+static int make_scale_map(CUtensorMap* m, const void* base, uint64_t row_blocks, uint64_t k_chunks, uint32_t chunks_per_stage) {
+    cuuint64_t dims[3] = {128, k_chunks, row_blocks};
+    cuuint64_t strides[2] = {512, 512 * k_chunks};
+    cuuint32_t box[3] = {128, chunks_per_stage, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(scales) failed with CUresult %d", int(r));
+    return TKB_OK;
+}
+
+static int pick_config(int config, int M, int N, int sm_count) {
+    if (config >= TKB_GEMM_PAIR_N256 && config <= TKB_GEMM_SINGLE_N128) return config - 1;
+    // default: CTA pairs; 256-wide N tiles unless that leaves most of the SMs without a tile
+    const long tiles256 = long((M + 255) / 256) * ((N + 255) / 256);
+    if (tiles256 * 2 >= sm_count || (N % 256 == 0 && tiles256 * 4 >= sm_count)) return 0;
+    return 2;
+}
+
+static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A_sc, const float* A_sg, const void* B,
+                       int64_t ldb_bytes, const void* B_sc, const float* B_sg, void* D, int64_t ldd, int M, int N, int K, int config,
+                       void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!A || !B || !D) return fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
+    if (M < 1 || N < 1 || K < 1) return fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+    if (config < 0 || config > TKB_GEMM_SINGLE_N128) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
+    const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : 8);
+    if (K % kmult) return fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
+    if (N % 8) return fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
+    if (ldd == 0) ldd = N;
+    if (ldd < N || ldd % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
+    if (!aligned16(A) || !aligned16(B) || !aligned16(D) || lda_bytes % 16 || ldb_bytes % 16)
+        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
+    if (kind != KIND_BF16) {
+        if (!A_sc || !B_sc) return fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
+        if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
+    }
+    if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
+
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.kind = kind;
+    g.config = pick_config(config, M, N, c->sm_count);
+    const int ctas = (g.config & 1) ? 1 : 2;
+    const int bn = gemm_tile_n(g.config);
+    const int elem_bytes = kind == KIND_BF16 ? 2 : 1;
+    const CUtensorMapDataType dt = kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint64_t inner = kind == KIND_NVFP4 ? uint64_t(K / 2) : uint64_t(K);
+    if (int e = make_operand_map(&g.tmA, A, dt, elem_bytes, inner, M, lda_bytes, 128)) return e;
+    if (int e = make_operand_map(&g.tmB, B, dt, elem_bytes, inner, N, ldb_bytes, bn / ctas)) return e;
+    if (kind != KIND_BF16) {
+        const int kc = kind == KIND_NVFP4 ? K / 64 : K / 128;
+        const int per_stage = kind == KIND_NVFP4 ? 4 : 1;
+        if (int e = make_scale_map(&g.tmSA, A_sc, (M + 127) / 128, kc, per_stage)) return e;
+        if (int e = make_scale_map(&g.tmSB, B_sc, (N + 127) / 128, kc, per_stage)) return e;
+    } else {
+        g.tmSA = g.tmA; g.tmSB = g.tmB;
+    }
+    g.sgA = A_sg; g.sgB = B_sg; g.D = D; g.ldd = ldd; g.M = M; g.N = N; g.K = K;
+    g.status = c->status; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
+    TKB_CUDA(launch_gemm(g));
+    return TKB_OK;
+}
+
+static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
+                                 int scale_2d, int arithmetic, void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!A || !codes || !sc || !sg) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
+    if (M < 1 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: need M >= 1 and K a positive multiple of 64 (got M=%d K=%d)", M, K);
+    if (arithmetic < 0 || arithmetic > 2) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: unknown arithmetic %d", arithmetic);
+    if (lda == 0) lda = K;
+    if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: lda must be >= K and a multiple of 8 elements");
+    if (!aligned16(A) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: buffers must be 16-byte aligned");
+    NvQuantArgs a;
+    a.A = A; a.lda = lda; a.codes = codes; a.ldc = K / 2; a.sc = sc; a.sg = sg; a.amax_in = amax;
+    a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
+    a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
+    a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count;
+    TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
+    return TKB_OK;
+}
+
+} // namespace tkb
+
+using namespace tkb;
+
+extern "C" {
+
+int tkb_version(void) { return 100; }
+const char* tkb_last_error(void) { return g_err; }
+
+int tkb_device_status(void* stream, int* status) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!status) return fail(TKB_ERR_INVALID_ARG, "device_status: null output");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    TKB_CUDA(cudaStreamSynchronize(s));
+    TKB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status) TKB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+    return TKB_OK;
+}
+
+int tkb_nvfp4_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int scale_2d, int arithmetic,
+                       void* stream) {
+    return nvfp4_quantize_common(A_bf16, lda, codes, sc, sg, nullptr, M, K, scale_2d, arithmetic, stream);
+}
+
+int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
+                                 int scale_2d, int arithmetic, void* stream) {
+    if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_with_amax: null amax");
+    return nvfp4_quantize_common(A_bf16, lda, codes, sc, sg, amax, M, K, scale_2d, arithmetic, stream);
+}
+
+int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!A_bf16 || !amax) return fail(TKB_ERR_INVALID_ARG, "absmax: null pointer");
+    if (M < 1 || K < 8 || K % 8) return fail(TKB_ERR_INVALID_ARG, "absmax: need M >= 1 and K a positive multiple of 8");
+    if (lda == 0) lda = K;
+    if (lda < K || lda % 8 || !aligned16(A_bf16)) return fail(TKB_ERR_BAD_ALIGNMENT, "absmax: A must be 16-byte aligned with lda %% 8 == 0");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    TKB_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), s));
+    TKB_CUDA(launch_absmax(A_bf16, lda, M, K, reinterpret_cast<unsigned int*>(amax), c->sm_count, s));
+    return TKB_OK;
+}
+
+int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, int M, int K, void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!A_bf16 || !codes || !sc) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: null pointer");
+    if (M < 1 || K < 128 || K % 128) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: need M >= 1 and K a positive multiple of 128 (got M=%d K=%d)", M, K);
+    if (lda == 0) lda = K;
+    if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: lda must be >= K and a multiple of 8 elements");
+    if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
+    TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
+    return TKB_OK;
+}
+
+int tkb_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp32_to_fp4x2: null pointer");
+    if (reinterpret_cast<uintptr_t>(in) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp32_to_fp4x2: input must be 8-byte aligned");
+    if (n_pairs == 0) return TKB_OK;
+    TKB_CUDA(launch_fp32_to_fp4x2(in, out, n_pairs, static_cast<cudaStream_t>(stream)));
+    return TKB_OK;
+}
+int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp4x2_to_fp32: null pointer");
+    if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp4x2_to_fp32: output must be 8-byte aligned");
+    if (n_pairs == 0) return TKB_OK;
+    TKB_CUDA(launch_fp4x2_to_fp32(in, out, n_pairs, static_cast<cudaStream_t>(stream)));
+    return TKB_OK;
+}
+
+int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg, void* D,
+                      int64_t ldd, int M, int N, int K, int config, void* stream) {
+    return gemm_common(KIND_NVFP4, A, K / 2, A_sc, A_sg, B, K / 2, B_sc, B_sg, D, ldd, M, N, K, config, stream);
+}
+int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg, void* D,
+                   int64_t ldd, int M, int N, int K, void* stream) {
+    return tkb_nvfp4_gemm_ex(A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
+}
+int tkb_mxfp8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
+                      int config, void* stream) {
+    return gemm_common(KIND_MXFP8, A, K, A_sc, nullptr, B, K, B_sc, nullptr, D, ldd, M, N, K, config, stream);
+}
+int tkb_mxfp8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
+                   void* stream) {
+    return tkb_mxfp8_gemm_ex(A, A_sc, B, B_sc, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
+}
+int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, int config,
+                     void* stream) {
+    if (lda == 0) lda = K;
+    if (ldb == 0) ldb = K;
+    if (lda < K || ldb < K) return fail(TKB_ERR_INVALID_ARG, "bf16_gemm: lda/ldb must be >= K");
+    return gemm_common(KIND_BF16, A, lda * 2, nullptr, nullptr, B, ldb * 2, nullptr, nullptr, D, ldd, M, N, K, config, stream);
+}
+int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {
+    return tkb_bf16_gemm_ex(A, lda, B, ldb, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
+}
+
+} // extern "C"

@@ -1,0 +1,345 @@
+// Block-scaled and dense GEMMs for sm_100a: D[M,N] (bf16) = A[M,K] * B[N,K]^T, fp32 accumulation
+// in tensor memory.  One kernel template covers the three operand formats of the path:
+//   KIND_NVFP4 : e2m1 codes (2 per byte), one e4m3 scale per 16 K-elements, fp32 per-tensor scales
+//                (replaces nvfp4_gemm::kernel, kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:88-307)
+//   KIND_MXFP8 : e4m3 codes, one ue8m0 scale per 32 K-elements
+//                (replaces mxfp8_gemm::kernel, kernels/gemm/mxfp8_b200/mxfp8_b200_gemm.cu:83-292)
+//   KIND_BF16  : dense control (replaces kernel<C>, kernels/gemm/bf16_b200/bf16_b200_gemm.cu:61-253)
+//
+// Design (one CTA per SM, persistent over output tiles):
+//   * A stage of the operand ring always holds exactly 128 bytes of K per row (64 bf16, 128 e4m3,
+//     256 e2m1), i.e. one 128-byte-swizzle panel: one TMA box per operand per stage and four
+//     tcgen05.mma per stage (32 bytes of K each) for every format.
+//   * CTAS == 2: two CTAs of a cluster form one 256 x BN tile (cta_group::2).  Each CTA loads its own
+//     128 rows of A, its half of the B rows, its A scales and ALL of the tile's B scales.  Loads
+//     are plain (non-multicast) TMA copies whose completion bytes are credited to the leader CTA's
+//     "full" barrier; the leader's MMA thread releases a stage in both CTAs with one commit.
+//   * warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2.. = epilogue.
+//   * Scale factors travel shared memory -> tensor memory with tcgen05.cp right before the MMAs
+//     that use them, into one of four rotating slots next to the accumulator.
+//   * The accumulator is single-buffered (256 fp32 columns + scale slots do not leave room for two):
+//     the epilogue first drains it into registers as packed bf16, hands TMEM back to the MMA warp,
+//     and only then writes to global memory, so the stores overlap the next tile's main loop.
+//   * Every mbarrier wait is bounded (ptx.cuh); on a timeout the kernel records the status, leaves
+//     its loops, joins the final cluster barrier, frees TMEM and returns.
+#include "ptx.cuh"
+#include "internal.h"
+
+namespace tkb {
+
+template <int KIND, int CTAS, int BN>
+struct GemmCfg {
+    static_assert(CTAS == 1 || CTAS == 2, "");
+    static_assert(BN == 128 || BN == 256, "");
+    static constexpr int BM = 128 * CTAS;                 // rows of D per cluster tile
+    static constexpr int BN_CTA = BN / CTAS;              // rows of B each CTA loads
+    static constexpr int KB = KIND == KIND_BF16 ? 64 : (KIND == KIND_MXFP8 ? 128 : 256);   // K elements per stage
+    static constexpr int A_BYTES = 128 * 128;
+    static constexpr int B_BYTES = BN_CTA * 128;
+    static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP8 ? 1 : 0);  // 512-byte chunks per 128 rows per stage
+    static constexpr int SFA_BYTES = SF_CHUNKS * 512;
+    static constexpr int SFB_BYTES = SF_CHUNKS * 512 * (BN / 128);
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+    static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;
+    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+    static constexpr int COLS_PER_EPI_WARP = BN / (EPI_WARPS / 4);   // 128
+    // tensor memory: accumulator at column 0, then rotating scale slots
+    static constexpr int SFA_COLS = SF_CHUNKS * 4;                   // per stage
+    static constexpr int SFB_COLS = SF_CHUNKS * 4 * (BN / 128);
+    static constexpr int SF_SLOTS = 4;
+    static constexpr int TMEM_COLS = 512;
+    static_assert(BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS, "tensor memory overflow");
+    static_assert(STAGES >= 3, "not enough pipeline stages");
+    static constexpr uint32_t TX_BYTES = CTAS * STAGE_BYTES;
+};
+
+struct GemmParams {
+    const float* sgA; const float* sgB;
+    __nv_bfloat16* D; int64_t ldd;
+    int M, N, K;
+    int* status;
+};
+
+__device__ __forceinline__ void tile_to_block(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
+    constexpr int GROUP = 8;                       // row-blocks that share a sweep over the columns (L2 reuse)
+    const int per_group = GROUP * tiles_n;
+    const int g = tile / per_group, in_g = tile % per_group;
+    const int first_m = g * GROUP;
+    const int gsz = min(GROUP, tiles_m - first_m);
+    m_blk = first_m + in_g % gsz;
+    n_blk = in_g / gsz;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, uint32_t cluster_bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+template <int KIND, int CTAS, int BN>
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN>::THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const GemmParams p) {
+    using C = GemmCfg<KIND, CTAS, BN>;
+    constexpr bool SCALED = KIND != KIND_BF16;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[C::STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[C::STAGES];
+    __shared__ __align__(8) uint64_t bar_tmem_full;
+    __shared__ __align__(8) uint64_t bar_tmem_empty;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0;
+    const bool is_leader = cta_rank == 0;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA = smem_base;
+    const uint32_t sB = sA + C::STAGES * C::A_BYTES;
+    const uint32_t sSA = sB + C::STAGES * C::B_BYTES;
+    const uint32_t sSB = sSA + C::STAGES * C::SFA_BYTES;
+
+    const int tiles_m = (p.M + C::BM - 1) / C::BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + C::KB - 1) / C::KB;
+    const int first_tile = CTAS == 2 ? cluster_id_x() : blockIdx.x;
+    const int tile_stride = CTAS == 2 ? num_clusters_x() : gridDim.x;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+        mbar_init(smem_u32(&bar_tmem_full), 1);
+        mbar_init(smem_u32(&bar_tmem_empty), CTAS * C::EPI_WARPS);
+        fence_mbar_init();
+        prefetch_tensormap(&tmA); prefetch_tensormap(&tmB);
+        if (SCALED) { prefetch_tensormap(&tmSA); prefetch_tensormap(&tmSB); }
+    }
+    if (warp == 1) {
+        tmem_alloc<CTAS>(smem_u32(&s_tmem_base), C::TMEM_COLS);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    if constexpr (CTAS == 2) cluster_sync(); else __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    WaitCtx wc{&s_abort, p.status};
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer ----------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+                int m_blk, n_blk;
+                tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
+                const int a_row = m_blk * C::BM + int(cta_rank) * 128;
+                const int b_row = n_blk * BN + int(cta_rank) * C::BN_CTA;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                    const uint32_t full_local = smem_u32(&bar_full[stage]);
+                    if (is_leader) mbar_arrive_expect_tx(full_local, C::TX_BYTES);
+                    const int kx = kb * 128 / (KIND == KIND_BF16 ? 2 : 1);   // inner coordinate in tensor-map elements (bf16 or bytes)
+                    if constexpr (CTAS == 2) {
+                        const uint32_t full = mapa(full_local, 0);
+                        tma_load_2d_pair(sA + stage * C::A_BYTES, &tmA, full, kx, a_row);
+                        tma_load_2d_pair(sB + stage * C::B_BYTES, &tmB, full, kx, b_row);
+                        if constexpr (SCALED) {
+                            tma_load_3d_pair(sSA + stage * C::SFA_BYTES, &tmSA, full, 0, kb * C::SF_CHUNKS, m_blk * CTAS + int(cta_rank));
+#pragma unroll
+                            for (int j = 0; j < BN / 128; j++)
+                                tma_load_3d_pair(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES, &tmSB, full, 0, kb * C::SF_CHUNKS,
+                                                 n_blk * (BN / 128) + j);
+                        }
+                    } else {
+                        tma_load_2d(sA + stage * C::A_BYTES, &tmA, full_local, kx, a_row);
+                        tma_load_2d(sB + stage * C::B_BYTES, &tmB, full_local, kx, b_row);
+                        if constexpr (SCALED) {
+                            tma_load_3d(sSA + stage * C::SFA_BYTES, &tmSA, full_local, 0, kb * C::SF_CHUNKS, m_blk);
+#pragma unroll
+                            for (int j = 0; j < BN / 128; j++)
+                                tma_load_3d(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES, &tmSB, full_local, 0, kb * C::SF_CHUNKS,
+                                            n_blk * (BN / 128) + j);
+                        }
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // tail: do not leave while stage releases from the MMA thread may still be in flight
+            for (int s = 0; s < C::STAGES && ok; s++) {
+                ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer ------------
+        if (is_leader && elect_one()) {
+            uint32_t stage = 0, phase = 0, tile_phase = 0, slot = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+                if (!mbar_wait(wc, smem_u32(&bar_tmem_empty), tile_phase ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sfa_t = tmem_base + BN + slot * (C::SFA_COLS + C::SFB_COLS);
+                    const uint32_t sfb_t = sfa_t + C::SFA_COLS;
+                    if constexpr (SCALED) {
+#pragma unroll
+                        for (int c = 0; c < C::SF_CHUNKS; c++) {
+                            tc_cp_scale<CTAS>(sfa_t + 4 * c, smem_desc_scale(sSA + stage * C::SFA_BYTES + c * 512));
+#pragma unroll
+                            for (int j = 0; j < BN / 128; j++)
+                                tc_cp_scale<CTAS>(sfb_t + (BN / 128) * 4 * c + 4 * j,
+                                                  smem_desc_scale(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES + c * 512));
+                        }
+                    }
+                    const uint64_t a_desc = smem_desc_sw128(sA + stage * C::A_BYTES);
+                    const uint64_t b_desc = smem_desc_sw128(sB + stage * C::B_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+                        // +32 bytes of K inside the 128-byte swizzle panel = +2 in the (addr >> 4) field
+                        if constexpr (KIND == KIND_BF16) {
+                            mma_f16<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::BM, BN), acc);
+                        } else if constexpr (KIND == KIND_MXFP8) {
+                            mma_mxfp8<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::BM, BN, j), acc, sfa_t, sfb_t);
+                        } else {
+                            mma_nvfp4<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(C::BM, BN), acc, sfa_t + 4 * j,
+                                            sfb_t + (BN / 128) * 4 * j);
+                        }
+                    }
+                    tc_commit<CTAS>(smem_u32(&bar_empty[stage]));       // frees the stage (in both CTAs)
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    slot = (slot + 1) % C::SF_SLOTS;
+                }
+                tc_commit<CTAS>(smem_u32(&bar_tmem_full));               // accumulator complete (both CTAs)
+                tile_phase ^= 1;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- epilogue --------------
+        const int ew = warp - 2;
+        const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
+        const int col_base = (ew >> 2) * C::COLS_PER_EPI_WARP;
+        float alpha = 1.0f;
+        if constexpr (KIND == KIND_NVFP4) alpha = __fmul_rn(*p.sgA, *p.sgB);
+        const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
+        uint32_t tile_phase = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+            int m_blk, n_blk;
+            tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
+            if (!mbar_wait(wc, smem_u32(&bar_tmem_full), tile_phase)) { ok = false; break; }
+            tile_phase ^= 1;
+            tc_fence_after();
+            uint32_t packed[C::COLS_PER_EPI_WARP / 2];
+#pragma unroll
+            for (int c = 0; c < C::COLS_PER_EPI_WARP / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 32 * c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    packed[c * 16 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r[2 * i]), alpha), __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha));
+            }
+            // accumulator drained: hand tensor memory back before touching global memory
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CTAS == 2) mbar_arrive_cluster(tmem_empty_leader); else mbar_arrive(tmem_empty_leader);
+            }
+            const int row = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32 + lane;
+            const int col0 = n_blk * BN + col_base;
+            if (row < p.M) {
+                __nv_bfloat16* drow = p.D + int64_t(row) * p.ldd;
+#pragma unroll
+                for (int g = 0; g < C::COLS_PER_EPI_WARP / 8; g++) {
+                    const int col = col0 + 8 * g;
+                    if (col + 8 <= p.N) {
+                        *reinterpret_cast<uint4*>(drow + col) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+                    } else {
+                        for (int e = 0; e < 8; e++)
+                            if (col + e < p.N) {
+                                const uint32_t w = packed[4 * g + e / 2];
+                                reinterpret_cast<uint16_t*>(drow)[col + e] = uint16_t((e & 1) ? (w >> 16) : (w & 0xffffu));
+                            }
+                    }
+                }
+            }
+        }
+    }
+
+    // ----------------------------------------------------------------- teardown --------------
+    tc_fence_before();
+    if constexpr (CTAS == 2) cluster_sync(); else __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------ host -------
+template <int KIND, int CTAS, int BN>
+static cudaError_t launch_t(const GemmArgs& a) {
+    using C = GemmCfg<KIND, CTAS, BN>;
+    auto kern = gemm_kernel<KIND, CTAS, BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int tiles = ((a.M + C::BM - 1) / C::BM) * ((a.N + BN - 1) / BN);
+    int units = a.sm_count / CTAS;
+    if (units > tiles) units = tiles;
+    if (units < 1) units = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units * CTAS, 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    GemmParams p{a.sgA, a.sgB, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.status};
+    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, p);
+}
+
+template <int KIND>
+static cudaError_t launch_k(const GemmArgs& a) {
+    switch (a.config & 3) {
+        case 0: return launch_t<KIND, 2, 256>(a);
+        case 1: return launch_t<KIND, 1, 256>(a);
+        case 2: return launch_t<KIND, 2, 128>(a);
+        default: return launch_t<KIND, 1, 128>(a);
+    }
+}
+
+int gemm_tile_n(int config) { return (config & 2) ? 128 : 256; }
+int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
+
+cudaError_t launch_gemm(const GemmArgs& a) {
+    switch (a.kind) {
+        case KIND_BF16: return launch_k<KIND_BF16>(a);
+        case KIND_MXFP8: return launch_k<KIND_MXFP8>(a);
+        case KIND_NVFP4: return launch_k<KIND_NVFP4>(a);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace tkb

@@ -1,0 +1,38 @@
+// Internal declarations shared by the translation units of libtkb200 (not part of the C ABI).
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace tkb {
+
+enum GemmKind : int { KIND_BF16 = 0, KIND_MXFP8 = 1, KIND_NVFP4 = 2 };
+
+struct QuantWork;
+struct NvQuantArgs;
+
+// quantize.cu / quantize_fast.cu
+cudaError_t launch_nvfp4_quantize_mode(const NvQuantArgs& a, int mode);
+cudaError_t launch_absmax(const void* A, int64_t lda, int M, int K, unsigned int* out_bits, int sm_count, cudaStream_t s);
+cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64_t ldc, void* sc, int M, int K, int sm_count,
+                                  cudaStream_t s);
+cudaError_t launch_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, cudaStream_t s);
+cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cudaStream_t s);
+
+// gemm.cu
+struct GemmArgs {
+    int kind;                 // 0 bf16, 1 mxfp8, 2 nvfp4
+    int config;               // bit 0: 0 = CTA pair (cta_group::2), 1 = single CTA; bit 1: 0 = N tile 256, 1 = N tile 128
+    CUtensorMap tmA, tmB, tmSA, tmSB;
+    const float* sgA; const float* sgB;
+    void* D; int64_t ldd;     // bf16 output, leading dimension in elements
+    int M, N, K;
+    int* status;
+    int sm_count;
+    cudaStream_t stream;
+};
+cudaError_t launch_gemm(const GemmArgs& a);
+int gemm_tile_n(int config);
+int gemm_tile_m(int config);
+
+} // namespace tkb

@@ -1,0 +1,236 @@
+// bf16 -> NVFP4 / MXFP8 quantize kernels (HBM-bound, CUDA cores only).
+//
+// Replaces nvfp4_quantize::{zero,absmax,divide,quantize}_kernel (ThunderKittens
+// kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:356-545) and mxfp8_quantize::kernel
+// (kernels/gemm/mxfp8_b200/mxfp8_b200_gemm.cu:328-430).  Same outputs (packed nibbles, swizzled
+// 512-byte scale chunks, fp32 per-tensor scale), different dataflow:
+//   * one persistent launch: tiles of 128 rows x 128 columns are walked grid-stride, each thread
+//     owns 8 consecutive bf16 (one 16-byte load) of 8 rows, so a half-warp reads one 256-byte row
+//     segment and writes one 64-byte (NVFP4) or 128-byte (MXFP8) code segment: fully coalesced,
+//     no shared-memory round trip for the data;
+//   * the per-tensor amax pass of NVFP4 is fused into the same launch (cooperative grid, one
+//     bounded grid barrier between the two passes; the second pass re-reads through L2);
+//   * block amax comes from warp shuffles between the 2 (NVFP4) or 4 (MXFP8) lanes that share a
+//     block; scales are staged in 1 KB of shared memory so each 512-byte chunk leaves as one
+//     coalesced store.
+// The arithmetic policy `Arith` fixes the exact floating-point operation sequence (see
+// quantize.cu / quantize_fast.cu).
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <cuda_runtime.h>
+#include "quantize_types.h"
+
+namespace tkb {
+
+
+constexpr int QT_ROWS = 128, QT_COLS = 128, Q_THREADS = 256;
+#ifndef TKB_SPIN_LIMIT_CYCLES
+#define TKB_SPIN_LIMIT_CYCLES (2000000000ll)
+#endif
+
+__device__ __forceinline__ uint32_t habs2_max(uint32_t a, uint32_t b) {
+    __nv_bfloat162 x = __habs2(*reinterpret_cast<__nv_bfloat162*>(&a));
+    __nv_bfloat162 y = __habs2(*reinterpret_cast<__nv_bfloat162*>(&b));
+    __nv_bfloat162 m = __hmax2(x, y);
+    return *reinterpret_cast<uint32_t*>(&m);
+}
+// max |x| over the 8 bf16 packed in v, as a float (NaNs are dropped by __hmax2, as in the reference)
+__device__ __forceinline__ float amax8(const uint4& v) {
+    uint32_t m = habs2_max(habs2_max(v.x, v.y), habs2_max(v.z, v.w));
+    __nv_bfloat162 mm = *reinterpret_cast<__nv_bfloat162*>(&m);
+    return __bfloat162float(__hmax(mm.x, mm.y));
+}
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ float e4m3_to_float(uint8_t c) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(c, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+struct TileCoord { int row0, col0; };
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_n) {
+    return TileCoord{(tile / tiles_n) * QT_ROWS, (tile % tiles_n) * QT_COLS};
+}
+
+// Loads this thread's 8 x 16 bytes of a tile (zeros outside the matrix).
+__device__ __forceinline__ void load_tile(const __nv_bfloat16* A, int64_t lda, int M, int K, TileCoord tc, int warp, int lane,
+                                          uint4 (&v)[8]) {
+    const int col = tc.col0 + (lane & 15) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = tc.row0 + warp * 16 + 2 * i + (lane >> 4);
+        if (row < M && col < K) v[i] = __ldg(reinterpret_cast<const uint4*>(A + int64_t(row) * lda + col));
+        else v[i] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Bounded grid barrier on a QuantWork slot.  Returns the agreed per-tensor amax, or a negative
+// value when the wait ran out (status receives the timeout code).
+__device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status) {
+    __shared__ float s_amax;
+    __shared__ float s_warp[Q_THREADS / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) block_amax = fmaxf(block_amax, __shfl_xor_sync(0xffffffffu, block_amax, o));
+    if (lane == 0) s_warp[warp] = block_amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = s_warp[0];
+#pragma unroll
+        for (int w = 1; w < Q_THREADS / 32; w++) m = fmaxf(m, s_warp[w]);
+        atomicMax(&ws->amax_bits, __float_as_uint(m));
+        __threadfence();
+        atomicAdd(&ws->arrived, 1u);
+        const long long t0 = clock64();
+        bool ok = true;
+        while (*reinterpret_cast<volatile unsigned int*>(&ws->arrived) < gridDim.x) {
+            if (clock64() - t0 > TKB_SPIN_LIMIT_CYCLES) { ok = false; break; }
+            __nanosleep(64);
+        }
+        __threadfence();
+        float r = ok ? __uint_as_float(*reinterpret_cast<volatile unsigned int*>(&ws->amax_bits)) : -1.0f;
+        if (!ok && status) atomicExch(status, 4 /* timeout */);
+        // the last block to leave restores the slot for the next call
+        if (atomicAdd(&ws->departed, 1u) == gridDim.x - 1) {
+            ws->amax_bits = 0u; ws->departed = 0u;
+            __threadfence();
+            ws->arrived = 0u;
+        }
+        s_amax = r;
+    }
+    __syncthreads();
+    return s_amax;
+}
+
+// ------------------------------------------------------------------------------ NVFP4 -----
+// Arith supplies:
+//   static void global_scales(float amax, float& sg_dec, float& sg_enc)
+//   static float block_scale(float amax16, float sg_enc)             value fed to the e4m3 conversion
+//   static float block_enc(float s_local_dec, float sg_dec)          multiplier applied to the inputs
+//   static float scale_value(float x, float s_enc)
+template <class Arith, bool SCALE_2D, bool FUSED_AMAX>
+__global__ void __launch_bounds__(Q_THREADS)
+nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
+                      uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
+                      int M, int K, int* status) {
+    __shared__ __align__(16) uint8_t s_sc[2][2][512];   // [double buffer][chunk][byte]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
+    const int tiles_m = (M + QT_ROWS - 1) / QT_ROWS;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_chunks = K / 64;
+
+    float amax;
+    if constexpr (FUSED_AMAX) {
+        float local = 0.f;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            uint4 v[8];
+            load_tile(A, lda, M, K, tile_coord(tile, tiles_n), warp, lane, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
+        }
+        amax = grid_amax_barrier(ws, local, status);
+        if (amax < 0.f) return;
+    } else {
+        amax = *amax_in;
+    }
+    float sg_dec, sg_enc;
+    Arith::global_scales(amax, sg_dec, sg_enc);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *sg = sg_dec;
+
+    int buf = 0;
+    // walk the tiles in reverse: the tail of the amax pass is the part most likely still in L2
+    for (int t = num_tiles - 1 - int(blockIdx.x); t >= 0; t -= gridDim.x, buf ^= 1) {
+        const TileCoord tc = tile_coord(t, tiles_n);
+        uint4 v[8];
+        load_tile(A, lda, M, K, tc, warp, lane, v);
+        float am[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float a = amax8(v[i]);
+            am[i] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+        }
+        if constexpr (SCALE_2D) {
+            float a = am[0];
+#pragma unroll
+            for (int i = 1; i < 8; i++) a = fmaxf(a, am[i]);
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+#pragma unroll
+            for (int i = 0; i < 8; i++) am[i] = a;
+        }
+        const int kb_local = (lane & 15) >> 1;        // 16-element block within the 128-column tile
+        const int col = tc.col0 + (lane & 15) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int r = warp * 16 + 2 * i + (lane >> 4);     // row within the tile
+            const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(am[i], sg_enc), __NV_SATFINITE, __NV_E4M3);
+            if ((lane & 1) == 0) s_sc[buf][kb_local >> 2][(r & 31) * 16 + (r >> 5) * 4 + (kb_local & 3)] = s8;
+            const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
+            const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float2 f = bf16x2_to_f2(w[j]);
+                f.x = Arith::scale_value(f.x, s_enc);
+                f.y = Arith::scale_value(f.y, s_enc);
+                packed |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * j);
+            }
+            const int row = tc.row0 + r;
+            if (row < M && col < K) *reinterpret_cast<uint32_t*>(codes + int64_t(row) * ldc + col / 2) = packed;
+        }
+        __syncthreads();
+        {
+            const int c = threadIdx.x >> 7, word = threadIdx.x & 127;
+            const int kc = tc.col0 / 64 + c;
+            if (kc < k_chunks) {
+                uint32_t* dst = reinterpret_cast<uint32_t*>(sc + (int64_t(tc.row0 / 128) * k_chunks + kc) * 512);
+                dst[word] = reinterpret_cast<const uint32_t*>(&s_sc[buf][c][0])[word];
+            }
+        }
+        // the next iteration writes the other staging buffer; the one after that is fenced by the
+        // __syncthreads() of the iteration in between
+    }
+}
+
+} // namespace tkb
+
+// ------------------------------------------------------------------------------ host ------
+namespace tkb {
+
+
+template <class Arith, bool S2D, bool FUSED>
+inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
+    auto kern = nvfp4_quantize_kernel<Arith, S2D, FUSED>;
+    const int tiles = ((a.M + QT_ROWS - 1) / QT_ROWS) * ((a.K + QT_COLS - 1) / QT_COLS);
+    static int blocks_per_sm = 0;   // same for every instantiation's first call; cheap to query once each
+    if (blocks_per_sm == 0) {
+        int b = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, Q_THREADS, 0);
+        if (e != cudaSuccess) return e;
+        blocks_per_sm = b < 1 ? 1 : (b > 4 ? 4 : b);
+    }
+    int grid = a.sm_count * blocks_per_sm;
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) grid = 1;
+    const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(a.A);
+    uint8_t* codes = static_cast<uint8_t*>(a.codes);
+    uint8_t* sc = static_cast<uint8_t*>(a.sc);
+    int64_t lda = a.lda, ldc = a.ldc;
+    float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
+    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status};
+    if (FUSED) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
+    return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
+}
+
+template <class Arith>
+inline cudaError_t launch_nvfp4_quantize(const NvQuantArgs& a) {
+    const bool fused = a.amax_in == nullptr;
+    if (a.scale_2d) return fused ? launch_nvfp4_quantize_t<Arith, true, true>(a) : launch_nvfp4_quantize_t<Arith, true, false>(a);
+    return fused ? launch_nvfp4_quantize_t<Arith, false, true>(a) : launch_nvfp4_quantize_t<Arith, false, false>(a);
+}
+
+} // namespace tkb

@@ -1,0 +1,20 @@
+// Host-visible types of the quantize kernels (shared by api.cu and the kernel translation units).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace tkb {
+
+struct QuantWork {            // one slot of library-owned scratch per in-flight NVFP4 quantize call
+    unsigned int amax_bits;   // running maximum of |x| as fp32 bits (non-negative floats order as uints)
+    unsigned int arrived;     // grid-barrier arrival counter
+    unsigned int departed;    // blocks that have consumed amax_bits; the last one re-zeroes the slot
+    unsigned int pad;
+};
+
+struct NvQuantArgs {
+    const void* A; int64_t lda; void* codes; int64_t ldc; void* sc; float* sg; const float* amax_in; QuantWork* ws;
+    int M, K, scale_2d; int* status; cudaStream_t stream; int sm_count;
+};
+
+} // namespace tkb
