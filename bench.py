@@ -1,0 +1,398 @@
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic input:
+
+  N = 1   workload = MXFP8 GEMM M=N=K=8192 (bf16 ~N(0,1) with 1 % of entries x32, quantized to e4m3 with per-32
+          UE8M0 scales, fp32 accumulate, bf16 out).  `value` = TFLOP/s of the GEMM with operands resident in HBM;
+          `e2e` = the same FLOPs through the C-ABI calls a user makes, starting from bf16 matrices in pinned HOST
+          memory: H2D copies, both quantize launches, the GEMM and the D2H copy of D are all inside the timed region.
+  N > 1   workload = tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192 (tp.py), strong scaling; until a rank count is
+          supported by the TP path the ranks run independent replicas of the N=1 workload ("replicas", weak).
+
+`--impl reference` times the reference's CPU implementation of the same GEMM arithmetic — its own naive kernels from
+kernels/gemm/common.cuh compiled for the host (oracle/_ref) when that build exists, otherwise the oracle's C++
+restatement — on all host cores, on a bounded row slab of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOPS = 2.0 * M * N * K
+NOMINAL = {"bf16": 2250.0, "fp8": 4500.0, "fp4": 9000.0, "hbm_gbs": 8000.0}
+
+
+def measured_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks ------
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons through NVML (read-only) from a background thread while a
+    timed region runs; the timed loops here last only milliseconds, too short for `nvidia-smi -lms`."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []          # (sm_mhz, power_w, reasons_mask)
+        self.max_mhz = None
+        self._stop = False
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                self.samples.append((float(mhz), pw, int(rs)))
+            except Exception:
+                break
+            time.sleep(0.0005)
+
+    def __enter__(self):
+        if self._h is not None:
+            import threading
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        power = [p for _, p, _ in self.samples]
+        thr = (min(power) + max(power)) / 2
+        loaded = [c for c, p, _ in self.samples if p >= thr] or [c for c, _, _ in self.samples]
+        mask = 0
+        for _, _, r in self.samples:
+            mask |= r
+        return {"sm_mhz": statistics.median(loaded), "sm_min_mhz": min(c for c, _, _ in self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for b, n in self.REASONS.items() if mask & b), "samples": len(self.samples),
+                "power_w_max": max(power)}
+
+
+# ----------------------------------------------------------------------------- CPU arm -----
+def cpu_reference_gemm(steps: int, warmup: int, rows: int = 16):
+    """Times the reference's CPU arithmetic for the N=1 workload on a `rows`-row slab (full N, full K)."""
+    import numpy as np
+    import oracle as O
+    rng = np.random.default_rng(3)
+    A = rng.standard_normal((rows, K)).astype(np.float32)
+    A[rng.random((rows, K)) < 0.01] *= 32.0
+    # B: 8192 x 8192 generated in blocks to keep peak memory modest
+    B = rng.standard_normal((N, K)).astype(np.float32)
+    B[rng.random((N, K)) < 0.01] *= 32.0
+    ac, asc = O.mxfp8_quantize(O.f32_to_bf16(A))
+    bc, bsc = O.mxfp8_quantize(O.f32_to_bf16(B))
+    del A, B
+    ref = O.ref_host()
+    cores = O.num_threads()
+    if ref is not None:
+        kind = "reference"
+        # the reference kernel indexes the scale tensor by row; give it a full 128-row block
+        D = np.empty((rows, N), np.uint16)
+        def run():
+            ref.tkref_mxfp8_gemm(ac, asc.reshape(-1), bc, bsc.reshape(-1), D, rows, N, K)
+    else:
+        kind = "port"
+        def run():
+            O.mxfp8_gemm(ac, asc, bc, bsc, 0, rows)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / steps
+    tflops = 2.0 * rows * N * K / dt * 1e-12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"{rows} of {M} output rows x full N={N} x full K={K} per step, {steps} steps ({dt:.2f} s/step)"}, dt
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, dt = cpu_reference_gemm(max(1, args.steps), max(0, min(args.warmup, 1)), rows=16)
+    line = {"impl": "reference", "metric": "block-scaled GEMM throughput (MXFP8 8192^3)", "value": cb["value"], "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (M / 16),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8 (e4m3 x ue8m0, fp32 acc)",
+            "data": "synthetic", "config": {"workload": "MXFP8 GEMM M=N=K=8192, 1% x32 outliers", "timed": "CPU row slab"},
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm -----
+def synth(torch, dev, rows, cols, seed, std=1.0, outliers=0.0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32) * std
+    if outliers > 0:
+        mask = torch.rand(rows, cols, generator=g, device=dev) < outliers
+        x = torch.where(mask, x * 32.0, x)
+    return x.to(torch.bfloat16)
+
+
+def event_time(torch, fn, steps, cooldown=0.5):
+    """CUDA-event time per step on the current stream.  A 500 ms idle period precedes the timed loop, as in the
+    reference's own protocol (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:673-700), so the loop starts from the
+    same thermal/power state every time."""
+    s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    time.sleep(cooldown)
+    s.record()
+    for i in range(steps):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) * 1e-3 / steps
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()   # fail loudly if the CUDA library is missing
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    u8 = torch.uint8
+    GROUPS = 3   # rotating operand sets: 3 x (64 + 64 + 128 MiB) so every launch starts with a cold L2
+    groups = []
+    for gi in range(GROUPS):
+        A = synth(torch, dev, M, K, 3 + 10 * gi + 100 * rank, outliers=0.01)
+        B = synth(torch, dev, N, K, 4 + 10 * gi + 100 * rank, outliers=0.01)
+        a = torch.empty(M, K, dtype=u8, device=dev); asc = torch.empty(M // 128, K // 128, 512, dtype=u8, device=dev)
+        b = torch.empty(N, K, dtype=u8, device=dev); bsc = torch.empty(N // 128, K // 128, 512, dtype=u8, device=dev)
+        ops.mxfp8_quantize(A, a, asc); ops.mxfp8_quantize(B, b, bsc)
+        groups.append((a, asc, b, bsc, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        if gi == 0:
+            hostA = A.cpu().pin_memory(); hostB = B.cpu().pin_memory()
+        del A, B
+    torch.cuda.synchronize()
+
+    def step(i):
+        ops.mxfp8_gemm(*groups[i % GROUPS])
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    with ClockSampler(local_rank) as cs:
+        dt = event_time(torch, step, args.steps)
+    clocks = cs.summary()
+    assert _lib.device_status() == 0, "a device-side wait timed out"
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    barrier()
+
+    # end to end: bf16 in pinned host memory -> H2D -> quantize x2 -> GEMM -> D2H
+    dA = torch.empty(M, K, dtype=torch.bfloat16, device=dev); dB = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+    hostD = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    a, asc, b, bsc, D = groups[0]
+
+    def e2e_step(i):
+        dA.copy_(hostA, non_blocking=True); dB.copy_(hostB, non_blocking=True)
+        ops.mxfp8_quantize(dA, a, asc); ops.mxfp8_quantize(dB, b, bsc)
+        ops.mxfp8_gemm(a, asc, b, bsc, D)
+        hostD.copy_(D, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(2):
+        e2e_step(i)
+    barrier()
+    dt_e2e = event_time(torch, e2e_step, e2e_steps)
+    if world > 1:
+        t = torch.tensor([dt_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt_e2e = float(t.item())
+
+    extras = {}
+    if rank == 0:
+        extras = side_measurements(torch, ops, dev)
+
+    if rank == 0:
+        pk = measured_peaks()
+        tflops = FLOPS / dt * 1e-12
+        peak = 2.0 * pk["bf16_tflops"]
+        line = {
+            "metric": "block-scaled GEMM throughput (MXFP8 8192^3)", "value": tflops * world, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "mxfp8 (e4m3 x ue8m0, fp32 acc)", "data": "synthetic",
+            "config": {"workload": "MXFP8 GEMM M=N=K=8192, bf16~N(0,1) with 1% x32 outliers, per-32 UE8M0 scales, bf16 out",
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
+                       "l2": f"{GROUPS} rotating operand sets of 256 MiB (> 126 MB L2)"},
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                         "traffic": None, "kernel": "tkb::gemm_kernel<MXFP8, cta pair, N256>",
+                         "peak_source": f"2 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense FP8 ceiling)",
+                         "frac_of_nominal_4500": tflops / NOMINAL["fp8"]},
+            "e2e": {"value": FLOPS / dt_e2e * 1e-12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
+                    "d2h_bytes_per_step": M * N * 2, "ms_per_step": dt_e2e * 1e3,
+                    "path": "pinned host bf16 -> H2D -> tkb_mxfp8_quantize x2 -> tkb_mxfp8_gemm -> D2H"},
+            "gpu_launches": args.steps, "clocks": clocks, "extra": extras,
+        }
+        if world == 1:
+            cb, _ = cpu_reference_gemm(3, 1, rows=16)
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def side_measurements(torch, ops, dev) -> dict:
+    """Other single-GPU rows of the path, timed the same way (CUDA events, rotating buffers)."""
+    out = {}
+    u8 = torch.uint8
+    pk = measured_peaks()
+
+    def quant4(X):
+        r, k = X.shape
+        c = torch.empty(r, k // 2, dtype=u8, device=dev); s = torch.empty((r + 127) // 128, k // 64, 512, dtype=u8, device=dev)
+        g = torch.empty(1, dtype=torch.float32, device=dev)
+        ops.nvfp4_quantize(X, c, s, g, False)
+        return c, s, g
+
+    try:
+        gs = []
+        for gi in range(3):
+            A = synth(torch, dev, M, K, 21 + gi); B = synth(torch, dev, N, K, 31 + gi, std=0.02)
+            gs.append((*quant4(A), *quant4(B), torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+            del A, B
+        f = lambda i: ops.nvfp4_gemm(*gs[i % 3])
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        tf = FLOPS / t * 1e-12
+        out["nvfp4_gemm_8192"] = {"tflops": tf, "us": t * 1e6, "frac_of_4x_measured_bf16": tf / (4 * pk["bf16_tflops"]),
+                                  "frac_of_nominal_9000": tf / NOMINAL["fp4"]}
+        del gs
+        torch.cuda.empty_cache()
+        gs = [(synth(torch, dev, M, K, 41 + gi), synth(torch, dev, N, K, 51 + gi), torch.empty(M, N, dtype=torch.bfloat16, device=dev)) for gi in range(3)]
+        f = lambda i: ops.bf16_gemm(*gs[i % 3])
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        tf = FLOPS / t * 1e-12
+        out["bf16_gemm_8192"] = {"tflops": tf, "us": t * 1e6, "frac_of_measured_bf16": tf / pk["bf16_tflops"]}
+        # quantize kernels (HBM-bound)
+        qs = [(g[0], torch.empty(M, K // 2, dtype=u8, device=dev), torch.empty(M // 128, K // 64, 512, dtype=u8, device=dev),
+               torch.empty(1, dtype=torch.float32, device=dev)) for g in gs]
+        f = lambda i: ops.nvfp4_quantize(*qs[i % 3], False)
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        out["nvfp4_quantize_8192x8192"] = {"us": t * 1e6, "gbs_two_pass_bytes": M * K * (2 + 2 + 0.5 + 1 / 16) / t * 1e-9,
+                                           "gbs_one_pass_bytes": M * K * (2 + 0.5 + 1 / 16) / t * 1e-9}
+        q8 = [(g[0], torch.empty(M, K, dtype=u8, device=dev), torch.empty(M // 128, K // 128, 512, dtype=u8, device=dev)) for g in gs]
+        f = lambda i: ops.mxfp8_quantize(*q8[i % 3])
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        gbs = M * K * (2 + 1 + 1 / 32) / t * 1e-9
+        out["mxfp8_quantize_8192x8192"] = {"us": t * 1e6, "gbs": gbs, "frac_of_measured_hbm": gbs / pk["hbm_gbs"]}
+    except Exception as e:   # side measurements never invalidate the headline line
+        out["error"] = repr(e)
+    return out
+
+
+def run_case(args) -> None:
+    """One kernel of the path, a few launches, nothing else: the command line used for ncu captures
+    (python bench.py --case nvfp4_gemm --size 8192 --steps 3)."""
+    import torch
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    u8 = torch.uint8
+    m, n, k = args.size if args.m is None else args.m, args.size, args.size if args.k is None else args.k
+    A = synth(torch, dev, m, k, 1, outliers=0.01 if "mxfp8" in args.case else 0.0)
+    B = synth(torch, dev, n, k, 2, std=1.0 if "mxfp8" in args.case or "bf16" in args.case else 0.02)
+    D = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    if args.case == "nvfp4_gemm" or args.case == "nvfp4_quantize":
+        a = torch.empty(m, k // 2, dtype=u8, device=dev); asc = torch.empty((m + 127) // 128, k // 64, 512, dtype=u8, device=dev); ag = torch.empty(1, device=dev)
+        b = torch.empty(n, k // 2, dtype=u8, device=dev); bsc = torch.empty((n + 127) // 128, k // 64, 512, dtype=u8, device=dev); bg = torch.empty(1, device=dev)
+        ops.nvfp4_quantize(A, a, asc, ag, False); ops.nvfp4_quantize(B, b, bsc, bg, False)
+        fn = (lambda: ops.nvfp4_gemm(a, asc, ag, b, bsc, bg, D, args.config)) if args.case == "nvfp4_gemm" else (lambda: ops.nvfp4_quantize(A, a, asc, ag, False))
+    elif args.case == "mxfp8_gemm" or args.case == "mxfp8_quantize":
+        a = torch.empty(m, k, dtype=u8, device=dev); asc = torch.empty((m + 127) // 128, k // 128, 512, dtype=u8, device=dev)
+        b = torch.empty(n, k, dtype=u8, device=dev); bsc = torch.empty((n + 127) // 128, k // 128, 512, dtype=u8, device=dev)
+        ops.mxfp8_quantize(A, a, asc); ops.mxfp8_quantize(B, b, bsc)
+        fn = (lambda: ops.mxfp8_gemm(a, asc, b, bsc, D, args.config)) if args.case == "mxfp8_gemm" else (lambda: ops.mxfp8_quantize(A, a, asc))
+    elif args.case == "bf16_gemm":
+        fn = lambda: ops.bf16_gemm(A, B, D, args.config)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    for _ in range(max(args.warmup, 0)):
+        fn()
+    t = event_time(torch, lambda i: fn(), args.steps, cooldown=0.0)
+    assert _lib.device_status() == 0
+    print(json.dumps({"case": args.case, "m": m, "n": n, "k": k, "us": t * 1e6, "tflops": 2.0 * m * n * k / t * 1e-12}))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, help="run a single kernel only (for profiling): nvfp4_gemm, mxfp8_gemm, bf16_gemm, nvfp4_quantize, mxfp8_quantize")
+    ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--m", type=int, default=None)
+    ap.add_argument("--k", type=int, default=None)
+    ap.add_argument("--config", default=None)
+    args = ap.parse_args()
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

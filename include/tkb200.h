@@ -59,6 +59,12 @@ const char* tkb_last_error(void);
  * Synchronises `stream`, returns the word through *status and clears it. */
 int tkb_device_status(void* stream, int* status);
 
+/* Diagnostics (no counterpart in the reference): when set to a device buffer of 8 x uint64 per launched CTA,
+ * GEMM kernels record per-CTA wait cycles: [0] producer waiting for a free stage, [1] producer total,
+ * [2] MMA thread waiting for the accumulator to be drained, [3] MMA thread waiting for operands, [4] MMA total,
+ * [5] epilogue waiting for the accumulator, [6] epilogue drain.  NULL (default) switches it off. */
+int tkb_gemm_set_profile_buffer(void* device_u64);
+
 /* ---- quantize ----------------------------------------------------------------------------- */
 
 /* Replaces nvfp4_quantize(A_bf16, A_fp4x2, A_sc, A_sc_global, scale_2d)

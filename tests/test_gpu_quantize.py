@@ -103,8 +103,10 @@ def test_nvfp4_fast_mode_close_to_ieee(cuda, lib):
 
 def test_nvfp4_zero_and_edge_inputs(cuda, lib):
     Z = torch.zeros(128, 128, dtype=torch.bfloat16, device=cuda)
-    c, s, g = gpu_nvfp4_quantize(Z)
-    assert not c.any() and not s.any() and g[0] == 0.0
+    for arith, assoc in (("spec", "spec"), ("kernel_ieee", "kernel")):
+        c, s, g = gpu_nvfp4_quantize(Z, False, arith)
+        rc, rs, rg = O.nvfp4_quantize(np.zeros((128, 128), np.uint16), False, assoc)
+        assert not c.any() and not s.any() and g[0] == rg[0]     # spec: 1/(2688/1e-12); kernel order: 0
     A = randn_bf16((128, 128), seed=3)
     A[0, 0] = 3.0e38     # near bf16 max
     rc, rs, rg = O.nvfp4_quantize(bf16_bits(A))
@@ -144,7 +146,7 @@ def test_fp4_pack_unpack(cuda, lib):
 
 def test_full_size_quantize_properties(cuda, lib):
     """8192 x 8192 (the GEMM operand size of the headline configs): row slabs against the oracle with the
-    global amax, and idempotence: quantizing the dequantised tensor returns the same codes and scales."""
+    global amax, and the reconstruction error of the dequantised tensor."""
     g = torch.Generator(device=cuda).manual_seed(7)
     A = torch.randn(8192, 8192, generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16)
     codes, sc, sg = gpu_nvfp4_quantize(A)
@@ -159,10 +161,12 @@ def test_full_size_quantize_properties(cuda, lib):
     for r0 in (0, 8192 - 128):
         rc, rs = O.mxfp8_quantize(bf16_bits(A[r0:r0 + 128]))
         assert np.array_equal(mc[r0:r0 + 128], rc) and np.array_equal(ms[r0 // 128], rs[0])
-    # idempotence on a slab (dequantised values are exactly representable again)
-    deq = O.dequant_mxfp8(mc[:128], ms[:1])
-    c2, s2 = gpu_mxfp8_quantize(torch.from_numpy(deq).to(torch.bfloat16).to(cuda))
-    assert np.array_equal(O.e4m3_to_f32(c2) * 1.0, O.e4m3_to_f32(mc[:128])) and np.array_equal(s2, ms[:1])
+    # reconstruction error of the whole tensor stays at the format's level (e4m3: 3 mantissa bits; e2m1: 1)
+    a32 = A[:1024].float().cpu().numpy()
+    d8 = O.dequant_mxfp8(mc[:1024], ms[:8])
+    assert np.linalg.norm(d8 - a32) / np.linalg.norm(a32) < 0.04
+    d4 = O.dequant_nvfp4(codes[:1024], sc[:8], sg)
+    assert np.linalg.norm(d4 - a32) / np.linalg.norm(a32) < 0.15
 
 
 def test_argument_errors(cuda, lib):

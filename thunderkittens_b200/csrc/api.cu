@@ -47,6 +47,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
+static unsigned long long* g_prof = nullptr;   // tkb_gemm_set_profile_buffer
 
 static int get_ctx(DeviceCtx** out) {
     int dev = 0;
@@ -156,8 +157,17 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
     } else {
         g.tmSA = g.tmA; g.tmSB = g.tmB;
     }
-    g.sgA = A_sg; g.sgB = B_sg; g.D = D; g.ldd = ldd; g.M = M; g.N = N; g.K = K;
-    g.status = c->status; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
+    {
+        cuuint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+        cuuint64_t strides[1] = {uint64_t(ldd) * 2};
+        cuuint32_t box[2] = {64, 32};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode(&g.tmD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
+    }
+    g.sgA = A_sg; g.sgB = B_sg; g.M = M; g.N = N; g.K = K;
+    g.status = c->status; g.prof = g_prof; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
     TKB_CUDA(launch_gemm(g));
     return TKB_OK;
 }
@@ -189,6 +199,11 @@ extern "C" {
 
 int tkb_version(void) { return 100; }
 const char* tkb_last_error(void) { return g_err; }
+
+int tkb_gemm_set_profile_buffer(void* device_u64) {
+    g_prof = static_cast<unsigned long long*>(device_u64);
+    return TKB_OK;
+}
 
 int tkb_device_status(void* stream, int* status) {
     DeviceCtx* c;

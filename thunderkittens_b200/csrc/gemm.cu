@@ -19,7 +19,10 @@
 //     that use them, into one of four rotating slots next to the accumulator.
 //   * The accumulator is single-buffered (256 fp32 columns + scale slots do not leave room for two):
 //     the epilogue first drains it into registers as packed bf16, hands TMEM back to the MMA warp,
-//     and only then writes to global memory, so the stores overlap the next tile's main loop.
+//     and only then writes D, so the stores overlap the next tile's main loop.  Each epilogue warp
+//     owns a private 4 KB staging box (32 rows x 64 columns, 128-byte swizzle) and issues its own
+//     TMA stores: whole 128-byte lines reach L2, no cross-warp synchronisation, and rows / columns
+//     past M / N are clipped by the TMA unit.
 //   * Every mbarrier wait is bounded (ptx.cuh); on a timeout the kernel records the status, leaves
 //     its loops, joins the final cluster barrier, frees TMEM and returns.
 #include "ptx.cuh"
@@ -40,11 +43,13 @@ struct GemmCfg {
     static constexpr int SFA_BYTES = SF_CHUNKS * 512;
     static constexpr int SFB_BYTES = SF_CHUNKS * 512 * (BN / 128);
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
+    static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;
+    static constexpr int EPI_WARP_BYTES = 32 * 128;                  // one 32-row x 64-column bf16 store box per warp
+    static constexpr int EPI_BYTES = EPI_WARPS * EPI_WARP_BYTES;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 2048 - EPI_BYTES;
     static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
-    static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 2048;   // + alignment slack (base and staging area)
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
     static constexpr int COLS_PER_EPI_WARP = BN / (EPI_WARPS / 4);   // 128
     // tensor memory: accumulator at column 0, then rotating scale slots
@@ -59,9 +64,9 @@ struct GemmCfg {
 
 struct GemmParams {
     const float* sgA; const float* sgB;
-    __nv_bfloat16* D; int64_t ldd;
     int M, N, K;
     int* status;
+    unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
 };
 
 __device__ __forceinline__ void tile_to_block(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
@@ -88,7 +93,8 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, 
 template <int KIND, int CTAS, int BN>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
+            const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
     using C = GemmCfg<KIND, CTAS, BN>;
     constexpr bool SCALED = KIND != KIND_BF16;
 
@@ -109,6 +115,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t sB = sA + C::STAGES * C::A_BYTES;
     const uint32_t sSA = sB + C::STAGES * C::B_BYTES;
     const uint32_t sSB = sSA + C::STAGES * C::SFA_BYTES;
+    const uint32_t sEpi = (sSB + C::STAGES * C::SFB_BYTES + 1023u) & ~1023u;
 
     const int tiles_m = (p.M + C::BM - 1) / C::BM;
     const int tiles_n = (p.N + BN - 1) / BN;
@@ -123,7 +130,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         mbar_init(smem_u32(&bar_tmem_full), 1);
         mbar_init(smem_u32(&bar_tmem_empty), CTAS * C::EPI_WARPS);
         fence_mbar_init();
-        prefetch_tensormap(&tmA); prefetch_tensormap(&tmB);
+        prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD);
         if (SCALED) { prefetch_tensormap(&tmSA); prefetch_tensormap(&tmSB); }
     }
     if (warp == 1) {
@@ -141,13 +148,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            long long waited = 0;
+            const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
                 tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
                 const int a_row = m_blk * C::BM + int(cta_rank) * 128;
                 const int b_row = n_blk * BN + int(cta_rank) * C::BN_CTA;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                    { const long long t0 = clock64();
+                      if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                      waited += clock64() - t0; }
                     const uint32_t full_local = smem_u32(&bar_full[stage]);
                     if (is_leader) mbar_arrive_expect_tx(full_local, C::TX_BYTES);
                     const int kx = kb * 128 / (KIND == KIND_BF16 ? 2 : 1);   // inner coordinate in tensor-map elements (bf16 or bytes)
@@ -176,6 +187,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+            if (p.prof) { p.prof[blockIdx.x * 8 + 0] = waited; p.prof[blockIdx.x * 8 + 1] = clock64() - t_begin; }
             // tail: do not leave while stage releases from the MMA thread may still be in flight
             for (int s = 0; s < C::STAGES && ok; s++) {
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
@@ -188,11 +200,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (is_leader && elect_one()) {
             uint32_t stage = 0, phase = 0, tile_phase = 0, slot = 0;
             bool ok = true;
+            long long wait_acc = 0, wait_full = 0;
+            const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
-                if (!mbar_wait(wc, smem_u32(&bar_tmem_empty), tile_phase ^ 1)) { ok = false; break; }
+                { const long long t0 = clock64();
+                  if (!mbar_wait(wc, smem_u32(&bar_tmem_empty), tile_phase ^ 1)) { ok = false; break; }
+                  wait_acc += clock64() - t0; }
                 tc_fence_after();
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                    { const long long t0 = clock64();
+                      if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                      wait_full += clock64() - t0; }
                     tc_fence_after();
                     const uint32_t sfa_t = tmem_base + BN + slot * (C::SFA_COLS + C::SFB_COLS);
                     const uint32_t sfb_t = sfa_t + C::SFA_COLS;
@@ -228,6 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 tc_commit<CTAS>(smem_u32(&bar_tmem_full));               // accumulator complete (both CTAs)
                 tile_phase ^= 1;
             }
+            if (p.prof) { p.prof[blockIdx.x * 8 + 2] = wait_acc; p.prof[blockIdx.x * 8 + 3] = wait_full; p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin; }
         }
         __syncwarp();
     } else {
@@ -238,23 +257,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         float alpha = 1.0f;
         if constexpr (KIND == KIND_NVFP4) alpha = __fmul_rn(*p.sgA, *p.sgB);
         const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
+        const uint32_t stage_box = sEpi + ew * C::EPI_WARP_BYTES;
         uint32_t tile_phase = 0;
         bool ok = true;
+        long long wait_tf = 0, drain = 0;
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
             int m_blk, n_blk;
             tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
+            const long long t0 = clock64();
             if (!mbar_wait(wc, smem_u32(&bar_tmem_full), tile_phase)) { ok = false; break; }
+            const long long t1 = clock64();
+            wait_tf += t1 - t0;
             tile_phase ^= 1;
             tc_fence_after();
             uint32_t packed[C::COLS_PER_EPI_WARP / 2];
 #pragma unroll
-            for (int c = 0; c < C::COLS_PER_EPI_WARP / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 32 * c, r);
+            for (int c = 0; c < C::COLS_PER_EPI_WARP / 64; c++) {
+                uint32_t r[64];
+                tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 64 * c, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 16; i++)
-                    packed[c * 16 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r[2 * i]), alpha), __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha));
+                for (int i = 0; i < 32; i++)
+                    packed[c * 32 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r[2 * i]), alpha), __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha));
             }
             // accumulator drained: hand tensor memory back before touching global memory
             tc_fence_before();
@@ -262,25 +286,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (lane == 0) {
                 if constexpr (CTAS == 2) mbar_arrive_cluster(tmem_empty_leader); else mbar_arrive(tmem_empty_leader);
             }
-            const int row = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32 + lane;
+            drain += clock64() - t1;
+            const int row0 = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32;
             const int col0 = n_blk * BN + col_base;
-            if (row < p.M) {
-                __nv_bfloat16* drow = p.D + int64_t(row) * p.ldd;
 #pragma unroll
-                for (int g = 0; g < C::COLS_PER_EPI_WARP / 8; g++) {
-                    const int col = col0 + 8 * g;
-                    if (col + 8 <= p.N) {
-                        *reinterpret_cast<uint4*>(drow + col) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-                    } else {
-                        for (int e = 0; e < 8; e++)
-                            if (col + e < p.N) {
-                                const uint32_t w = packed[4 * g + e / 2];
-                                reinterpret_cast<uint16_t*>(drow)[col + e] = uint16_t((e & 1) ? (w >> 16) : (w & 0xffffu));
-                            }
-                    }
+            for (int h = 0; h < C::COLS_PER_EPI_WARP / 64; h++) {
+                // the previous store of this warp must have finished reading the staging box
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; j++)      // 16-byte chunk j of this thread's 128-byte row, 128-byte swizzle
+                    st_shared_v4(stage_box + lane * 128 + ((j ^ (lane & 7)) << 4), packed[h * 32 + 4 * j], packed[h * 32 + 4 * j + 1],
+                                 packed[h * 32 + 4 * j + 2], packed[h * 32 + 4 * j + 3]);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && row0 < p.M && col0 + 64 * h < p.N) {
+                    tma_store_2d(&tmD, stage_box, col0 + 64 * h, row0);
+                    tma_store_commit();
                 }
             }
         }
+        if (lane == 0) tma_store_wait<0>();
+        __syncwarp();
+        if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 8 + 5] = wait_tf; p.prof[blockIdx.x * 8 + 6] = drain; }
     }
 
     // ----------------------------------------------------------------- teardown --------------
@@ -316,8 +344,8 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    GemmParams p{a.sgA, a.sgB, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.status};
-    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, p);
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, a.status, a.prof};
+    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p);
 }
 
 template <int KIND>

@@ -23,11 +23,11 @@ cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cud
 struct GemmArgs {
     int kind;                 // 0 bf16, 1 mxfp8, 2 nvfp4
     int config;               // bit 0: 0 = CTA pair (cta_group::2), 1 = single CTA; bit 1: 0 = N tile 256, 1 = N tile 128
-    CUtensorMap tmA, tmB, tmSA, tmSB;
+    CUtensorMap tmA, tmB, tmSA, tmSB, tmD;   // tmD: bf16 output, box 64 columns x 32 rows, 128-byte swizzle
     const float* sgA; const float* sgB;
-    void* D; int64_t ldd;     // bf16 output, leading dimension in elements
     int M, N, K;
     int* status;
+    unsigned long long* prof;   // optional per-CTA wait counters, 8 x uint64 per CTA
     int sm_count;
     cudaStream_t stream;
 };

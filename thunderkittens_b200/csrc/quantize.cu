@@ -77,7 +77,7 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
             a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
             const float scale = fmaxf(__fmul_rn(a, 0.002232142857f), 0.000000000001f);
             const uint8_t s8 = (uint8_t)__nv_cvt_float_to_e8m0(scale, __NV_SATFINITE, cudaRoundPosInf);
-            if ((lane & 3) == 0) s_sc[buf][(r & 31) * 16 + (r >> 5) * 4 + kb_local] = s8;
+            if ((lane & 3) == 0) s_sc[buf][(r & 31) * 16 + (r >> 5) * 4 + kb_local] = (tc.row0 + r < M) ? s8 : uint8_t(0);   // rows past M: 0
             // 1 / 2^(s8-127): exact for every finite e8m0 code
             const float inv = __frcp_rn(s8 == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(uint32_t(s8) << 23));
             const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
