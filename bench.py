@@ -335,6 +335,31 @@ def side_measurements(torch, ops, dev) -> dict:
         t = event_time(torch, f, 10)
         gbs = M * K * (2 + 1 + 1 / 32) / t * 1e-9
         out["mxfp8_quantize_8192x8192"] = {"us": t * 1e6, "gbs": gbs, "frac_of_measured_hbm": gbs / pk["hbm_gbs"]}
+        del gs, qs, q8
+        torch.cuda.empty_cache()
+        # decode: activations quantized on the fly + skinny-M NVFP4 GEMM, weights N=28672 K=8192 (3 rotating copies)
+        Nw, Kw = 28672, 8192
+        ws = []
+        for gi in range(3):
+            W = synth(torch, dev, Nw, Kw, 61 + gi, std=0.02)
+            ws.append(quant4(W))
+            del W
+        for Md in (1, 16, 128):
+            X = synth(torch, dev, Md, Kw, 71 + Md)
+            xc = torch.empty(Md, Kw // 2, dtype=u8, device=dev); xs = torch.empty(1, Kw // 64, 512, dtype=u8, device=dev)
+            xg = torch.empty(1, dtype=torch.float32, device=dev)
+            Dd = torch.empty(Md, Nw, dtype=torch.bfloat16, device=dev)
+            def f(i):
+                ops.nvfp4_quantize(X, xc, xs, xg, False)
+                ops.nvfp4_gemm(xc, xs, xg, *ws[i % 3], Dd)
+            for i in range(3):
+                f(i)
+            t = event_time(torch, f, 20)
+            algo = Nw * Kw // 2 + Nw * Kw // 16 + 8 + Md * Kw * 2 + Md * Nw * 2
+            out[f"decode_nvfp4_M{Md}"] = {"us": t * 1e6, "algorithmic_bytes": algo, "gbs": algo / t * 1e-9,
+                                          "frac_of_measured_hbm": algo / t * 1e-9 / pk["hbm_gbs"],
+                                          "frac_of_nominal_8000": algo / t * 1e-9 / NOMINAL["hbm_gbs"],
+                                          "launches_per_step": 2}
     except Exception as e:   # side measurements never invalidate the headline line
         out["error"] = repr(e)
     return out

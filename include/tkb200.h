@@ -49,7 +49,8 @@ enum {
     TKB_GEMM_PAIR_N256 = 1,    /* two-CTA 256 x 256 tiles */
     TKB_GEMM_SINGLE_N256 = 2,  /* one-CTA 128 x 256 tiles */
     TKB_GEMM_PAIR_N128 = 3,    /* two-CTA 256 x 128 tiles */
-    TKB_GEMM_SINGLE_N128 = 4   /* one-CTA 128 x 128 tiles */
+    TKB_GEMM_SINGLE_N128 = 4,  /* one-CTA 128 x 128 tiles */
+    TKB_GEMM_SKINNY = 5        /* NVFP4, M <= 128: weight-streaming stream-K kernel (the default for such M) */
 };
 
 int tkb_version(void);
@@ -98,7 +99,10 @@ int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream);
 /* Replaces nvfp4_gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D) (nvfp4_b200_gemm.cu:748-770).
  *   A [M, K/2] bytes, B [N, K/2] bytes (row pitch K/2); A_sc/B_sc swizzled e4m3 chunks with
  *   ceil(rows/128) row blocks; A_sg/B_sg fp32[1]; D [M, N] bf16 with leading dimension ldd (0 = N).
- *   K % 64 == 0, N % 8 == 0; any M, N (the reference needs M,N,K % 256 == 0). */
+ *   K % 64 == 0, N % 8 == 0; any M, N (the reference needs M,N,K % 256 == 0).
+ *   M <= 128 ("decode" shapes, which the reference kernel cannot run) goes to a weight-streaming kernel that
+ *   uses library-owned scratch (per-CTA fp32 partial tiles); up to 4 such calls may be in flight on
+ *   different streams of one device. */
 int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
                    void* D, int64_t ldd, int M, int N, int K, void* stream);
 int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
@@ -115,6 +119,37 @@ int tkb_mxfp8_gemm_ex(const void* A, const void* A_sc, const void* B, const void
 int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream);
 int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
                      int config, void* stream);
+
+/* ---- single-node multi-GPU plumbing ------------------------------------------------------------
+ * Replaces, for this path, TKParallelTensor / KittensBroker (include/pyutils/parallel_tensor.cuh:23-336,
+ * include/pyutils/broker.cuh:340-547) and the device-side signal / wait helpers
+ * (include/ops/thread/util/sync.cuh:296-327).  One process per GPU.  A symmetric buffer is a tkb_dev_alloc
+ * allocation on every rank; its 64-byte CUDA IPC handle is exchanged by the host program and opened with
+ * tkb_ipc_open, which yields a device pointer into the peer's memory (NVLink peer access). */
+int tkb_dev_alloc(size_t bytes, void** ptr);          /* zero-filled, IPC-exportable device memory */
+int tkb_dev_free(void* ptr);
+int tkb_ipc_export(const void* ptr, void* handle64);
+int tkb_ipc_open(const void* handle64, void** ptr);
+int tkb_ipc_close(void* ptr);
+/* Stores `value` into element `index` of a 32-bit flag array on every peer (system-scope release; peer_flags[i]
+ * is rank i's array as seen from this rank).  Replaces signal_all (sync.cuh:301-309). */
+int tkb_signal_peers(void* const* peer_flags, int world, int rank, int index, unsigned int value, int include_self, void* stream);
+/* Blocks the stream until flags[i] >= value for all i != skip (bounded device-side wait; epochs only grow).
+ * Replaces wait / barrier_all (sync.cuh:311-327). */
+int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, void* stream);
+
+/* Tensor-parallel all-gather GEMM, NVFP4.  Replaces all_gather_matmul(A, B, C, barrier, num_comm_sms)
+ * (kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305; the reference ships bf16 and fp8 variants only).
+ *   D[M, N_local] = gather_rows(Xq)[M, K] . W_local[N_local, K]^T.
+ * peer_codes[i] / peer_scales[i]: rank i's gathered buffers ([M, K/2] bytes, [M/128, K/64, 512] bytes) as seen
+ * from this rank; entry `rank` is local and writable.  Each rank quantizes its M/world rows (with the all-reduced
+ * per-tensor amax, so X_sg is the same everywhere) into its own slice of its own buffers, then signals
+ * ready[rank] = epoch on every peer.  comm_ctas CTAs of the kernel pull the other slices over NVLink while the
+ * rest multiply, own rows first.  `ready` [world] and `arrived` [M/256] are 32-bit epoch arrays on this rank.
+ * M % (256 * world) == 0. */
+int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
+                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, const void* ready,
+                      void* arrived, unsigned int epoch, int comm_ctas, void* stream);
 
 #ifdef __cplusplus
 }

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libtkb200.so")
 
 OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
 NVFP4_SPEC, NVFP4_KERNEL_IEEE, NVFP4_KERNEL_FAST = 0, 1, 2
-GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128 = range(5)
+GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY = range(6)
 
 
 class TkbError(RuntimeError):
@@ -38,6 +38,15 @@ _SIGNATURES = {
     "tkb_mxfp8_gemm": ([_vp] * 5 + [_i64, _i, _i, _i, _vp], _i),
     "tkb_mxfp8_gemm_ex": ([_vp] * 5 + [_i64, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp], _i),
+    "tkb_gemm_set_profile_buffer": ([_vp], _i),
+    "tkb_dev_alloc": ([_sz, C.POINTER(_vp)], _i),
+    "tkb_dev_free": ([_vp], _i),
+    "tkb_ipc_export": ([_vp, _vp], _i),
+    "tkb_ipc_open": ([_vp, C.POINTER(_vp)], _i),
+    "tkb_ipc_close": ([_vp], _i),
+    "tkb_signal_peers": ([C.POINTER(_vp), _i, _i, _i, C.c_uint, _i, _vp], _i),
+    "tkb_wait_flags": ([_vp, _i, _i, C.c_uint, _vp], _i),
+    "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, C.c_uint, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
 

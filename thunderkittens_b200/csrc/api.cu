@@ -15,6 +15,13 @@ namespace tkb {
 
 static thread_local char g_err[512] = "";
 
+int api_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
 static int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -31,6 +38,9 @@ static int fail(int code, const char* fmt, ...) {
 // ------------------------------------------------------------------ per-device context -----
 constexpr int kMaxDevices = 64;
 constexpr int kQuantSlots = 256;
+constexpr int kDecodeRing = 4;
+constexpr int kDecodeMaxGrid = 160;                      // CTAs the scratch is sized for
+constexpr size_t kDecodePartialFloats = size_t(kDecodeMaxGrid) * 128 * 128;
 
 struct DeviceCtx {
     bool ready = false;
@@ -39,6 +49,10 @@ struct DeviceCtx {
     int* status = nullptr;          // device int, zero when healthy
     QuantWork* quant_ws = nullptr;  // kQuantSlots zeroed slots, each returned to zero by the kernel that used it
     std::atomic<unsigned> next_slot{0};
+    // skinny-M GEMM scratch: kDecodeRing independent sets of (per-CTA fp32 partial tiles, per-CTA flags)
+    float* decode_partials = nullptr;
+    unsigned int* decode_flags = nullptr;
+    std::atomic<unsigned> decode_calls{0};
 };
 static DeviceCtx g_ctx[kMaxDevices];
 static std::mutex g_ctx_mu;
@@ -109,6 +123,43 @@ static int make_scale_map(CUtensorMap* m, const void* base, uint64_t row_blocks,
     return TKB_OK;
 }
 
+static int ensure_decode_scratch(DeviceCtx* c) {
+    if (c->decode_partials) return TKB_OK;
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    if (c->decode_partials) return TKB_OK;
+    float* part = nullptr; unsigned int* flags = nullptr;
+    TKB_CUDA(cudaMalloc(&part, kDecodeRing * kDecodePartialFloats * sizeof(float)));
+    TKB_CUDA(cudaMalloc(&flags, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
+    TKB_CUDA(cudaMemset(flags, 0, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
+    TKB_CUDA(cudaDeviceSynchronize());
+    c->decode_flags = flags;
+    c->decode_partials = part;
+    return TKB_OK;
+}
+
+// Skinny-M NVFP4 GEMM (M <= 128): X is the activation (A operand of the public call), W the weight.
+static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const float* X_sg, const void* W, const void* W_sc,
+                         const float* W_sg, void* D, int64_t ldd, int M, int N, int K, void* stream) {
+    if (int e = ensure_decode_scratch(c)) return e;
+    DecodeArgs d;
+    memset(&d, 0, sizeof(d));
+    const int nb = decode_padded_rows(M);
+    if (int e = make_operand_map(&d.tmW, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(K / 2), N, K / 2, 128)) return e;
+    if (int e = make_operand_map(&d.tmX, X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(K / 2), M, K / 2, nb)) return e;
+    if (int e = make_scale_map(&d.tmSW, W_sc, (N + 127) / 128, K / 64, 4)) return e;
+    if (int e = make_scale_map(&d.tmSX, X_sc, 1, K / 64, 4)) return e;
+    const unsigned call = c->decode_calls.fetch_add(1);
+    const unsigned ring = call % kDecodeRing;
+    d.sgX = X_sg; d.sgW = W_sg; d.D = D; d.ldd = ldd; d.M = M; d.N = N; d.K = K;
+    d.partials = c->decode_partials + ring * kDecodePartialFloats;
+    d.flags = c->decode_flags + ring * kDecodeMaxGrid;
+    d.epoch = call / kDecodeRing + 1;           // strictly increasing per scratch set, never 0
+    d.max_grid = kDecodeMaxGrid;
+    d.status = c->status; d.sm_count = c->sm_count; d.stream = static_cast<cudaStream_t>(stream);
+    TKB_CUDA(launch_decode(d));
+    return TKB_OK;
+}
+
 static int pick_config(int config, int M, int N, int sm_count) {
     if (config >= TKB_GEMM_PAIR_N256 && config <= TKB_GEMM_SINGLE_N128) return config - 1;
     // default: CTA pairs; 256-wide N tiles unless that leaves most of the SMs without a tile
@@ -117,31 +168,10 @@ static int pick_config(int config, int M, int N, int sm_count) {
     return 2;
 }
 
-static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A_sc, const float* A_sg, const void* B,
-                       int64_t ldb_bytes, const void* B_sc, const float* B_sg, void* D, int64_t ldd, int M, int N, int K, int config,
-                       void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
-    if (!A || !B || !D) return fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
-    if (M < 1 || N < 1 || K < 1) return fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
-    if (config < 0 || config > TKB_GEMM_SINGLE_N128) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
-    const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : 8);
-    if (K % kmult) return fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
-    if (N % 8) return fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
-    if (ldd == 0) ldd = N;
-    if (ldd < N || ldd % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
-    if (!aligned16(A) || !aligned16(B) || !aligned16(D) || lda_bytes % 16 || ldb_bytes % 16)
-        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
-    if (kind != KIND_BF16) {
-        if (!A_sc || !B_sc) return fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
-        if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
-    }
-    if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
-
-    GemmArgs g;
-    memset(&g, 0, sizeof(g));
-    g.kind = kind;
-    g.config = pick_config(config, M, N, c->sm_count);
+// Tensor maps of one GEMM call (g->kind / g->config already set).
+int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
+                       const void* B_sc, void* D, int64_t ldd, int M, int N, int K) {
+    GemmArgs& g = *gp;
     const int ctas = (g.config & 1) ? 1 : 2;
     const int bn = gemm_tile_n(g.config);
     const int elem_bytes = kind == KIND_BF16 ? 2 : 1;
@@ -166,6 +196,48 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
     }
+    return TKB_OK;
+}
+
+int api_device(int* sm_count, int** status) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    *sm_count = c->sm_count;
+    *status = c->status;
+    return TKB_OK;
+}
+
+static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A_sc, const float* A_sg, const void* B,
+                       int64_t ldb_bytes, const void* B_sc, const float* B_sg, void* D, int64_t ldd, int M, int N, int K, int config,
+                       void* stream) {
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (!A || !B || !D) return fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
+    if (M < 1 || N < 1 || K < 1) return fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+    if (config < 0 || config > TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
+    if (config == TKB_GEMM_SKINNY && (kind != KIND_NVFP4 || M > 128))
+        return fail(TKB_ERR_INVALID_ARG, "gemm: the skinny-M kernel needs NVFP4 operands and M <= 128");
+    const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : 8);
+    if (K % kmult) return fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
+    if (N % 8) return fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
+    if (ldd == 0) ldd = N;
+    if (ldd < N || ldd % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
+    if (!aligned16(A) || !aligned16(B) || !aligned16(D) || lda_bytes % 16 || ldb_bytes % 16)
+        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
+    if (kind != KIND_BF16) {
+        if (!A_sc || !B_sc) return fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
+        if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
+    }
+    if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
+
+    if (kind == KIND_NVFP4 && M <= 128 && (config == TKB_GEMM_DEFAULT || config == TKB_GEMM_SKINNY))
+        return decode_common(c, A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, stream);
+
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.kind = kind;
+    g.config = pick_config(config, M, N, c->sm_count);
+    if (int e = api_make_gemm_maps(&g, kind, A, lda_bytes, A_sc, B, ldb_bytes, B_sc, D, ldd, M, N, K)) return e;
     g.sgA = A_sg; g.sgB = B_sg; g.M = M; g.N = N; g.K = K;
     g.status = c->status; g.prof = g_prof; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
     TKB_CUDA(launch_gemm(g));

@@ -1,0 +1,341 @@
+// Skinny-M ("decode") NVFP4 GEMM for sm_100a: D[M,N] (bf16) = X[M,K] * W[N,K]^T with M <= 128.
+//
+// The reference's nvfp4_gemm (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:88-307) needs M % 256 == 0,
+// so it has no kernel for these shapes; the arithmetic is the same block-scaled product as the large
+// GEMM and is checked against the same oracle.  The problem is bound by streaming the weights
+// (N*K/2 bytes of codes + N*K/16 bytes of scales) from HBM once, so the design is about keeping
+// every SM's TMA queue full and the work split evenly:
+//   * operands are swapped: the 128-row weight slab is the MMA's M side (tcgen05.mma M=128), the
+//     (padded) activation rows are its N side (N = 16/32/64/128), so no tensor-core work is wasted
+//     on padding a 1..128-row activation up to a 128/256-row tile;
+//   * stream-K: the (slab, 256-wide K-block) work items are cut into one contiguous, equal range per
+//     CTA (one persistent CTA per SM, cooperative launch).  A CTA that starts a slab finishes it; a
+//     CTA that only covers the tail of a slab writes its fp32 partial tile to scratch first thing
+//     and raises a flag.  The finisher reaches its (last) head segment after all its other work, so
+//     the partials it needs are normally already there; its wait is bounded like every other wait;
+//   * warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue; two accumulator buffers in
+//     tensor memory so the epilogue of one segment overlaps the main loop of the next.
+#include <cstdlib>
+#include "ptx.cuh"
+#include "internal.h"
+
+namespace tkb {
+
+template <int NB>
+struct DecodeCfg {
+    static_assert(NB == 16 || NB == 32 || NB == 64 || NB == 128, "");
+    static constexpr int W_BYTES = 128 * 128;            // 128 weight rows x 256 e2m1 of K
+    static constexpr int X_BYTES = NB * 128;
+    static constexpr int SF_BYTES = 4 * 512;             // 4 scale chunks (4 x 64 K) per 128 rows
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
+    static constexpr int STAGES_RAW = (227 * 1024 - 3072) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
+    static constexpr int THREADS = 6 * 32;
+    static constexpr int SF_SLOTS = 4;
+    static constexpr int SF_BASE = 2 * (NB < 32 ? 32 : NB);      // accumulators at columns 0 and ACC_STRIDE
+    static constexpr int ACC_STRIDE = NB < 32 ? 32 : NB;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr uint32_t TX_BYTES = STAGE_BYTES;
+    static constexpr int CHUNK = NB < 32 ? NB : 32;      // accumulator columns read per tcgen05.ld
+};
+
+struct DecodeParams {
+    const float* sgX; const float* sgW;
+    __nv_bfloat16* D; int64_t ldd;
+    int M, N, K;
+    float* partials;            // [grid][NB][128] fp32
+    unsigned int* flags;        // [grid]
+    unsigned int epoch;
+    int* status;
+};
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_d(uint32_t dst, const void* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+struct Segment { int slab, kb0, kb1; };
+
+// Work range of CTA g and iteration over its segments (identical in every role).
+struct WorkRange {
+    long long item, end; int kblk;
+    __device__ WorkRange(int g, int grid, int slabs, int kblk_) : kblk(kblk_) {
+        const long long items = (long long)slabs * kblk_;
+        item = items * g / grid;
+        end = items * (g + 1) / grid;
+    }
+    __device__ bool next(Segment& s) {
+        if (item >= end) return false;
+        s.slab = int(item / kblk);
+        s.kb0 = int(item % kblk);
+        const long long left = end - item;
+        s.kb1 = int(min((long long)kblk, s.kb0 + left));
+        item += s.kb1 - s.kb0;
+        return true;
+    }
+};
+
+template <int NB>
+__global__ void __launch_bounds__(DecodeCfg<NB>::THREADS, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+              const __grid_constant__ CUtensorMap tmSW, const __grid_constant__ CUtensorMap tmSX, const DecodeParams p) {
+    using C = DecodeCfg<NB>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[C::STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[C::STAGES];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    __shared__ int s_flag_ok;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sW = smem_base;
+    const uint32_t sX = sW + C::STAGES * C::W_BYTES;
+    const uint32_t sSW = (sX + C::STAGES * C::X_BYTES + 1023u) & ~1023u;
+    const uint32_t sSX = sSW + C::STAGES * C::SF_BYTES;
+
+    const int slabs = (p.N + 127) / 128;
+    const int kblk = (p.K + 255) / 256;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), 4); }
+        fence_mbar_init();
+        prefetch_tensormap(&tmW); prefetch_tensormap(&tmX); prefetch_tensormap(&tmSW); prefetch_tensormap(&tmSX);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(&s_tmem_base), C::TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    WaitCtx wc{&s_abort, p.status};
+
+    if (warp == 0) {
+        // ----------------------------------------------------------------- TMA producer -----
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+            Segment sg;
+            while (ok && wr.next(sg)) {
+                for (int kb = sg.kb0; kb < sg.kb1; kb++) {
+                    if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&bar_full[stage]);
+                    mbar_arrive_expect_tx(full, C::TX_BYTES);
+                    tma_load_2d(sW + stage * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
+                    tma_load_3d_d(sSW + stage * C::SF_BYTES, &tmSW, full, 0, kb * 4, sg.slab);
+                    tma_load_2d(sX + stage * C::X_BYTES, &tmX, full, kb * 128, 0);
+                    tma_load_3d_d(sSX + stage * C::SF_BYTES, &tmSX, full, 0, kb * 4, 0);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            for (int s = 0; s < C::STAGES && ok; s++) {
+                ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ----------------------------------------------------------------- MMA issuer -------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, slot = 0;
+            int seg_idx = 0;
+            bool ok = true;
+            WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+            Segment sg;
+            while (ok && wr.next(sg)) {
+                const int buf = seg_idx & 1;
+                if (!mbar_wait(wc, smem_u32(&bar_acc_empty[buf]), ((seg_idx >> 1) & 1) ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc_t = tmem_base + buf * C::ACC_STRIDE;
+                for (int kb = sg.kb0; kb < sg.kb1; kb++) {
+                    if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sfa_t = tmem_base + C::SF_BASE + slot * 32;
+                    const uint32_t sfb_t = sfa_t + 16;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        tc_cp_scale<1>(sfa_t + 4 * c, smem_desc_scale(sSW + stage * C::SF_BYTES + c * 512));
+                        tc_cp_scale<1>(sfb_t + 4 * c, smem_desc_scale(sSX + stage * C::SF_BYTES + c * 512));
+                    }
+                    const uint64_t a_desc = smem_desc_sw128(sW + stage * C::W_BYTES);
+                    const uint64_t b_desc = smem_desc_sw128(sX + stage * C::X_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        mma_nvfp4<1>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(128, NB), (kb > sg.kb0 || j > 0) ? 1u : 0u,
+                                     sfa_t + 4 * j, sfb_t + 4 * j);
+                    tc_commit<1>(smem_u32(&bar_empty[stage]));
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    slot = (slot + 1) % C::SF_SLOTS;
+                }
+                tc_commit<1>(smem_u32(&bar_acc_full[buf]));
+                seg_idx++;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ----------------------------------------------------------------- epilogue ----------
+        const int quarter = warp & 3;
+        const int n_local = quarter * 32 + lane;           // weight row inside the slab
+        const float alpha = __fmul_rn(*p.sgX, *p.sgW);
+        int seg_idx = 0;
+        bool ok = true;
+        WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+        Segment sg;
+        while (ok && wr.next(sg)) {
+            const int buf = seg_idx & 1;
+            if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const bool head = sg.kb0 == 0;
+            const bool complete = head && sg.kb1 == kblk;
+            const int n = sg.slab * 128 + n_local;
+            // Which CTAs hold the rest of this slab (only meaningful for an incomplete head)?
+            int contrib_lo = 0, contrib_hi = 0;
+            if (head && !complete) {
+                const long long items = (long long)slabs * kblk;
+                const long long slab_end = (long long)(sg.slab + 1) * kblk;
+                contrib_lo = int(blockIdx.x) + 1;
+                contrib_hi = contrib_lo;
+                while (contrib_hi < int(gridDim.x) && items * contrib_hi / gridDim.x < slab_end) contrib_hi++;
+                // wait for their partial tiles
+                if (threadIdx.x == 64) {
+                    int good = 1;
+                    for (int h = contrib_lo; h < contrib_hi && good; h++) {
+                        const long long t0 = clock64();
+                        while (ld_acquire_gpu(p.flags + h) != p.epoch) {
+                            if (s_abort || clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+                                good = 0; s_abort = 1;
+                                if (p.status) atomicExch(p.status, (int)TKB_DEV_TIMEOUT);
+                                break;
+                            }
+                            __nanosleep(32);
+                        }
+                    }
+                    s_flag_ok = good;
+                }
+                epi_barrier();
+                if (!s_flag_ok) ok = false;
+            }
+#pragma unroll
+            for (int c0 = 0; c0 < NB; c0 += C::CHUNK) {
+                float v[C::CHUNK];
+                if constexpr (C::CHUNK == 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * C::ACC_STRIDE + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+                } else {
+                    uint32_t r[16];
+                    tmem_ld_32x16(tmem_base + (uint32_t(quarter * 32) << 16) + buf * C::ACC_STRIDE + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+                }
+                if (c0 + C::CHUNK >= NB) {
+                    // last chunk read: the accumulator buffer can be reused
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                }
+                if (!head) {
+                    float* dst = p.partials + (size_t(blockIdx.x) * NB + c0) * 128 + n_local;
+#pragma unroll
+                    for (int i = 0; i < C::CHUNK; i++) __stcg(dst + i * 128, v[i]);
+                } else {
+                    if (!complete && ok) {
+                        for (int h = contrib_lo; h < contrib_hi; h++) {
+                            const float* src = p.partials + (size_t(h) * NB + c0) * 128 + n_local;
+#pragma unroll
+                            for (int i = 0; i < C::CHUNK; i++) v[i] += __ldcg(src + i * 128);
+                        }
+                    }
+                    if (n < p.N) {
+#pragma unroll
+                        for (int i = 0; i < C::CHUNK; i++)
+                            if (c0 + i < p.M) p.D[int64_t(c0 + i) * p.ldd + n] = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
+                    }
+                }
+            }
+            if (!head) {
+                // publish the partial tile: all four epilogue warps have stored, then one release
+                epi_barrier();
+                if (threadIdx.x == 64) {
+                    __threadfence();
+                    st_release_gpu(p.flags + blockIdx.x, p.epoch);
+                }
+            }
+            seg_idx++;
+        }
+        __syncwarp();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, C::TMEM_COLS);
+    }
+}
+
+template <int NB>
+static cudaError_t launch_decode_t(const DecodeArgs& a) {
+    using C = DecodeCfg<NB>;
+    auto kern = decode_kernel<NB>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const long long items = (long long)((a.N + 127) / 128) * ((a.K + 255) / 256);
+    int grid = a.sm_count;
+    if (grid > a.max_grid) grid = a.max_grid;
+    if (grid > items) grid = int(items);
+    if (grid < 1) grid = 1;
+    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status};
+    CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
+    void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
+    static const bool coop = getenv("TKB_COOP") && atoi(getenv("TKB_COOP")) != 0;
+    if (coop) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(C::THREADS), params, C::SMEM_BYTES, a.stream);
+    return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(C::THREADS), params, C::SMEM_BYTES, a.stream);
+}
+
+int decode_padded_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+cudaError_t launch_decode(const DecodeArgs& a) {
+    switch (decode_padded_rows(a.M)) {
+        case 16: return launch_decode_t<16>(a);
+        case 32: return launch_decode_t<32>(a);
+        case 64: return launch_decode_t<64>(a);
+        default: return launch_decode_t<128>(a);
+    }
+}
+
+} // namespace tkb

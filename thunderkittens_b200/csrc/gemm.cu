@@ -69,14 +69,100 @@ struct GemmParams {
     unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
 };
 
-__device__ __forceinline__ void tile_to_block(int tile, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
-    constexpr int GROUP = 8;                       // row-blocks that share a sweep over the columns (L2 reuse)
-    const int per_group = GROUP * tiles_n;
+// All-gather mode (tensor-parallel GEMM): the A operand is row-sharded over `world` GPUs.  Every rank
+// keeps a full-size buffer for the gathered codes and scales and quantizes its own shard into its own
+// slice; `comm_ctas` CTAs of this kernel pull the other slices from the owners' buffers over NVLink
+// (plain bulk copies through shared memory, no multicast) while the remaining CTAs multiply, own rows
+// first, then the other shards in the order they are pulled.
+// tile index -> (row block, column block).  `group` row-blocks share a sweep over the columns (L2
+// reuse); `rot` rotates the row-block order (all-gather mode starts with the rank's own rows).
+__device__ __forceinline__ void tile_to_block(int tile, int tiles_m, int tiles_n, int group, int rot, int& m_blk, int& n_blk) {
+    const int per_group = group * tiles_n;
     const int g = tile / per_group, in_g = tile % per_group;
-    const int first_m = g * GROUP;
-    const int gsz = min(GROUP, tiles_m - first_m);
-    m_blk = first_m + in_g % gsz;
+    const int first_m = g * group;
+    const int gsz = min(group, tiles_m - first_m);
+    m_blk = first_m + in_g % gsz + rot;
+    if (m_blk >= tiles_m) m_blk -= tiles_m;
     n_blk = in_g / gsz;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded spin until a global epoch flag has reached `value` (epochs only grow).  False on timeout / abort.
+__device__ __forceinline__ bool flag_wait(const WaitCtx& w, const unsigned int* flag, unsigned int value) {
+    if (int(ld_acquire_sys(flag) - value) >= 0) return true;
+    const long long t0 = clock64();
+    while (int(ld_acquire_sys(flag) - value) < 0) {
+        if (*w.abort_flag) return false;
+        if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+            *w.abort_flag = 1;
+            if (w.status) atomicExch(w.status, (int)TKB_DEV_TIMEOUT);
+            return false;
+        }
+        __nanosleep(64);
+    }
+    return true;
+}
+// 1-D bulk copies (16-byte aligned, size a multiple of 16): global (possibly a peer GPU) -> shared, shared -> global
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
+}
+
+// One comm CTA: pulls its share of the (source rank, 256-row block) units into the local buffers.
+template <int RING, int PIECE>
+__device__ void ag_pull(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
+                        const WaitCtx& wc) {
+    // single thread; bars[0..RING) are "piece landed" barriers
+    const int units = (ag.world - 1) * ag.blocks_per_rank;
+    uint32_t issued = 0, stored = 0;         // piece counters over the whole kernel (ring position / phase)
+    for (int u = comm_idx; u < units; u += ag.comm_ctas) {
+        const int src = (ag.rank + 1 + u / ag.blocks_per_rank) % ag.world;
+        const int b = u % ag.blocks_per_rank;
+        if (!flag_wait(wc, ag.ready + src, ag.epoch)) return;
+        const size_t row0 = (size_t(src) * ag.blocks_per_rank + b) * 256;
+        // two contiguous spans: codes of 256 rows, scales of two 128-row blocks
+        const size_t off[2] = {row0 * k_bytes, (row0 / 128) * sc_bytes_per_mblock};
+        const size_t len[2] = {size_t(256) * k_bytes, size_t(2) * sc_bytes_per_mblock};
+        const uint8_t* sbase[2] = {ag.peer_codes[src], ag.peer_scales[src]};
+        uint8_t* dbase[2] = {ag.codes, ag.scales};
+        for (int span = 0; span < 2; span++) {
+            const size_t n_pieces = (len[span] + PIECE - 1) / PIECE;
+            size_t next_load = 0;
+            for (size_t i = 0; i < n_pieces; i++) {
+                // keep up to RING loads in flight
+                while (next_load < n_pieces && issued - stored < RING) {
+                    const uint32_t slot = issued % RING;
+                    const size_t o = next_load * PIECE;
+                    const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
+                    mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
+                    bulk_load(smem + slot * PIECE, sbase[span] + off[span] + o, bytes, smem_u32(&bars[slot]));
+                    issued++; next_load++;
+                }
+                const uint32_t slot = stored % RING;
+                if (!mbar_wait(wc, smem_u32(&bars[slot]), (stored / RING) & 1)) return;
+                const size_t o = i * PIECE;
+                const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
+                bulk_store(dbase[span] + off[span] + o, smem + slot * PIECE, bytes);
+                tma_store_commit();
+                tma_store_wait_read<0>();    // the slot may be refilled once the store has read it
+                stored++;
+            }
+        }
+        tma_store_wait<0>();                 // all bytes of this unit are in local memory
+        __threadfence();
+        st_release_gpu_u32(ag.arrived + src * ag.blocks_per_rank + b, ag.epoch);
+    }
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int x, int y, int z) {
@@ -90,13 +176,14 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, 
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
-template <int KIND, int CTAS, int BN>
+template <int KIND, int CTAS, int BN, bool AG>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
-            const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmD, const GemmParams p, const AgParams ag) {
     using C = GemmCfg<KIND, CTAS, BN>;
     constexpr bool SCALED = KIND != KIND_BF16;
+    static_assert(!AG || (KIND == KIND_NVFP4 && CTAS == 2 && BN == 256), "all-gather mode: NVFP4, CTA pairs, N tile 256");
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[C::STAGES];
@@ -121,8 +208,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + C::KB - 1) / C::KB;
-    const int first_tile = CTAS == 2 ? cluster_id_x() : blockIdx.x;
-    const int tile_stride = CTAS == 2 ? num_clusters_x() : gridDim.x;
+    // all-gather mode: the first comm_ctas CTAs (whole clusters) only move data
+    const int comm_units = AG ? ag.comm_ctas / CTAS : 0;
+    const bool is_comm = AG && int(blockIdx.x) < ag.comm_ctas;
+    const int first_tile = (CTAS == 2 ? int(cluster_id_x()) : int(blockIdx.x)) - comm_units;
+    const int tile_stride = (CTAS == 2 ? int(num_clusters_x()) : int(gridDim.x)) - comm_units;
+    const int tile_group = AG ? ag.blocks_per_rank : 8;
+    const int tile_rot = AG ? ag.rank * ag.blocks_per_rank : 0;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -133,7 +225,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD);
         if (SCALED) { prefetch_tensormap(&tmSA); prefetch_tensormap(&tmSB); }
     }
-    if (warp == 1) {
+    if (warp == 1 && !is_comm) {
         tmem_alloc<CTAS>(smem_u32(&s_tmem_base), C::TMEM_COLS);
         tmem_relinquish<CTAS>();
     }
@@ -142,6 +234,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     WaitCtx wc{&s_abort, p.status};
+
+    if constexpr (AG) {
+        if (is_comm) {
+            if (threadIdx.x == 0) {
+                // reuse the (idle) "full" barriers of this CTA as piece barriers and the operand ring as staging
+                constexpr int PIECE = 32768;
+                constexpr int RING = (C::STAGES * C::STAGE_BYTES) / PIECE < C::STAGES ? (C::STAGES * C::STAGE_BYTES) / PIECE : C::STAGES;
+                ag_pull<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_full, wc);
+            }
+            __syncthreads();
+            cluster_sync();      // matches the teardown barrier of the compute clusters' code path below
+            return;
+        }
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer ----------
@@ -152,9 +258,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
-                tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
+                tile_to_block(tile, tiles_m, tiles_n, tile_group, tile_rot, m_blk, n_blk);
                 const int a_row = m_blk * C::BM + int(cta_rank) * 128;
                 const int b_row = n_blk * BN + int(cta_rank) * C::BN_CTA;
+                if constexpr (AG) {
+                    const int src = m_blk / ag.blocks_per_rank;
+                    if (src != ag.rank) {
+                        if (!flag_wait(wc, ag.arrived + m_blk, ag.epoch)) { ok = false; break; }
+                        fence_proxy_async_all();
+                    }
+                }
                 for (int kb = 0; kb < num_kb; kb++) {
                     { const long long t0 = clock64();
                       if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
@@ -263,7 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         long long wait_tf = 0, drain = 0;
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
             int m_blk, n_blk;
-            tile_to_block(tile, tiles_m, tiles_n, m_blk, n_blk);
+            tile_to_block(tile, tiles_m, tiles_n, tile_group, tile_rot, m_blk, n_blk);
             const long long t0 = clock64();
             if (!mbar_wait(wc, smem_u32(&bar_tmem_full), tile_phase)) { ok = false; break; }
             const long long t1 = clock64();
@@ -321,10 +434,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ------------------------------------------------------------------------------ host -------
-template <int KIND, int CTAS, int BN>
+template <int KIND, int CTAS, int BN, bool AG = false>
 static cudaError_t launch_t(const GemmArgs& a) {
     using C = GemmCfg<KIND, CTAS, BN>;
-    auto kern = gemm_kernel<KIND, CTAS, BN>;
+    auto kern = gemm_kernel<KIND, CTAS, BN, AG>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -332,9 +445,11 @@ static cudaError_t launch_t(const GemmArgs& a) {
         attr_set = true;
     }
     const int tiles = ((a.M + C::BM - 1) / C::BM) * ((a.N + BN - 1) / BN);
-    int units = a.sm_count / CTAS;
+    const int comm_units = AG ? a.ag.comm_ctas / CTAS : 0;
+    int units = a.sm_count / CTAS - comm_units;
     if (units > tiles) units = tiles;
     if (units < 1) units = 1;
+    units += comm_units;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units * CTAS, 1, 1);
     cfg.blockDim = dim3(C::THREADS, 1, 1);
@@ -345,7 +460,7 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, a.status, a.prof};
-    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p);
+    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.ag);
 }
 
 template <int KIND>
@@ -362,6 +477,7 @@ int gemm_tile_n(int config) { return (config & 2) ? 128 : 256; }
 int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
 
 cudaError_t launch_gemm(const GemmArgs& a) {
+    if (a.use_ag) return launch_t<KIND_NVFP4, 2, 256, true>(a);
     switch (a.kind) {
         case KIND_BF16: return launch_k<KIND_BF16>(a);
         case KIND_MXFP8: return launch_k<KIND_MXFP8>(a);

@@ -20,6 +20,17 @@ cudaError_t launch_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, cud
 cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cudaStream_t s);
 
 // gemm.cu
+constexpr int kMaxWorld = 8;
+struct AgParams {
+    const uint8_t* peer_codes[kMaxWorld];    // base of every rank's gathered-codes buffer [M, K/2] (own entry = local)
+    const uint8_t* peer_scales[kMaxWorld];   // base of every rank's gathered-scales buffer [M/128, K/64, 512]
+    uint8_t* codes; uint8_t* scales;         // this rank's buffers (same as peer_*[rank], writable)
+    const unsigned int* ready;               // [world] written by peers: "my slice holds epoch e"
+    unsigned int* arrived;                   // [world * blocks_per_rank] written by the comm CTAs of this kernel
+    unsigned int epoch;
+    int rank, world, blocks_per_rank, comm_ctas;
+};
+
 struct GemmArgs {
     int kind;                 // 0 bf16, 1 mxfp8, 2 nvfp4
     int config;               // bit 0: 0 = CTA pair (cta_group::2), 1 = single CTA; bit 1: 0 = N tile 256, 1 = N tile 128
@@ -30,9 +41,23 @@ struct GemmArgs {
     unsigned long long* prof;   // optional per-CTA wait counters, 8 x uint64 per CTA
     int sm_count;
     cudaStream_t stream;
+    bool use_ag;              // all-gather mode (NVFP4, CTA pairs, N tile 256)
+    AgParams ag;
 };
 cudaError_t launch_gemm(const GemmArgs& a);
 int gemm_tile_n(int config);
 int gemm_tile_m(int config);
+
+// decode.cu
+struct DecodeArgs {
+    CUtensorMap tmW, tmX, tmSW, tmSX;
+    const float* sgX; const float* sgW;
+    void* D; int64_t ldd;
+    int M, N, K;
+    float* partials; unsigned int* flags; unsigned int epoch; int max_grid;
+    int* status; int sm_count; cudaStream_t stream;
+};
+cudaError_t launch_decode(const DecodeArgs& a);
+int decode_padded_rows(int M);
 
 } // namespace tkb

@@ -17,6 +17,7 @@
 // quantize.cu / quantize_fast.cu).
 #pragma once
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
@@ -222,7 +223,8 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     int64_t lda = a.lda, ldc = a.ldc;
     float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
     void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status};
-    if (FUSED) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
+    static const bool coop = getenv("TKB_COOP") && atoi(getenv("TKB_COOP")) != 0;
+    if (FUSED && coop) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
     return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
 }
 

@@ -16,7 +16,7 @@ from . import _lib as L
 
 _ARITH = {"spec": L.NVFP4_SPEC, "kernel_ieee": L.NVFP4_KERNEL_IEEE, "kernel_fast": L.NVFP4_KERNEL_FAST}
 _CONFIG = {None: L.GEMM_DEFAULT, "default": L.GEMM_DEFAULT, "pair_n256": L.GEMM_PAIR_N256, "single_n256": L.GEMM_SINGLE_N256,
-           "pair_n128": L.GEMM_PAIR_N128, "single_n128": L.GEMM_SINGLE_N128}
+           "pair_n128": L.GEMM_PAIR_N128, "single_n128": L.GEMM_SINGLE_N128, "skinny": L.GEMM_SKINNY}
 
 #: default NVFP4 arithmetic (see include/tkb200.h)
 default_nvfp4_arithmetic = "spec"

@@ -1,0 +1,171 @@
+"""Single-node multi-GPU host layer: symmetric buffers and the collective-fused operators.
+
+Mirrors the reference's Python-visible parallel API for this path:
+  TKParallelTensor(shape, dtype, local_rank, local_world_size, multicast)   include/pyutils/parallel_tensor.cuh:320-336
+  all_gather_matmul(A, B, C, barrier, num_comm_sms)                          kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305
+One process per GPU (torchrun); `torch.distributed` must be initialised — it carries the 64-byte CUDA IPC
+handles (the reference ships its own unix-socket broker for that) and the 4-byte amax all-reduce.  All data
+moves through kernels of libtkb200 over NVLink peer mappings; NCCL is never on the data path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import ops
+
+_DT_SIZE = {torch.uint8: 1, torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.int32: 4, torch.int: 4}
+
+
+class _RawCuda:
+    """Minimal __cuda_array_interface__ carrier so torch can view memory owned by libtkb200."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class TKParallelTensor:
+    """A tensor of the same shape on every rank of the node whose storage is mapped into every other rank.
+
+    data_               torch view of the local storage
+    local_rank_, local_world_size_
+    peer_ptr(i)         device pointer of rank i's storage as seen from this rank
+    The `multicast` argument is accepted for signature compatibility and ignored: nothing on this path uses
+    an NVSwitch multicast object.
+    """
+
+    def __init__(self, shape, dtype, local_rank: int, local_world_size: int, multicast: bool = False, group=None):
+        self.shape_ = tuple(int(s) for s in shape)
+        self.dtype_ = dtype
+        self.local_rank_ = int(local_rank)
+        self.local_world_size_ = int(local_world_size)
+        self.multicast_ = False
+        self._group = group
+        self.nbytes = int(math.prod(self.shape_)) * _DT_SIZE[dtype]
+        ptr = C.c_void_p()
+        L.check(L.lib().tkb_dev_alloc(max(self.nbytes, 16), C.byref(ptr)))
+        self._ptr = ptr.value
+        self.data_ = torch.as_tensor(_RawCuda(self._ptr, self.nbytes), device=torch.device("cuda", torch.cuda.current_device())) \
+            .view(dtype).view(self.shape_)
+        self._peer = [None] * self.local_world_size_
+        self._peer[self.local_rank_] = self._ptr
+        self._opened = []
+        if self.local_world_size_ > 1:
+            self._exchange()
+
+    def _exchange(self) -> None:
+        handle = (C.c_ubyte * 64)()
+        L.check(L.lib().tkb_ipc_export(self._ptr, handle))
+        handles = [None] * self.local_world_size_
+        dist.all_gather_object(handles, bytes(handle), group=self._group)
+        for r, h in enumerate(handles):
+            if r == self.local_rank_:
+                continue
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            p = C.c_void_p()
+            L.check(L.lib().tkb_ipc_open(buf, C.byref(p)))
+            self._peer[r] = p.value
+            self._opened.append(p.value)
+
+    def peer_ptr(self, rank: int) -> int:
+        return self._peer[rank]
+
+    def peer_ptr_array(self):
+        arr = (C.c_void_p * self.local_world_size_)(*self._peer)
+        return arr
+
+    def close(self) -> None:
+        if self._ptr is None:
+            return
+        torch.cuda.synchronize()
+        for p in self._opened:
+            L.lib().tkb_ipc_close(p)
+        self._opened = []
+        if self.local_world_size_ > 1:
+            dist.barrier(group=self._group)     # nobody frees while a peer still has the mapping open
+        self.data_ = None
+        L.lib().tkb_dev_free(self._ptr)
+        self._ptr = None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class AllGatherMatmulNVFP4:
+    """Column-parallel linear layer with NVFP4 operands: every rank owns M/world activation rows (bf16) and
+    N_local = N/world weight rows (already NVFP4).  One call =
+        amax(X_local) -> all-reduce(max) -> quantize into this rank's slice of the gathered buffers ->
+        signal peers -> fused kernel (a few CTAs pull the other slices over NVLink, the rest multiply).
+    Two buffer sets alternate between calls; a slice is overwritten only after every peer has acknowledged
+    that it finished reading the previous contents.
+    """
+
+    def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None):
+        if M % (256 * local_world_size):
+            raise RuntimeError("M must be a multiple of 256 * world size")
+        if K % 64:
+            raise RuntimeError("K must be a multiple of 64")
+        self.M, self.K = M, K
+        self.rank, self.world = local_rank, local_world_size
+        self.group = group
+        self.num_comm_sms = 0 if local_world_size == 1 else max(2, num_comm_sms - num_comm_sms % 2)
+        mk = lambda shape, dt: TKParallelTensor(shape, dt, local_rank, local_world_size, False, group)
+        self.codes = [mk((M, K // 2), torch.uint8) for _ in range(2)]
+        self.scales = [mk((M // 128, K // 64, 512), torch.uint8) for _ in range(2)]
+        # flags[0:world] = ready epochs, flags[world:2*world] = done (acknowledge) epochs
+        self.flags = mk((2 * local_world_size,), torch.int32)
+        dev = self.flags.data_.device
+        self.arrived = [torch.zeros(M // 256, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.epoch = 0
+        self.rows = M // local_world_size
+        if local_world_size > 1:
+            dist.barrier(group=group)
+
+    def __call__(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
+        lib = L.lib()
+        if tuple(X_local.shape) != (self.rows, self.K) or X_local.dtype != torch.bfloat16 or not X_local.is_contiguous():
+            raise RuntimeError("X_local must be a contiguous bf16 tensor of shape (M / world, K)")
+        n_local = W.shape[0]
+        if tuple(D.shape) != (self.M, n_local) or D.dtype != torch.bfloat16 or not D.is_contiguous():
+            raise RuntimeError("D must be a contiguous bf16 tensor of shape (M, N_local)")
+        self.epoch += 1
+        e, b, r, w, s = self.epoch, self.epoch % 2, self.rank, self.world, _stream()
+        codes, scales = self.codes[b], self.scales[b]
+        # my slice of set b was last filled at epoch e-2: wait until every peer acknowledged reading it
+        if w > 1 and e > 2:
+            L.check(lib.tkb_wait_flags(self.flags.data_.data_ptr() + 4 * w, w, r, e - 2, s))
+        ops.absmax_bf16(X_local, self.amax)
+        if w > 1:
+            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
+        my_codes = codes.data_[r * self.rows:(r + 1) * self.rows]
+        my_scales = scales.data_[r * self.rows // 128:(r + 1) * self.rows // 128]
+        ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, amax=self.amax)
+        if w > 1:
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))
+        L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), self.sg.data_ptr(), W.data_ptr(), W_sc.data_ptr(),
+                                      W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.flags.data_.data_ptr(),
+                                      self.arrived[b].data_ptr(), e, self.num_comm_sms, s))
+        if w > 1:
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, w + r, e, 0, s))
+
+    def close(self) -> None:
+        for t in self.codes + self.scales + [self.flags]:
+            t.close()
+
+
+def all_gather_matmul(A: TKParallelTensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, C_out: torch.Tensor,
+                      state: AllGatherMatmulNVFP4, num_comm_sms: int | None = None) -> None:
+    """Reference-shaped entry: A is a bf16 TKParallelTensor of the FULL shape (M, K) whose rows
+    [rank*M/world, (rank+1)*M/world) hold this rank's activations (ag_gemm/benchmark.py:55-63); the weight is
+    this rank's NVFP4 shard instead of a bf16 matrix and `state` replaces the reference's barrier tensor."""
+    r, rows = A.local_rank_, A.shape_[0] // A.local_world_size_
+    if num_comm_sms is not None and A.local_world_size_ > 1:
+        state.num_comm_sms = max(2, num_comm_sms - num_comm_sms % 2)
+    state(A.data_[r * rows:(r + 1) * rows], W, W_sc, W_sg, C_out)
