@@ -179,7 +179,106 @@ def event_time(torch, fn, steps, cooldown=0.5):
     return s.elapsed_time(e) * 1e-3 / steps
 
 
+def run_tp(args) -> None:
+    """N > 1: tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192, weights column(N)-sharded, bf16 activation rows sharded
+    and all-gathered (as NVFP4 codes + scales) over NVLink inside the GEMM kernel.  Strong scaling."""
+    import torch
+    import torch.distributed as dist
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib, parallel
+
+    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    Mt, Nt, Kt = 8192, 28672, 8192
+    n_local, rows = Nt // world, Mt // world
+    u8 = torch.uint8
+    GROUPS = 3
+    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=args.comm_sms)
+    sets = []
+    amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
+    for gi in range(GROUPS):
+        # weight shard: rows [rank*n_local, ...) of a seeded N(0, 0.02) matrix, quantized with the all-reduced amax
+        W = synth(torch, dev, n_local, Kt, 800 + 10 * gi + rank, std=0.02)
+        ops.absmax_bf16(W, amax_w)
+        dist.all_reduce(amax_w, op=dist.ReduceOp.MAX)
+        wc = torch.empty(n_local, Kt // 2, dtype=u8, device=dev); ws = torch.empty((n_local + 127) // 128, Kt // 64, 512, dtype=u8, device=dev)
+        wg = torch.empty(1, dtype=torch.float32, device=dev)
+        ops.nvfp4_quantize(W, wc, ws, wg, False, amax=amax_w)
+        X = synth(torch, dev, rows, Kt, 700 + 10 * gi + rank)
+        sets.append((X, wc, ws, wg, torch.empty(Mt, n_local, dtype=torch.bfloat16, device=dev)))
+        del W
+    hostX = sets[0][0].cpu().pin_memory()
+    hostD = torch.empty(Mt, n_local, dtype=torch.bfloat16).pin_memory()
+    torch.cuda.synchronize()
+
+    def step(i):
+        X, wc, ws, wg, D = sets[i % GROUPS]
+        op(X, wc, ws, wg, D)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    with ClockSampler(local_rank) as cs:
+        dt = event_time(torch, step, args.steps)
+    clocks = cs.summary()
+    assert _lib.device_status() == 0, "a device-side wait timed out"
+    t = torch.tensor([dt], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item())
+    barrier()
+
+    dX = torch.empty(rows, Kt, dtype=torch.bfloat16, device=dev)
+    _, wc, ws, wg, D = sets[0]
+
+    def e2e_step(i):
+        dX.copy_(hostX, non_blocking=True)
+        op(dX, wc, ws, wg, D)
+        hostD.copy_(D, non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i)
+    barrier()
+    dt_e2e = event_time(torch, e2e_step, max(3, min(args.steps, 10)))
+    t = torch.tensor([dt_e2e], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt_e2e = float(t.item())
+    barrier()
+    if rank == 0:
+        pk = measured_peaks()
+        flops = 2.0 * Mt * Nt * Kt
+        tf = flops / dt * 1e-12
+        peak = 4.0 * pk["bf16_tflops"] * world
+        nvl_bytes = (world - 1) / world * Mt * (Kt // 2 + Kt // 16)
+        line = {
+            "metric": "tensor-parallel NVFP4 GEMM throughput (M=8192 N=28672 K=8192)", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 x fp32, fp32 acc)", "data": "synthetic",
+            "config": {"workload": "TP NVFP4 GEMM M=8192 N=28672 K=8192: weights N-sharded, bf16 activation rows sharded, per step: amax all-reduce, "
+                                   "quantize, NVFP4 all-gather over NVLink fused with the tcgen05 GEMM", "parallelism": f"tp{world}",
+                       "l2": f"{GROUPS} rotating weight/activation/output sets", "comm_ctas": op.num_comm_sms},
+            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": 4.0 * pk["bf16_tflops"], "unit": "TFLOP/s per GPU",
+                         "frac": tf / peak, "traffic": None, "kernel": "tkb::gemm_kernel<NVFP4, cta pair, N256, all-gather>",
+                         "peak_source": f"4 x {pk['source']} cuBLAS bf16 burst (derived dense FP4 ceiling)",
+                         "nvlink_bytes_in_per_gpu": nvl_bytes, "nvlink_time_at_770GBs_ms": nvl_bytes / 770e9 * 1e3},
+            "e2e": {"value": flops / dt_e2e * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": rows * Kt * 2 * world,
+                    "d2h_bytes_per_step": Mt * n_local * 2 * world, "ms_per_step": dt_e2e * 1e3,
+                    "path": "pinned host bf16 shard -> H2D -> AllGatherMatmulNVFP4 -> D2H of the rank's output columns"},
+            "gpu_launches": args.steps * 5 * world, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    op.close()
+    dist.destroy_process_group()
+
+
 def run_ours(args) -> None:
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_tp(args)
     import torch
     import torch.distributed as dist
     import thunderkittens_b200.ops as ops
@@ -410,6 +509,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--k", type=int, default=None)
     ap.add_argument("--config", default=None)
+    ap.add_argument("--comm-sms", type=int, default=8, help="CTAs of the tensor-parallel kernel that pull peer shards")
     args = ap.parse_args()
     if args.case:
         run_case(args)

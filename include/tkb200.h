@@ -33,7 +33,8 @@ enum {
     TKB_ERR_BAD_ALIGNMENT = 2, /* base pointers / leading dimensions must be 16-byte aligned */
     TKB_ERR_CUDA = 3,          /* a CUDA runtime or driver call failed */
     TKB_ERR_TIMEOUT = 4,       /* a bounded device-side wait ran out */
-    TKB_ERR_UNSUPPORTED = 5    /* not an sm_100 device / driver without tensor-map support */
+    TKB_ERR_UNSUPPORTED = 5,   /* not an sm_100 device / driver without tensor-map support */
+    TKB_ERR_CAPACITY = 6       /* device status only: a caller-sized buffer was too small (MoE row capacity) */
 };
 
 /* NVFP4 quantizer arithmetic (see tkb_nvfp4_quantize) */
@@ -81,6 +82,12 @@ int tkb_nvfp4_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, f
  * reduce tkb_absmax_bf16 over the shards first so every shard quantizes like the full tensor). */
 int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M,
                                  int K, int scale_2d, int arithmetic, void* stream);
+
+/* Same arithmetic, but the block scales are written as plain rows sc_rows[M, K/16] instead of 512-byte chunks:
+ * the form in which quantized rows travel between GPUs (MoE dispatch re-tiles them at the destination).
+ * No counterpart in the reference, whose dispatch moves bf16 rows. */
+int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* codes, void* sc_rows, float* sg, const float* amax, int M, int K,
+                            int arithmetic, void* stream);
 
 /* max |x| of a bf16 matrix into *amax (device float; overwritten).  Part of
  * nvfp4_quantize::absmax_kernel (nvfp4_b200_gemm.cu:360-418) exposed for sharded tensors. */
@@ -150,6 +157,44 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, const void* ready,
                       void* arrived, unsigned int epoch, int comm_ctas, void* stream);
+
+/* ---- MoE layer -----------------------------------------------------------------------------------
+ * Replaces moe_dispatch_gemm(pre_tokens, post_tokens, weights, outputs, padded_tokens_per_expert,
+ * pull_dispatch_indices, barrier, num_comm_sms, num_padded_local_tokens)
+ * (kernels/parallel/moe_dispatch_gemm/moe_dispatch_gemm_h100.cu:260-299; Hopper-only in the reference) and the
+ * schedule its benchmark builds on the CPU (moe_dispatch_gemm/benchmark.py:112-166).  Experts are sharded
+ * E/world per rank (expert e lives on rank e / (E/world)), tokens T/world per rank. */
+
+/* softmax over E logits per token, top_k experts by probability (ties -> lower id), weights renormalised over the
+ * chosen k.  logits [T, E] fp32 -> experts [T, top_k] int32, weights [T, top_k] fp32.  E % 32 == 0, E <= 256.
+ * (The reference benchmark draws experts with torch.multinomial and has no gate weights: benchmark.py:112-121.) */
+int tkb_moe_route(const float* logits, int T, int E, int top_k, int* experts, float* weights, void* stream);
+
+/* Dispatch schedule on the device from the chosen experts of ALL tokens (experts_all [T, top_k], identical on every
+ * rank).  Outputs: counts[E] (scratch), padded_per_expert[E] (counts rounded up to 128), and for this rank
+ * pull_idx[cap_rows][2] = (source rank, source row) per row of its expert segments (ascending global token order,
+ * (-1,-1) padding), block_expert[cap_rows/128] (local expert of each 128-row block), num_blocks[1], and
+ * comb_idx[(T/world)*top_k][2] = (expert rank, row there) for this rank's own tokens.  If the rank's segments do
+ * not fit in cap_rows the device status becomes TKB_ERR_CAPACITY and num_blocks is 0. */
+int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world, int rank, int* counts, int* padded_per_expert,
+                     int* pull_idx, int* block_expert, int* num_blocks, int* comb_idx, int cap_rows, void* stream);
+
+/* Dispatch fused with the grouped expert GEMM: Y[row, :] = Xq[src(row)] . W[expert(row)]^T for every row of this
+ * rank's expert segments.  peer_codes[i] [T/world, K/2] and peer_scale_rows[i] [T/world, K/16] are rank i's
+ * quantized tokens (tkb_nvfp4_quantize_rows with the all-reduced amax; X_sg is that common scale);
+ * codes [cap_rows, K/2] and scales [cap_rows/128, K/64, 512] are local operand buffers the kernel fills;
+ * W [experts_local * I, K/2], W_sc [experts_local * I / 128, K/64, 512], W_sg[1]: the rank's stacked expert weights;
+ * Y [cap_rows, I] bf16 (leading dimension ldy, 0 = I).  ready [world] / arrived [cap_rows/128]: epoch arrays.
+ * comm_ctas CTAs pull rows over NVLink while the others multiply.  K % 256 == 0, I % 128 == 0. */
+int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows, const float* X_sg, void* codes, void* scales,
+                          const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
+                          const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,
+                          int I, int experts_local, int cap_rows, int rank, int world, int comm_ctas, void* stream);
+
+/* Combine (no counterpart in the reference): out[t, :] = bf16(sum_j weights[t,j] * Y_{rank(t,j)}[row(t,j), :]), fp32
+ * accumulation in ascending j.  peer_Y[i]: rank i's Y buffer as seen from this rank. */
+int tkb_moe_combine(void* const* peer_Y, int64_t ldy, const int* comb_idx, const float* weights, void* out, int T_local, int top_k, int I,
+                    int world, void* stream);
 
 #ifdef __cplusplus
 }

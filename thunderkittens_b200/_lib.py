@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtkb200.so")
 
-OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED = range(6)
+OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_CAPACITY = range(7)
 NVFP4_SPEC, NVFP4_KERNEL_IEEE, NVFP4_KERNEL_FAST = 0, 1, 2
 GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY = range(6)
 
@@ -47,6 +47,12 @@ _SIGNATURES = {
     "tkb_signal_peers": ([C.POINTER(_vp), _i, _i, _i, C.c_uint, _i, _vp], _i),
     "tkb_wait_flags": ([_vp, _i, _i, C.c_uint, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, C.c_uint, _i, _vp], _i),
+    "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),
+    "tkb_moe_schedule": ([_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
+    "tkb_moe_dispatch_gemm": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, C.c_uint,
+                               _i, _i, _i, _i, _i, _i, _i, _vp], _i),
+    "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
 

@@ -245,7 +245,7 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
 }
 
 static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
-                                 int scale_2d, int arithmetic, void* stream) {
+                                 int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0) {
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
     if (!A || !codes || !sc || !sg) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
@@ -258,7 +258,7 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     a.A = A; a.lda = lda; a.codes = codes; a.ldc = K / 2; a.sc = sc; a.sg = sg; a.amax_in = amax;
     a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
     a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
-    a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count;
+    a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count; a.sc_rowmajor = sc_rowmajor;
     TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
     return TKB_OK;
 }
@@ -297,6 +297,12 @@ int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, v
                                  int scale_2d, int arithmetic, void* stream) {
     if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_with_amax: null amax");
     return nvfp4_quantize_common(A_bf16, lda, codes, sc, sg, amax, M, K, scale_2d, arithmetic, stream);
+}
+
+int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* codes, void* sc_rows, float* sg, const float* amax, int M, int K,
+                            int arithmetic, void* stream) {
+    if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_rows: null amax");
+    return nvfp4_quantize_common(A_bf16, lda, codes, sc_rows, sg, amax, M, K, 0, arithmetic, stream, 1);
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {

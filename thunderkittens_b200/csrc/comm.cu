@@ -131,17 +131,17 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     if (int e = api_make_gemm_maps(&g, KIND_NVFP4, peer_codes[rank], K / 2, peer_scales[rank], W, K / 2, W_sc, D, ldd, M, N_local, K)) return e;
     g.sgA = X_sg; g.sgB = W_sg; g.M = M; g.N = N_local; g.K = K; g.status = status; g.sm_count = sm;
     g.stream = static_cast<cudaStream_t>(stream);
-    g.use_ag = true;
+    g.mode = MODE_AG;
     for (int i = 0; i < world; i++) {
-        g.ag.peer_codes[i] = static_cast<const uint8_t*>(peer_codes[i]);
-        g.ag.peer_scales[i] = static_cast<const uint8_t*>(peer_scales[i]);
+        g.comm.ag.peer_codes[i] = static_cast<const uint8_t*>(peer_codes[i]);
+        g.comm.ag.peer_scales[i] = static_cast<const uint8_t*>(peer_scales[i]);
     }
-    g.ag.codes = static_cast<uint8_t*>(peer_codes[rank]);
-    g.ag.scales = static_cast<uint8_t*>(peer_scales[rank]);
-    g.ag.ready = static_cast<const unsigned int*>(ready);
-    g.ag.arrived = static_cast<unsigned int*>(arrived);
-    g.ag.epoch = epoch; g.ag.rank = rank; g.ag.world = world; g.ag.blocks_per_rank = M / world / 256;
-    g.ag.comm_ctas = world > 1 ? comm_ctas : 0;
+    g.comm.ag.codes = static_cast<uint8_t*>(peer_codes[rank]);
+    g.comm.ag.scales = static_cast<uint8_t*>(peer_scales[rank]);
+    g.comm.ag.ready = static_cast<const unsigned int*>(ready);
+    g.comm.ag.arrived = static_cast<unsigned int*>(arrived);
+    g.comm.ag.epoch = epoch; g.comm.ag.rank = rank; g.comm.ag.world = world; g.comm.ag.blocks_per_rank = M / world / 256;
+    g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
     TKB_CUDA_C(launch_gemm(g));
     return TKB_OK;
 }

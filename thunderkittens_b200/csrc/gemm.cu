@@ -176,14 +176,105 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, 
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
-template <int KIND, int CTAS, int BN, bool AG>
+
+// One comm CTA of the MoE kernel (all 320 threads): fills its share of the 128-row blocks of the local
+// activation buffer.  Per block: the 128 (source rank, source row) pairs of the dispatch list are pulled
+// from the owners' quantized-token buffers — codes through a ring of row slots straight into the local
+// row, the 128 row-major scale rows into shared memory, where they are re-tiled into the 512-byte chunk
+// layout the tensor core wants and stored as one contiguous span.  Padding rows (-1) become zeros.
+__device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc_row_bytes, uint32_t smem, uint32_t smem_avail, uint64_t* bars,
+                         const WaitCtx& wc) {
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* sm = smem_raw_ + (smem - smem_u32(smem_raw_));
+    const int num_blocks = *moe.num_blocks;
+    const int sc_block_bytes = sc_row_bytes * 128;                // one block's scales, either layout
+    uint8_t* sc_rm = sm;                                          // [128][sc_row_bytes] row-major, as pulled
+    uint8_t* sc_sw = sm + sc_block_bytes;                         // [sc_row_bytes/4][512] chunk layout, as stored
+    uint8_t* zero_row = sc_sw + sc_block_bytes;                   // k_bytes of zeros
+    const uint32_t ring0 = smem + 2 * sc_block_bytes + ((k_bytes + 127) & ~127);
+    const int ring = min(24, int((smem_avail - (ring0 - smem)) / uint32_t(k_bytes)));
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    for (int i = tid; i < k_bytes / 4; i += nthr) reinterpret_cast<uint32_t*>(zero_row)[i] = 0;
+    fence_proxy_async();
+    __syncthreads();
+    if (tid == 0) {
+        for (int pr = 0; pr < moe.world; pr++)
+            if (pr != moe.rank && !flag_wait(wc, moe.ready + pr, moe.epoch)) break;
+    }
+    __syncthreads();
+    uint32_t issued = 0, stored = 0, sc_phase = 0;
+    const uint32_t sc_bar = smem_u32(&bars[0]);                   // bars[0]: scale rows landed; bars[1..]: ring slots
+    for (int blk = comm_idx; blk < num_blocks; blk += moe.comm_ctas) {
+        __syncthreads();
+        if (*wc.abort_flag) break;                                 // read by every thread right after the same barrier
+        const int* idx = moe.pull_idx + size_t(blk) * 128 * 2;
+        if (tid == 0) {
+            // scale rows: one barrier for the block
+            uint32_t expect = 0;
+            for (int r = 0; r < 128; r++) if (idx[2 * r] >= 0) expect += sc_row_bytes;
+            mbar_arrive_expect_tx(sc_bar, expect);
+            for (int r = 0; r < 128; r++) {
+                const int src = idx[2 * r], row = idx[2 * r + 1];
+                if (src >= 0) bulk_load(smem_u32(sc_rm + r * sc_row_bytes), moe.peer_scales[src] + size_t(row) * sc_row_bytes, sc_row_bytes, sc_bar);
+            }
+            // code rows through the ring
+            int next = 0;
+            for (int r = 0; r < 128; r++) {
+                while (next < 128 && int(issued - stored) < ring) {
+                    const int src = idx[2 * next], row = idx[2 * next + 1];
+                    const uint32_t slot = issued % ring;
+                    if (src >= 0) {
+                        mbar_arrive_expect_tx(smem_u32(&bars[1 + slot]), k_bytes);
+                        bulk_load(ring0 + slot * k_bytes, moe.peer_codes[src] + size_t(row) * k_bytes, k_bytes, smem_u32(&bars[1 + slot]));
+                    } else {
+                        mbar_arrive(smem_u32(&bars[1 + slot]));      // keeps the slot's phase in step
+                    }
+                    issued++; next++;
+                }
+                const uint32_t slot = stored % ring;
+                if (!mbar_wait(wc, smem_u32(&bars[1 + slot]), (stored / ring) & 1)) break;
+                uint8_t* dst = moe.codes + (size_t(blk) * 128 + r) * k_bytes;
+                bulk_store(dst, idx[2 * r] >= 0 ? ring0 + slot * k_bytes : smem_u32(zero_row), k_bytes);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                stored++;
+            }
+        }
+        // everybody: wait for the scale rows, re-tile them
+        mbar_wait(wc, sc_bar, sc_phase);
+        sc_phase ^= 1;
+        const int groups = sc_row_bytes / 4;                       // 4 scale bytes (64 K-elements) per row per chunk
+        for (int i = tid; i < 128 * groups; i += nthr) {
+            const int r = i / groups, kc = i % groups;
+            const uint32_t v = idx[2 * r] >= 0 ? *reinterpret_cast<const uint32_t*>(sc_rm + r * sc_row_bytes + kc * 4) : 0u;
+            *reinterpret_cast<uint32_t*>(sc_sw + kc * 512 + (r & 31) * 16 + (r >> 5) * 4) = v;
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            bulk_store(moe.scales + size_t(blk) * sc_block_bytes, smem_u32(sc_sw), sc_block_bytes);
+            tma_store_commit();
+            tma_store_wait<0>();                                   // codes and scales of this block are in local memory
+            __threadfence();
+            st_release_gpu_u32(moe.arrived + blk, moe.epoch);
+        }
+        __syncthreads();                                           // sc_rm / sc_sw are reused by the next block
+    }
+}
+
+template <int KIND, int CTAS, int BN, int MODE>
 __global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
-            const __grid_constant__ CUtensorMap tmD, const GemmParams p, const AgParams ag) {
+            const __grid_constant__ CUtensorMap tmD, const GemmParams p, const CommParams cp) {
     using C = GemmCfg<KIND, CTAS, BN>;
     constexpr bool SCALED = KIND != KIND_BF16;
+    constexpr bool AG = MODE == MODE_AG;
+    constexpr bool MOE = MODE == MODE_MOE;
     static_assert(!AG || (KIND == KIND_NVFP4 && CTAS == 2 && BN == 256), "all-gather mode: NVFP4, CTA pairs, N tile 256");
+    static_assert(!MOE || (KIND == KIND_NVFP4 && CTAS == 1 && BN == 256), "MoE mode: NVFP4, single CTA, 128 x 256 tiles");
+    const AgParams& ag = cp.ag;
+    const MoeParams& moe = cp.moe;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[C::STAGES];
@@ -192,6 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __shared__ __align__(8) uint64_t bar_tmem_empty;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : 1];   // comm CTAs of the MoE mode
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0;
@@ -204,16 +296,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t sSB = sSA + C::STAGES * C::SFA_BYTES;
     const uint32_t sEpi = (sSB + C::STAGES * C::SFB_BYTES + 1023u) & ~1023u;
 
-    const int tiles_m = (p.M + C::BM - 1) / C::BM;
+    // MoE mode: the number of 128-row blocks that hold routed tokens is only known on the device
+    const int tiles_m = MOE ? *moe.num_blocks : (p.M + C::BM - 1) / C::BM;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + C::KB - 1) / C::KB;
     // all-gather mode: the first comm_ctas CTAs (whole clusters) only move data
-    const int comm_units = AG ? ag.comm_ctas / CTAS : 0;
-    const bool is_comm = AG && int(blockIdx.x) < ag.comm_ctas;
+    const int comm_ctas = AG ? ag.comm_ctas : (MOE ? moe.comm_ctas : 0);
+    const int comm_units = comm_ctas / CTAS;
+    const bool is_comm = int(blockIdx.x) < comm_ctas;
     const int first_tile = (CTAS == 2 ? int(cluster_id_x()) : int(blockIdx.x)) - comm_units;
     const int tile_stride = (CTAS == 2 ? int(num_clusters_x()) : int(gridDim.x)) - comm_units;
-    const int tile_group = AG ? ag.blocks_per_rank : 8;
+    const int tile_group = AG ? ag.blocks_per_rank : (MOE ? 1 : 8);
     const int tile_rot = AG ? ag.rank * ag.blocks_per_rank : 0;
 
     if (threadIdx.x == 0) {
@@ -235,6 +329,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t tmem_base = s_tmem_base;
     WaitCtx wc{&s_abort, p.status};
 
+    if constexpr (MOE) {
+        if (is_comm) {
+            if (threadIdx.x == 0) {
+                for (int i = 0; i < 32; i++) mbar_init(smem_u32(&bar_comm[i]), 1);
+                fence_mbar_init();
+            }
+            __syncthreads();
+            moe_pull(moe, int(blockIdx.x), p.K / 2, p.K / 16, smem_base, C::STAGES * C::STAGE_BYTES + C::EPI_BYTES, bar_comm, wc);
+            __syncthreads();
+            return;
+        }
+    }
     if constexpr (AG) {
         if (is_comm) {
             if (threadIdx.x == 0) {
@@ -260,7 +366,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 int m_blk, n_blk;
                 tile_to_block(tile, tiles_m, tiles_n, tile_group, tile_rot, m_blk, n_blk);
                 const int a_row = m_blk * C::BM + int(cta_rank) * 128;
-                const int b_row = n_blk * BN + int(cta_rank) * C::BN_CTA;
+                // MoE mode: the B operand is the weight matrix of the expert that owns this row block
+                const int expert = MOE ? moe.block_expert[m_blk] : 0;
+                const int b_row = expert * (MOE ? moe.expert_rows : 0) + n_blk * BN + int(cta_rank) * C::BN_CTA;
+                const int b_sblk = expert * (MOE ? moe.expert_rows / 128 : 0) + n_blk * (BN / 128);
+                if constexpr (MOE) {
+                    if (!flag_wait(wc, moe.arrived + m_blk, moe.epoch)) { ok = false; break; }
+                    fence_proxy_async_all();
+                }
                 if constexpr (AG) {
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
@@ -284,7 +397,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                             for (int j = 0; j < BN / 128; j++)
                                 tma_load_3d_pair(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES, &tmSB, full, 0, kb * C::SF_CHUNKS,
-                                                 n_blk * (BN / 128) + j);
+                                                 b_sblk + j);
                         }
                     } else {
                         tma_load_2d(sA + stage * C::A_BYTES, &tmA, full_local, kx, a_row);
@@ -294,7 +407,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                             for (int j = 0; j < BN / 128; j++)
                                 tma_load_3d(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES, &tmSB, full_local, 0, kb * C::SF_CHUNKS,
-                                            n_blk * (BN / 128) + j);
+                                            b_sblk + j);
                         }
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -434,10 +547,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ------------------------------------------------------------------------------ host -------
-template <int KIND, int CTAS, int BN, bool AG = false>
+template <int KIND, int CTAS, int BN, int MODE = MODE_PLAIN>
 static cudaError_t launch_t(const GemmArgs& a) {
     using C = GemmCfg<KIND, CTAS, BN>;
-    auto kern = gemm_kernel<KIND, CTAS, BN, AG>;
+    auto kern = gemm_kernel<KIND, CTAS, BN, MODE>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -445,9 +558,9 @@ static cudaError_t launch_t(const GemmArgs& a) {
         attr_set = true;
     }
     const int tiles = ((a.M + C::BM - 1) / C::BM) * ((a.N + BN - 1) / BN);
-    const int comm_units = AG ? a.ag.comm_ctas / CTAS : 0;
+    const int comm_units = MODE == MODE_AG ? a.comm.ag.comm_ctas / CTAS : (MODE == MODE_MOE ? a.comm.moe.comm_ctas / CTAS : 0);
     int units = a.sm_count / CTAS - comm_units;
-    if (units > tiles) units = tiles;
+    if (units > tiles && MODE != MODE_MOE) units = tiles;
     if (units < 1) units = 1;
     units += comm_units;
     cudaLaunchConfig_t cfg = {};
@@ -460,7 +573,7 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, a.status, a.prof};
-    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.ag);
+    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
 
 template <int KIND>
@@ -477,7 +590,8 @@ int gemm_tile_n(int config) { return (config & 2) ? 128 : 256; }
 int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
 
 cudaError_t launch_gemm(const GemmArgs& a) {
-    if (a.use_ag) return launch_t<KIND_NVFP4, 2, 256, true>(a);
+    if (a.mode == MODE_AG) return launch_t<KIND_NVFP4, 2, 256, MODE_AG>(a);
+    if (a.mode == MODE_MOE) return launch_t<KIND_NVFP4, 1, 256, MODE_MOE>(a);
     switch (a.kind) {
         case KIND_BF16: return launch_k<KIND_BF16>(a);
         case KIND_MXFP8: return launch_k<KIND_MXFP8>(a);

@@ -31,6 +31,22 @@ struct AgParams {
     int rank, world, blocks_per_rank, comm_ctas;
 };
 
+// MoE mode: dispatch (pull of routed token rows from their home ranks) fused with the grouped expert GEMM.
+struct MoeParams {
+    const uint8_t* peer_codes[kMaxWorld];    // every rank's quantized tokens [tokens_per_rank, K/2]
+    const uint8_t* peer_scales[kMaxWorld];   // every rank's ROW-MAJOR token scales [tokens_per_rank, K/16]
+    uint8_t* codes; uint8_t* scales;         // local gathered activations [cap_rows, K/2], chunked scales [cap_rows/128, K/64, 512]
+    const int* pull_idx;                     // [cap_rows][2] (source rank, source row), -1 = padding
+    const int* block_expert;                 // [cap_rows/128] local expert of each 128-row block
+    const int* num_blocks;                   // device scalar: blocks in use
+    const unsigned int* ready;               // [world] epochs: peers' tokens are quantized
+    unsigned int* arrived;                   // [cap_rows/128] epochs: block is in local memory
+    unsigned int epoch;
+    int rank, world, comm_ctas, expert_rows; // expert_rows = rows of one expert's weight matrix (the GEMM's N)
+};
+enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2 };
+struct CommParams { AgParams ag; MoeParams moe; };
+
 struct GemmArgs {
     int kind;                 // 0 bf16, 1 mxfp8, 2 nvfp4
     int config;               // bit 0: 0 = CTA pair (cta_group::2), 1 = single CTA; bit 1: 0 = N tile 256, 1 = N tile 128
@@ -41,8 +57,8 @@ struct GemmArgs {
     unsigned long long* prof;   // optional per-CTA wait counters, 8 x uint64 per CTA
     int sm_count;
     cudaStream_t stream;
-    bool use_ag;              // all-gather mode (NVFP4, CTA pairs, N tile 256)
-    AgParams ag;
+    int mode;                 // GemmMode
+    CommParams comm;
 };
 cudaError_t launch_gemm(const GemmArgs& a);
 int gemm_tile_n(int config);

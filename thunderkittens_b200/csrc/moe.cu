@@ -1,0 +1,294 @@
+// MoE layer pieces around the grouped expert GEMM: routing, dispatch schedule, combine, and the entry point of
+// the fused dispatch + grouped NVFP4 GEMM (the kernel itself is the MoE mode of gemm.cu).
+//
+// Replaces the reference's moe_dispatch_gemm path (kernels/parallel/moe_dispatch_gemm/moe_dispatch_gemm_h100.cu:
+// 13-293, Hopper/wgmma only, bf16 rows and weights) and the schedule that its benchmark builds on the CPU in
+// Python loops (moe_dispatch_gemm/benchmark.py:112-166).  Differences that matter to a caller:
+//   * everything data-dependent stays on the device: expert counts, padded segment sizes, the pull list, the
+//     number of row blocks and the combine map are produced by two small kernels, so a layer needs no host
+//     synchronisation;
+//   * rows travel as NVFP4 codes + row-major e4m3 scales (4032 bytes per 7168-wide token instead of 14336) and
+//     are pulled straight into the grouped GEMM's operand buffers by a few CTAs of the GEMM kernel;
+//   * within an expert segment rows are in ascending global token order (the reference walks source ranks as a
+//     ring starting at the local rank); segments are padded to 128 rows with (-1, -1) entries as in the reference;
+//   * combine (no counterpart in the reference): out[t] = bf16(sum_j w[t,j] * Y[row(t,j)]), fp32 accumulation in
+//     ascending j, rows read from the expert ranks over NVLink.
+#include <cstring>
+#include "../../include/tkb200.h"
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace tkb {
+
+int api_fail(int code, const char* fmt, ...);
+int api_device(int* sm_count, int** status);
+int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
+                       const void* B_sc, void* D, int64_t ldd, int M, int N, int K);
+
+// ------------------------------------------------------------------------------ routing ------
+// softmax over E logits, top-k by probability (ties -> lower expert id), weights renormalised over the k.
+// One warp per token; E % 32 == 0, E <= 256.
+template <int PER>
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int top_k, int* __restrict__ experts, float* __restrict__ weights) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    constexpr int E = PER * 32;
+    float p[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; i++) { p[i] = logits[size_t(warp) * E + i * 32 + lane]; mx = fmaxf(mx, p[i]); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    // sum in expert order (lane-major within each group of 32) so that it is the same on every launch
+#pragma unroll
+    for (int i = 0; i < PER; i++) { p[i] = expf(p[i] - mx); }
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        float s = p[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        sum += s;
+    }
+#pragma unroll
+    for (int i = 0; i < PER; i++) p[i] = __fdiv_rn(p[i], sum);
+    unsigned used = 0;
+    float wsum = 0.f, myw = 0.f; int mye = 0;
+    for (int j = 0; j < top_k; j++) {
+        float best = -1.f; int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < PER; i++)
+            if (!(used & (1u << i)) && p[i] > best) { best = p[i]; bi = i * 32 + lane; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if ((bi & 31) == lane) used |= 1u << (bi >> 5);
+        wsum += best;
+        if (lane == j) { myw = best; mye = bi; }
+    }
+    if (lane < top_k) {
+        experts[size_t(warp) * top_k + lane] = mye;
+        weights[size_t(warp) * top_k + lane] = __fdiv_rn(myw, wsum);
+    }
+}
+
+// ------------------------------------------------------------------------------ schedule -----
+// CTA e walks the whole (token, slot) -> expert list.  Warp w owns the contiguous span w of the list, so
+// positions come out in ascending list order without any block-wide synchronisation inside the loops.
+__device__ __forceinline__ int span_len(int total) { return ((total + 31) / 32 + 31) / 32 * 32; }
+
+__global__ void __launch_bounds__(1024) moe_count_kernel(const int* __restrict__ experts_all, int total, int* __restrict__ counts,
+                                                        int* __restrict__ padded) {
+    __shared__ int s_cnt[32];
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int span = span_len(total), lo = warp * span, hi = min(total, lo + span);
+    int c = 0;
+    for (int i = lo + lane; i < hi + ((32 - (hi - lo) % 32) % 32); i += 32)
+        c += __popc(__ballot_sync(0xffffffffu, i < hi && experts_all[i] == e));
+    if (lane == 0) s_cnt[warp] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 32; w++) t += s_cnt[w];
+        counts[e] = t;
+        padded[e] = (t + 127) / 128 * 128;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_assign_kernel(const int* __restrict__ experts_all, int total, int top_k, int E, int world, int rank, int tokens_per_rank,
+                  const int* __restrict__ counts, const int* __restrict__ padded, int* __restrict__ pull_idx, int* __restrict__ block_expert,
+                  int* __restrict__ num_blocks, int* __restrict__ comb_idx, int cap_rows, int* status) {
+    __shared__ int s_cnt[32];
+    __shared__ int s_base[33];
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e_per = E / world, owner = e / e_per, e_local = e % e_per;
+    int seg = 0;
+    for (int x = owner * e_per; x < e; x++) seg += padded[x];
+    const int span = span_len(total), lo = warp * span, hi = min(total, lo + span);
+    const int hi_pad = hi + ((32 - (hi - lo) % 32) % 32);
+    int c = 0;
+    for (int i = lo + lane; i < hi_pad; i += 32) c += __popc(__ballot_sync(0xffffffffu, i < hi && experts_all[i] == e));
+    if (lane == 0) s_cnt[warp] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 32; w++) { s_base[w] = t; t += s_cnt[w]; }
+        s_base[32] = t;
+    }
+    __syncthreads();
+    const bool mine = owner == rank;
+    const bool fits = seg + padded[e] <= cap_rows;
+    if (mine && !fits && threadIdx.x == 0 && status) atomicExch(status, 6 /* capacity */);
+    int run = s_base[warp];
+    for (int i = lo + lane; i < hi_pad; i += 32) {
+        const bool hit = i < hi && experts_all[i] == e;
+        const unsigned b = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+            const int pos = run + __popc(b & ((1u << lane) - 1u));
+            const int tok = i / top_k;
+            if (mine && fits) {
+                pull_idx[2 * (seg + pos)] = tok / tokens_per_rank;
+                pull_idx[2 * (seg + pos) + 1] = tok % tokens_per_rank;
+            }
+            if (tok / tokens_per_rank == rank) {
+                const int li = (tok % tokens_per_rank) * top_k + i % top_k;
+                comb_idx[2 * li] = owner;
+                comb_idx[2 * li + 1] = seg + pos;
+            }
+        }
+        run += __popc(b);
+    }
+    if (mine && fits) {
+        for (int r = counts[e] + threadIdx.x; r < padded[e]; r += blockDim.x) { pull_idx[2 * (seg + r)] = -1; pull_idx[2 * (seg + r) + 1] = -1; }
+        for (int b = threadIdx.x; b < padded[e] / 128; b += blockDim.x) block_expert[seg / 128 + b] = e_local;
+    }
+    if (mine && e_local == 0 && threadIdx.x == 0) {
+        int t = 0;
+        for (int x = owner * e_per; x < (owner + 1) * e_per; x++) t += padded[x];
+        *num_blocks = t <= cap_rows ? t / 128 : 0;
+    }
+}
+
+// ------------------------------------------------------------------------------ combine ------
+struct PeerRows { const __nv_bfloat16* p[kMaxWorld]; };
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(PeerRows Y, int64_t ldy, const int* __restrict__ comb_idx, const float* __restrict__ weights, int top_k, int I,
+                   __nv_bfloat16* __restrict__ out) {
+    const int t = blockIdx.x;
+    for (int v = threadIdx.x; v < I / 8; v += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j0 = 0; j0 < top_k; j0 += 4) {
+            uint4 q[4]; float w[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const int j = j0 + jj;
+                if (j < top_k) {
+                    const int dst = comb_idx[2 * (t * top_k + j)], row = comb_idx[2 * (t * top_k + j) + 1];
+                    w[jj] = weights[t * top_k + j];
+                    q[jj] = __ldcg(reinterpret_cast<const uint4*>(Y.p[dst] + int64_t(row) * ldy + v * 8));
+                } else { w[jj] = 0.f; q[jj] = make_uint4(0, 0, 0, 0); }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const uint32_t u[4] = {q[jj].x, q[jj].y, q[jj].z, q[jj].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    acc[2 * k] = fmaf(w[jj], __uint_as_float(u[k] << 16), acc[2 * k]);
+                    acc[2 * k + 1] = fmaf(w[jj], __uint_as_float(u[k] & 0xffff0000u), acc[2 * k + 1]);
+                }
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(out + int64_t(t) * I + v * 8) = o;
+    }
+}
+
+} // namespace tkb
+
+using namespace tkb;
+
+#define TKB_CUDA_M(expr)                                                                                      \
+    do {                                                                                                      \
+        cudaError_t _e = (expr);                                                                              \
+        if (_e != cudaSuccess) return api_fail(TKB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+extern "C" {
+
+int tkb_moe_route(const float* logits, int T, int E, int top_k, int* experts, float* weights, void* stream) {
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    if (!logits || !experts || !weights) return api_fail(TKB_ERR_INVALID_ARG, "moe_route: null pointer");
+    if (T < 1 || E % 32 || E < 32 || E > 256 || top_k < 1 || top_k > 32 || top_k > E)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_route: need E in {32,..,256} (multiple of 32) and 1 <= top_k <= 32");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int blocks = (T + 7) / 8;
+    switch (E / 32) {
+        case 1: moe_route_kernel<1><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 2: moe_route_kernel<2><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 3: moe_route_kernel<3><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 4: moe_route_kernel<4><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 5: moe_route_kernel<5><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 6: moe_route_kernel<6><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        case 7: moe_route_kernel<7><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+        default: moe_route_kernel<8><<<blocks, 256, 0, s>>>(logits, T, top_k, experts, weights); break;
+    }
+    TKB_CUDA_M(cudaGetLastError());
+    return TKB_OK;
+}
+
+int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world, int rank, int* counts, int* padded_per_expert,
+                     int* pull_idx, int* block_expert, int* num_blocks, int* comb_idx, int cap_rows, void* stream) {
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    if (!experts_all || !counts || !padded_per_expert || !pull_idx || !block_expert || !num_blocks || !comb_idx)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_schedule: null pointer");
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E % world || T % world || cap_rows % 128 || top_k < 1)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_schedule: E and T must divide by world (<= %d), cap_rows by 128", kMaxWorld);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    moe_count_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, counts, padded_per_expert);
+    moe_assign_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, top_k, E, world, rank, T / world, counts, padded_per_expert, pull_idx,
+                                         block_expert, num_blocks, comb_idx, cap_rows, status);
+    TKB_CUDA_M(cudaGetLastError());
+    return TKB_OK;
+}
+
+int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows, const float* X_sg, void* codes, void* scales,
+                          const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
+                          const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,
+                          int I, int experts_local, int cap_rows, int rank, int world, int comm_ctas, void* stream) {
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    if (!peer_codes || !peer_scale_rows || !X_sg || !codes || !scales || !W || !W_sc || !W_sg || !Y || !pull_idx || !block_expert ||
+        !num_blocks || !ready || !arrived)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: null pointer");
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: bad rank/world");
+    if (K % 256 || I % 128 || cap_rows % 128 || cap_rows < 128) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
+    if (K / 2 * 25 + (K / 16) * 256 > 190 * 1024) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
+    if (comm_ctas < 1 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [1, %d]", sm / 2);
+    if (ldy == 0) ldy = I;
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.kind = KIND_NVFP4; g.config = 1;        // single CTA, N tile 256
+    if (int e = api_make_gemm_maps(&g, KIND_NVFP4, codes, K / 2, scales, W, K / 2, W_sc, Y, ldy, cap_rows, I, K)) return e;
+    // the B maps above cover one expert; rebuild them over the stacked experts
+    GemmArgs gb;
+    memset(&gb, 0, sizeof(gb));
+    gb.kind = KIND_NVFP4; gb.config = 1;
+    if (int e = api_make_gemm_maps(&gb, KIND_NVFP4, codes, K / 2, scales, W, K / 2, W_sc, Y, ldy, cap_rows, I * experts_local, K)) return e;
+    g.tmB = gb.tmB; g.tmSB = gb.tmSB;
+    g.sgA = X_sg; g.sgB = W_sg; g.M = cap_rows; g.N = I; g.K = K; g.status = status; g.sm_count = sm;
+    g.stream = static_cast<cudaStream_t>(stream);
+    g.mode = MODE_MOE;
+    MoeParams& m = g.comm.moe;
+    for (int i = 0; i < world; i++) {
+        m.peer_codes[i] = static_cast<const uint8_t*>(peer_codes[i]);
+        m.peer_scales[i] = static_cast<const uint8_t*>(peer_scale_rows[i]);
+    }
+    m.codes = static_cast<uint8_t*>(codes); m.scales = static_cast<uint8_t*>(scales);
+    m.pull_idx = pull_idx; m.block_expert = block_expert; m.num_blocks = num_blocks;
+    m.ready = static_cast<const unsigned int*>(ready); m.arrived = static_cast<unsigned int*>(arrived);
+    m.epoch = epoch; m.rank = rank; m.world = world; m.comm_ctas = comm_ctas; m.expert_rows = I;
+    TKB_CUDA_M(launch_gemm(g));
+    return TKB_OK;
+}
+
+int tkb_moe_combine(void* const* peer_Y, int64_t ldy, const int* comb_idx, const float* weights, void* out, int T_local, int top_k, int I,
+                    int world, void* stream) {
+    if (!peer_Y || !comb_idx || !weights || !out) return api_fail(TKB_ERR_INVALID_ARG, "moe_combine: null pointer");
+    if (world < 1 || world > kMaxWorld || I % 8 || T_local < 1) return api_fail(TKB_ERR_INVALID_ARG, "moe_combine: bad arguments");
+    if (ldy == 0) ldy = I;
+    PeerRows pr;
+    for (int i = 0; i < kMaxWorld; i++) pr.p[i] = i < world ? static_cast<const __nv_bfloat16*>(peer_Y[i]) : nullptr;
+    moe_combine_kernel<<<T_local, 256, 0, static_cast<cudaStream_t>(stream)>>>(pr, ldy, comb_idx, weights, top_k, I, static_cast<__nv_bfloat16*>(out));
+    TKB_CUDA_M(cudaGetLastError());
+    return TKB_OK;
+}
+
+} // extern "C"

@@ -117,7 +117,7 @@ template <class Arith, bool SCALE_2D, bool FUSED_AMAX>
 __global__ void __launch_bounds__(Q_THREADS)
 nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
-                      int M, int K, int* status) {
+                      int M, int K, int* status, int sc_rowmajor) {
     __shared__ __align__(16) uint8_t s_sc[2][2][512];   // [double buffer][chunk][byte]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
@@ -169,7 +169,10 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
         for (int i = 0; i < 8; i++) {
             const int r = warp * 16 + 2 * i + (lane >> 4);     // row within the tile
             const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(am[i], sg_enc), __NV_SATFINITE, __NV_E4M3);
-            if ((lane & 1) == 0) s_sc[buf][kb_local >> 2][(r & 31) * 16 + (r >> 5) * 4 + (kb_local & 3)] = s8;
+            if ((lane & 1) == 0) {
+                if (sc_rowmajor) (&s_sc[buf][0][0])[r * 8 + kb_local] = s8;                       // [row][8 blocks of the tile]
+                else s_sc[buf][kb_local >> 2][(r & 31) * 16 + (r >> 5) * 4 + (kb_local & 3)] = s8;   // 512-byte chunk layout
+            }
             const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
             const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
             uint32_t packed = 0;
@@ -184,7 +187,13 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
             if (row < M && col < K) *reinterpret_cast<uint32_t*>(codes + int64_t(row) * ldc + col / 2) = packed;
         }
         __syncthreads();
-        {
+        if (sc_rowmajor) {
+            // plain [M, K/16] scale rows (used where rows travel individually, e.g. MoE dispatch)
+            const int r = threadIdx.x >> 1, half = threadIdx.x & 1;     // 4 scale bytes (64 columns) per thread
+            if (tc.row0 + r < M && tc.col0 + half * 64 < K)
+                *reinterpret_cast<uint32_t*>(sc + int64_t(tc.row0 + r) * (K / 16) + tc.col0 / 16 + half * 4) =
+                    reinterpret_cast<const uint32_t*>(&s_sc[buf][0][0])[r * 2 + half];
+        } else {
             const int c = threadIdx.x >> 7, word = threadIdx.x & 127;
             const int kc = tc.col0 / 64 + c;
             if (kc < k_chunks) {
@@ -222,7 +231,8 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     uint8_t* sc = static_cast<uint8_t*>(a.sc);
     int64_t lda = a.lda, ldc = a.ldc;
     float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
-    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status};
+    int sc_rowmajor = a.sc_rowmajor;
+    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status, &sc_rowmajor};
     static const bool coop = getenv("TKB_COOP") && atoi(getenv("TKB_COOP")) != 0;
     if (FUSED && coop) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
     return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);

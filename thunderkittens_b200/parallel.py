@@ -169,3 +169,97 @@ def all_gather_matmul(A: TKParallelTensor, W: torch.Tensor, W_sc: torch.Tensor, 
     if num_comm_sms is not None and A.local_world_size_ > 1:
         state.num_comm_sms = max(2, num_comm_sms - num_comm_sms % 2)
     state(A.data_[r * rows:(r + 1) * rows], W, W_sc, W_sg, C_out)
+
+
+class MoELayerNVFP4:
+    """Expert-parallel MoE layer with NVFP4 expert weights: route -> schedule -> quantize tokens -> dispatch fused
+    with the grouped expert GEMM -> combine.  Rank r owns tokens [r*T/world, (r+1)*T/world) and experts
+    [r*E/world, (r+1)*E/world); `W`, `W_sc`, `W_sg` are its stacked expert weights ([E/world * I, K/2] codes).
+
+    One forward(logits_local, X_local) call enqueues everything on the current stream and returns
+    out [T/world, I] bf16.  Nothing synchronises with the host; the row capacity of the operand buffers
+    (`cap_rows`, default twice the balanced share) is checked on the device.
+    """
+
+    def __init__(self, T: int, H: int, I: int, E: int, top_k: int, local_rank: int, local_world_size: int, cap_rows: int | None = None,
+                 num_comm_sms: int = 16, group=None):
+        w, r = local_world_size, local_rank
+        if T % w or E % w or H % 256 or I % 128:
+            raise RuntimeError("need T and E divisible by world, H % 256 == 0, I % 128 == 0")
+        self.T, self.H, self.I, self.E, self.top_k, self.rank, self.world, self.group = T, H, I, E, top_k, r, w, group
+        self.Tl, self.El = T // w, E // w
+        if cap_rows is None:
+            cap_rows = 2 * (T * top_k // w) + 128 * self.El
+        self.cap_rows = (cap_rows + 127) // 128 * 128
+        self.num_comm_sms = num_comm_sms
+        mk = lambda shape, dt: TKParallelTensor(shape, dt, r, w, False, group)
+        u8, i32, f32 = torch.uint8, torch.int32, torch.float32
+        # symmetric: quantized tokens (two sets), expert outputs, flags [ready(w), y_ready(w), done(w)]
+        self.xq_codes = [mk((self.Tl, H // 2), u8) for _ in range(2)]
+        self.xq_rows = [mk((self.Tl, H // 16), u8) for _ in range(2)]
+        self.Y = mk((self.cap_rows, I), torch.bfloat16)
+        self.flags = mk((3 * w,), i32)
+        dev = self.flags.data_.device
+        z = lambda *shape, dt=i32: torch.zeros(*shape, dtype=dt, device=dev)
+        self.codes = z(self.cap_rows, H // 2, dt=u8)
+        self.scales = z(self.cap_rows // 128, H // 64, 512, dt=u8)
+        self.experts_local = z(self.Tl, top_k)
+        self.weights = z(self.Tl, top_k, dt=f32)
+        self.experts_all = z(T, top_k)
+        self.counts, self.padded = z(E), z(E)
+        self.pull_idx = z(self.cap_rows, 2)
+        self.block_expert = z(self.cap_rows // 128)
+        self.num_blocks = z(1)
+        self.comb_idx = z(self.Tl * top_k, 2)
+        self.arrived = z(self.cap_rows // 128)
+        self.amax, self.sg = z(1, dt=f32), z(1, dt=f32)
+        self.out = torch.empty(self.Tl, I, dtype=torch.bfloat16, device=dev)
+        self.epoch = 0
+        if w > 1:
+            dist.barrier(group=group)
+
+    def forward(self, logits_local: torch.Tensor, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor) -> torch.Tensor:
+        lib, s = L.lib(), _stream()
+        w, r = self.world, self.rank
+        self.epoch += 1
+        e, b = self.epoch, self.epoch % 2
+        fl = self.flags.data_.data_ptr()
+        # routing of my tokens, then everybody's choices
+        L.check(lib.tkb_moe_route(logits_local.data_ptr(), self.Tl, self.E, self.top_k, self.experts_local.data_ptr(), self.weights.data_ptr(), s))
+        if w > 1:
+            dist.all_gather_into_tensor(self.experts_all, self.experts_local, group=self.group)
+        else:
+            self.experts_all.copy_(self.experts_local)
+        L.check(lib.tkb_moe_schedule(self.experts_all.data_ptr(), self.T, self.top_k, self.E, w, r, self.counts.data_ptr(), self.padded.data_ptr(),
+                                     self.pull_idx.data_ptr(), self.block_expert.data_ptr(), self.num_blocks.data_ptr(),
+                                     self.comb_idx.data_ptr(), self.cap_rows, s))
+        # quantize my tokens with the global amax into set b (peers finished reading its previous contents: done >= e-2)
+        if w > 1 and e > 2:
+            L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 2, s))
+        ops.absmax_bf16(X_local, self.amax)
+        if w > 1:
+            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
+        L.check(lib.tkb_nvfp4_quantize_rows(X_local.data_ptr(), 0, self.xq_codes[b].data_.data_ptr(), self.xq_rows[b].data_.data_ptr(),
+                                            self.sg.data_ptr(), self.amax.data_ptr(), self.Tl, self.H, L.NVFP4_SPEC, s))
+        if w > 1:
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))
+            # Y is rewritten below: every peer must have finished combining the previous layer call from it
+            if e > 1:
+                L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 1, s))
+        L.check(lib.tkb_moe_dispatch_gemm(self.xq_codes[b].peer_ptr_array(), self.xq_rows[b].peer_ptr_array(), self.sg.data_ptr(),
+                                          self.codes.data_ptr(), self.scales.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
+                                          self.Y.data_.data_ptr(), 0, self.pull_idx.data_ptr(), self.block_expert.data_ptr(),
+                                          self.num_blocks.data_ptr(), fl, self.arrived.data_ptr(), e, self.H, self.I, self.El, self.cap_rows,
+                                          r, w, self.num_comm_sms, s))
+        if w > 1:
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, w + r, e, 0, s))     # my Y rows are complete
+            L.check(lib.tkb_wait_flags(fl + 4 * w, w, r, e, s))                                  # everybody's are
+        L.check(lib.tkb_moe_combine(self.Y.peer_ptr_array(), 0, self.comb_idx.data_ptr(), self.weights.data_ptr(), self.out.data_ptr(),
+                                    self.Tl, self.top_k, self.I, w, s))
+        if w > 1:
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, 2 * w + r, e, 0, s))  # done with peers' tokens and Y
+        return self.out
+
+    def close(self) -> None:
+        for t in self.xq_codes + self.xq_rows + [self.Y, self.flags]:
+            t.close()
