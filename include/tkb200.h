@@ -115,6 +115,18 @@ int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const voi
 int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
                       void* D, int64_t ldd, int M, int N, int K, int config, void* stream);
 
+/* The skinny-M NVFP4 GEMM (M <= 16) for callers that must not allocate device memory where they call it:
+ * runtimes that reserve every buffer at start-up and forbid allocation on the request path, plug-in "enqueue"
+ * hooks, code that is recording into a stream capture.  It has no counterpart in the reference.  Same operands and
+ * result as tkb_nvfp4_gemm, but it neither creates the per-device context nor any scratch buffer: the stream-K
+ * scratch (one 16 x 128 fp32 partial tile and a flag per CTA, about 1.3 MB) is an array built into the library,
+ * which every GPU that loads the library holds until the process exits.  Hence the limit M <= 16; larger M is
+ * rejected with TKB_ERR_INVALID_ARG.  The first call on a device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls on a device share the array: calls that may overlap on the
+ * GPU (different streams) race and must be ordered by the caller.  Device-side timeouts are not reported. */
+int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, const float* X_sg, const void* W, const void* W_sc,
+                                 const float* W_sg, void* D, int64_t ldd, int M, int N, int K, void* stream);
+
 /* Replaces mxfp8_gemm(A, A_sc, B, B_sc, D) (mxfp8_b200_gemm.cu:585-603).  K % 128 == 0, N % 8 == 0. */
 int tkb_mxfp8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
                    void* stream);

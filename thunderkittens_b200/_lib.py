@@ -35,6 +35,7 @@ _SIGNATURES = {
     "tkb_fp4x2_to_fp32": ([_vp, _vp, _sz, _vp], _i),
     "tkb_nvfp4_gemm": ([_vp] * 7 + [_i64, _i, _i, _i, _vp], _i),
     "tkb_nvfp4_gemm_ex": ([_vp] * 7 + [_i64, _i, _i, _i, _i, _vp], _i),
+    "tkb_nvfp4_gemm_skinny_static": ([_vp] * 7 + [_i64, _i, _i, _i, _vp], _i),
     "tkb_mxfp8_gemm": ([_vp] * 5 + [_i64, _i, _i, _i, _vp], _i),
     "tkb_mxfp8_gemm_ex": ([_vp] * 5 + [_i64, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp], _i),

@@ -16,6 +16,8 @@
 //   * warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue; two accumulator buffers in
 //     tensor memory so the epilogue of one segment overlaps the main loop of the next.
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
 #include "ptx.cuh"
 #include "internal.h"
 
@@ -339,3 +341,119 @@ cudaError_t launch_decode(const DecodeArgs& a) {
 }
 
 } // namespace tkb
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the skinny-M GEMM.
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: inference
+// runtimes that size every buffer at start-up and treat an allocation on the request path as a bug (it
+// synchronises the device and can fail under memory pressure), plug-in interfaces whose "enqueue" hook
+// forbids cudaMalloc, and code that is recording work into a stream capture.  The regular entry point
+// tkb_nvfp4_gemm creates a per-device context and its stream-K scratch with cudaMalloc on first use, so those
+// callers get this second door: the scratch lives in a fixed array that is part of the loaded module.
+//
+// The array costs kStaticScratchBytes (about 1.3 MB) of device memory on every GPU that loads the library,
+// for as long as the process lives, which is why it is sized for the smallest activation tile only: M <= 16
+// (one 16 x 128 fp32 partial tile and one flag per CTA, up to kStaticMaxGrid CTAs).
+namespace tkb {
+
+constexpr int kStaticMaxGrid = 160;
+constexpr int kStaticMaxM = 16;
+constexpr size_t kStaticPartialBytes = size_t(kStaticMaxGrid) * 16 * 128 * sizeof(float);
+constexpr size_t kStaticFlagBytes = size_t(kStaticMaxGrid) * sizeof(unsigned int);
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + 1024;     // flags live in the last 1 KB
+
+static_assert(kStaticFlagBytes <= 1024, "flag area");
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int api_fail(int code, const char* fmt, ...);     // api.cu: records the calling thread's error message
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+struct StaticDev { bool ready; unsigned char* scratch; int sm_count; };
+StaticDev g_static_dev[kStaticMaxDevices];
+std::mutex g_static_mu;
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_static_encode = nullptr;
+
+bool encode_2d(CUtensorMap* m, const void* base, uint64_t inner_bytes, uint64_t rows, uint32_t box_rows) {
+    cuuint64_t dims[2] = {inner_bytes, rows};
+    cuuint64_t strides[1] = {inner_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return g_static_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+bool encode_scales(CUtensorMap* m, const void* base, uint64_t row_blocks, uint64_t k_chunks) {
+    cuuint64_t dims[3] = {128, k_chunks, row_blocks};
+    cuuint64_t strides[2] = {512, 512 * k_chunks};
+    cuuint32_t box[3] = {128, 4, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return g_static_encode(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+} // namespace
+} // namespace tkb
+
+extern "C" int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, const float* X_sg, const void* W, const void* W_sc,
+                                            const float* W_sg, void* D, int64_t ldd, int M, int N, int K, void* stream) {
+    using namespace tkb;
+    if (!X || !X_sc || !X_sg || !W || !W_sc || !W_sg || !D) return api_fail(1, "gemm_skinny_static: null pointer");
+    if (M < 1 || M > kStaticMaxM)
+        return api_fail(1, "gemm_skinny_static: M=%d is outside 1..%d, the range the built-in %zu-byte scratch array is sized for; "
+                           "use tkb_nvfp4_gemm for larger M", M, kStaticMaxM, kStaticScratchBytes);
+    if (N < 1 || K < 64 || K % 64 || N % 8) return api_fail(1, "gemm_skinny_static: need N %% 8 == 0 and K a positive multiple of 64 (N=%d K=%d)", N, K);
+    if (ldd == 0) ldd = N;
+    if (ldd < N) return api_fail(1, "gemm_skinny_static: ldd must be >= N");
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(X_sc) | reinterpret_cast<uintptr_t>(W_sc)) & 15u)
+        return api_fail(2, "gemm_skinny_static: operand and scale pointers must be 16-byte aligned");
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: cudaGetDevice failed: %s", cudaGetErrorString(ce));
+    if (dev < 0 || dev >= kStaticMaxDevices) return api_fail(1, "gemm_skinny_static: device ordinal %d out of range", dev);
+    StaticDev& sd = g_static_dev[dev];
+    if (!sd.ready) {
+        // First call on this device (it is the current device): resolve the device address of the scratch
+        // array.  The array's name is only a host-side handle for the symbol, never a pointer a kernel can use.
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!sd.ready) {
+            void* p = nullptr;
+            ce = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (ce != cudaSuccess || !p) return api_fail(3, "gemm_skinny_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(ce));
+            int major = 0, sms = 0;
+            ce = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+            if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: cudaDeviceGetAttribute failed: %s", cudaGetErrorString(ce));
+            if (major != 10) return api_fail(5, "gemm_skinny_static: device %d is not sm_100", dev);
+            if (!g_static_encode) {
+                void* fn = nullptr;
+                cudaDriverEntryPointQueryResult q;
+                ce = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+                if (ce != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess) return api_fail(5, "gemm_skinny_static: cuTensorMapEncodeTiled is unavailable");
+                g_static_encode = reinterpret_cast<EncodeFn>(fn);
+            }
+            sd.scratch = static_cast<unsigned char*>(p);
+            sd.sm_count = sms;
+            sd.ready = true;
+        }
+    }
+    DecodeArgs a;
+    memset(&a, 0, sizeof(a));
+    if (!encode_2d(&a.tmW, W, uint64_t(K / 2), uint64_t(N), 128) || !encode_2d(&a.tmX, X, uint64_t(K / 2), uint64_t(M), 16) ||
+        !encode_scales(&a.tmSW, W_sc, uint64_t((N + 127) / 128), uint64_t(K / 64)) || !encode_scales(&a.tmSX, X_sc, 1, uint64_t(K / 64)))
+        return api_fail(3, "gemm_skinny_static: cuTensorMapEncodeTiled failed");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned int* flags = reinterpret_cast<unsigned int*>(sd.scratch + kStaticPartialBytes);
+    // The array keeps whatever the previous call left in it.  Partial tiles are always written before they
+    // are read, but a flag still holding the value 1 would be taken for "already published": clear them.
+    ce = cudaMemsetAsync(flags, 0, kStaticFlagBytes, s);
+    if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: cudaMemsetAsync failed: %s", cudaGetErrorString(ce));
+    a.sgX = X_sg; a.sgW = W_sg; a.D = D; a.ldd = ldd; a.M = M; a.N = N; a.K = K;
+    a.partials = reinterpret_cast<float*>(sd.scratch); a.flags = flags; a.epoch = 1; a.max_grid = kStaticMaxGrid;
+    a.status = nullptr; a.sm_count = sd.sm_count; a.stream = s;
+    ce = launch_decode(a);
+    if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: launch failed: %s", cudaGetErrorString(ce));
+    return 0;
+}
