@@ -116,8 +116,8 @@ int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const 
                       void* D, int64_t ldd, int M, int N, int K, int config, void* stream);
 
 /* The skinny-M NVFP4 GEMM (M <= 16) for callers that must not allocate device memory where they call it:
- * runtimes that reserve every buffer at start-up and forbid allocation on the request path, plug-in "enqueue"
- * hooks, code that is recording into a stream capture.  It has no counterpart in the reference.  Same operands and
+ * runtimes that reserve every buffer at start-up and forbid allocation on the request path, and plug-in "enqueue"
+ * hooks that are not allowed to call cudaMalloc.  It has no counterpart in the reference.  Same operands and
  * result as tkb_nvfp4_gemm, but it neither creates the per-device context nor any scratch buffer: the stream-K
  * scratch (one 16 x 128 fp32 partial tile and a flag per CTA, about 1.3 MB) is an array built into the library,
  * which every GPU that loads the library holds until the process exits.  Hence the limit M <= 16; larger M is

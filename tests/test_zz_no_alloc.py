@@ -1,8 +1,8 @@
 """The allocation-free door to the skinny-M NVFP4 GEMM (tkb_nvfp4_gemm_skinny_static).
 
 Who needs it: a host program that is not allowed to allocate device memory at the moment it calls the library — a
-serving runtime that reserves all of its memory when it starts, a plug-in whose execute hook forbids cudaMalloc, a
-caller that is inside a stream capture.  The regular entry point allocates a per-device context and stream-K scratch
+serving runtime that reserves all of its memory when it starts, or a plug-in whose execute hook forbids
+cudaMalloc.  The regular entry point allocates a per-device context and stream-K scratch
 on first use; this one keeps its scratch in an array that is part of the library image and therefore only serves
 M <= 16.  The test drives both entry points through the C ABI with the same operands and expects the same result
 (the tolerance is the one of the other GEMM tests), twice in a row with different activations so that whatever the

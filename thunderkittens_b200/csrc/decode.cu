@@ -347,8 +347,8 @@ cudaError_t launch_decode(const DecodeArgs& a) {
 //
 // Some hosts of this library may not allocate device memory at the point where they call it: inference
 // runtimes that size every buffer at start-up and treat an allocation on the request path as a bug (it
-// synchronises the device and can fail under memory pressure), plug-in interfaces whose "enqueue" hook
-// forbids cudaMalloc, and code that is recording work into a stream capture.  The regular entry point
+// synchronises the device and can fail under memory pressure), and plug-in interfaces whose "enqueue"
+// hook forbids cudaMalloc.  The regular entry point
 // tkb_nvfp4_gemm creates a per-device context and its stream-K scratch with cudaMalloc on first use, so those
 // callers get this second door: the scratch lives in a fixed array that is part of the loaded module.
 //
