@@ -276,7 +276,81 @@ def run_tp(args) -> None:
     dist.destroy_process_group()
 
 
+def run_moe(args) -> None:
+    """MoE layer (BASELINE configs[4]): 16384 tokens, hidden 7168, 128 experts, intermediate 2048, top-8 routing from a
+    softmax over seeded N(0,1) logits, NVFP4 expert weights ~N(0,0.02), experts and tokens sharded over the ranks.
+    A step = route -> schedule -> quantize -> dispatch fused with the grouped GEMM -> combine."""
+    import torch
+    import torch.distributed as dist
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib, parallel
+
+    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T, H, I, E, k = 16384, 7168, 2048, 128, 8
+    Tl, El = T // world, E // world
+    u8 = torch.uint8
+    layer = parallel.MoELayerNVFP4(T, H, I, E, k, local_rank, world, num_comm_sms=args.comm_sms if args.comm_sms != 8 else 16)
+    amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
+    wc = torch.empty(El * I, H // 2, dtype=u8, device=dev); ws = torch.empty(El * I // 128, H // 64, 512, dtype=u8, device=dev)
+    wg = torch.empty(1, dtype=torch.float32, device=dev)
+    for e in range(El):       # expert by expert to keep the bf16 staging small
+        W = synth(torch, dev, I, H, 1100 + rank * El + e, std=0.02)
+        ops.absmax_bf16(W, amax_w)     # per-expert amax is fine for a benchmark; one common scale is used below
+        if e == 0:
+            common = amax_w.clone()
+        else:
+            common = torch.maximum(common, amax_w)
+        del W
+    if world > 1:
+        dist.all_reduce(common, op=dist.ReduceOp.MAX)
+    for e in range(El):
+        W = synth(torch, dev, I, H, 1100 + rank * El + e, std=0.02)
+        sg_tmp = torch.empty(1, dtype=torch.float32, device=dev)
+        ops.nvfp4_quantize(W, wc[e * I:(e + 1) * I], ws[e * I // 128:(e + 1) * I // 128], wg, False, amax=common)
+        del W
+    sets = [(synth(torch, dev, Tl, E, 900 + 10 * gi + rank).float(), synth(torch, dev, Tl, H, 1000 + 10 * gi + rank)) for gi in range(3)]
+    torch.cuda.synchronize()
+
+    def step(i):
+        lg, X = sets[i % 3]
+        layer.forward(lg, X, wc, ws, wg)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    dt = event_time(torch, step, args.steps)
+    st = _lib.device_status()
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    rows = int(layer.num_blocks.item()) * 128
+    if rank == 0:
+        flops = 2.0 * T * k * H * I
+        print(json.dumps({"metric": "MoE layer throughput (16384 tokens, H 7168, 128 experts, I 2048, top-8, NVFP4)", "value": flops / dt * 1e-12,
+                          "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "ms_per_step": dt * 1e3, "scaling": "strong",
+                          "device_status": st, "rank0_padded_rows": rows, "comm_ctas": layer.num_comm_sms,
+                          "dispatch_bytes_in_per_gpu": (world - 1) / world * T * k / world * (H // 2 + H // 16),
+                          "combine_bytes_in_per_gpu": (world - 1) / world * Tl * k * I * 2,
+                          "config": {"workload": "MoE layer", "parallelism": f"ep{world}"}}), flush=True)
+    barrier()
+    layer.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_ours(args) -> None:
+    if args.workload == "moe":
+        return run_moe(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         return run_tp(args)
     import torch
@@ -509,6 +583,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--k", type=int, default=None)
     ap.add_argument("--config", default=None)
+    ap.add_argument("--workload", default="auto", choices=["auto", "moe"], help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer")
     ap.add_argument("--comm-sms", type=int, default=8, help="CTAs of the tensor-parallel kernel that pull peer shards")
     args = ap.parse_args()
     if args.case:

@@ -161,14 +161,15 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
  * (kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305; the reference ships bf16 and fp8 variants only).
  *   D[M, N_local] = gather_rows(Xq)[M, K] . W_local[N_local, K]^T.
  * peer_codes[i] / peer_scales[i]: rank i's gathered buffers ([M, K/2] bytes, [M/128, K/64, 512] bytes) as seen
- * from this rank; entry `rank` is local and writable.  Each rank quantizes its M/world rows (with the all-reduced
- * per-tensor amax, so X_sg is the same everywhere) into its own slice of its own buffers, then signals
- * ready[rank] = epoch on every peer.  comm_ctas CTAs of the kernel pull the other slices over NVLink while the
- * rest multiply, own rows first.  `ready` [world] and `arrived` [M/256] are 32-bit epoch arrays on this rank.
- * M % (256 * world) == 0. */
+ * from this rank; entry `rank` is local.  Each rank quantizes its M/world rows (with the all-reduced per-tensor
+ * amax, so X_sg is the same everywhere) into its own slice of its own buffers; comm_ctas CTAs of the kernel push
+ * that slice into every peer's buffers over NVLink while the rest multiply, own rows first.  peer_arrived[i]: rank
+ * i's array of M/256 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own row blocks
+ * on every peer.  Before a buffer set is reused the caller must know that every peer finished reading it
+ * (tkb_signal_peers / tkb_wait_flags).  M % (256 * world) == 0. */
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
-                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, const void* ready,
-                      void* arrived, unsigned int epoch, int comm_ctas, void* stream);
+                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
+                      unsigned int epoch, int comm_ctas, void* stream);
 
 /* ---- MoE layer -----------------------------------------------------------------------------------
  * Replaces moe_dispatch_gemm(pre_tokens, post_tokens, weights, outputs, padded_tokens_per_expert,

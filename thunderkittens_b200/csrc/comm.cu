@@ -113,11 +113,11 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
 }
 
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
-                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, const void* ready,
-                      void* arrived, unsigned int epoch, int comm_ctas, void* stream) {
+                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
+                      unsigned int epoch, int comm_ctas, void* stream) {
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
-    if (!peer_codes || !peer_scales || !X_sg || !W || !W_sc || !W_sg || !D || !ready || !arrived)
+    if (!peer_codes || !peer_scales || !X_sg || !W || !W_sc || !W_sg || !D || !peer_arrived)
         return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world must be 1..%d", kMaxWorld);
     if (M % (256 * world)) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: M=%d must be a multiple of 256 * world", M);
@@ -138,8 +138,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     }
     g.comm.ag.codes = static_cast<uint8_t*>(peer_codes[rank]);
     g.comm.ag.scales = static_cast<uint8_t*>(peer_scales[rank]);
-    g.comm.ag.ready = static_cast<const unsigned int*>(ready);
-    g.comm.ag.arrived = static_cast<unsigned int*>(arrived);
+    for (int i = 0; i < world; i++) g.comm.ag.peer_arrived[i] = static_cast<unsigned int*>(peer_arrived[i]);
     g.comm.ag.epoch = epoch; g.comm.ag.rank = rank; g.comm.ag.world = world; g.comm.ag.blocks_per_rank = M / world / 256;
     g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
     TKB_CUDA_C(launch_gemm(g));

@@ -9,7 +9,7 @@
 //     (padded) activation rows are its N side (N = 16/32/64/128), so no tensor-core work is wasted
 //     on padding a 1..128-row activation up to a 128/256-row tile;
 //   * stream-K: the (slab, 256-wide K-block) work items are cut into one contiguous, equal range per
-//     CTA (one persistent CTA per SM, cooperative launch).  A CTA that starts a slab finishes it; a
+//     CTA (one persistent CTA per SM).  A CTA that starts a slab finishes it; a
 //     CTA that only covers the tail of a slab writes its fp32 partial tile to scratch first thing
 //     and raises a flag.  The finisher reaches its (last) head segment after all its other work, so
 //     the partials it needs are normally already there; its wait is bounded like every other wait;
@@ -137,21 +137,41 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     WaitCtx wc{&s_abort, p.status};
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ----------------------------------------------------------------- TMA producer -----
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // The weights do not depend on the kernel that runs before this one in the stream (the activation
+            // quantizer): fill the ring with weight tiles first, only then wait for that kernel and add the
+            // activation tiles of the same stages.
+            int prefetched = 0;
+            {
+                WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+                Segment sg;
+                while (prefetched < C::STAGES && wr.next(sg))
+                    for (int kb = sg.kb0; kb < sg.kb1 && prefetched < C::STAGES; kb++, prefetched++) {
+                        const uint32_t full = smem_u32(&bar_full[prefetched]);
+                        mbar_arrive_expect_tx(full, C::TX_BYTES);
+                        tma_load_2d(sW + prefetched * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
+                        tma_load_3d_d(sSW + prefetched * C::SF_BYTES, &tmSW, full, 0, kb * 4, sg.slab);
+                    }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
             Segment sg;
+            int item = 0;
             while (ok && wr.next(sg)) {
-                for (int kb = sg.kb0; kb < sg.kb1; kb++) {
-                    if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                for (int kb = sg.kb0; kb < sg.kb1; kb++, item++) {
                     const uint32_t full = smem_u32(&bar_full[stage]);
-                    mbar_arrive_expect_tx(full, C::TX_BYTES);
-                    tma_load_2d(sW + stage * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
-                    tma_load_3d_d(sSW + stage * C::SF_BYTES, &tmSW, full, 0, kb * 4, sg.slab);
+                    if (item >= prefetched) {
+                        if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
+                        mbar_arrive_expect_tx(full, C::TX_BYTES);
+                        tma_load_2d(sW + stage * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
+                        tma_load_3d_d(sSW + stage * C::SF_BYTES, &tmSW, full, 0, kb * 4, sg.slab);
+                    }
                     tma_load_2d(sX + stage * C::X_BYTES, &tmX, full, kb * 128, 0);
                     tma_load_3d_d(sSX + stage * C::SF_BYTES, &tmSX, full, 0, kb * 4, 0);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -205,6 +225,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // ----------------------------------------------------------------- epilogue ----------
         const int quarter = warp & 3;
         const int n_local = quarter * 32 + lane;           // weight row inside the slab
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // the activation scale comes from the previous kernel; D / scratch may still be read by it
         const float alpha = __fmul_rn(*p.sgX, *p.sgW);
         int seg_idx = 0;
         bool ok = true;
@@ -324,9 +345,18 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status};
     CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
     void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
-    static const bool coop = getenv("TKB_COOP") && atoi(getenv("TKB_COOP")) != 0;
-    if (coop) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(C::THREADS), params, C::SMEM_BYTES, a.stream);
-    return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(C::THREADS), params, C::SMEM_BYTES, a.stream);
+    (void)params;
+    // Programmatic stream serialization: the kernel may start while its predecessor in the stream drains; it prefetches
+    // weights, and executes griddepcontrol.wait before anything that depends on (or could disturb) earlier kernels.
+    // All CTAs of the grid are expected to be resident together (grid <= SM count, one CTA per SM); the stream-K waits
+    // are bounded, so a CTA that is kept off the GPU for long shows up as a reported timeout, not a hang.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(C::THREADS); cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmSW, tmSX, p);
 }
 
 int decode_padded_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }

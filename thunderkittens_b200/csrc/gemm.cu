@@ -25,6 +25,7 @@
 //     past M / N are clipped by the TMA unit.
 //   * Every mbarrier wait is bounded (ptx.cuh); on a timeout the kernel records the status, leaves
 //     its loops, joins the final cluster barrier, frees TMEM and returns.
+#include <cstdlib>
 #include "ptx.cuh"
 #include "internal.h"
 
@@ -65,6 +66,7 @@ struct GemmCfg {
 struct GemmParams {
     const float* sgA; const float* sgB;
     int M, N, K;
+    int group;                  // row blocks that share a sweep over the columns
     int* status;
     unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
 };
@@ -119,28 +121,30 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
                  ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
 }
 
-// One comm CTA: pulls its share of the (source rank, 256-row block) units into the local buffers.
+// One comm CTA: PUSHES its share of the (destination rank, 256-row block of this rank's slice) units into the
+// destinations' buffers.  Reads are local (fast), the NVLink side is posted writes, so a handful of CTAs can
+// fill the links; a pull over NVLink is limited per SM by the read round trip.  Destinations are served in
+// the order in which they will consume this rank's rows (rank-1 first).  After a unit's bytes are complete a
+// system-scope release store publishes the epoch in the destination's `arrived` array.
 template <int RING, int PIECE>
-__device__ void ag_pull(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
+__device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
                         const WaitCtx& wc) {
-    // single thread; bars[0..RING) are "piece landed" barriers
+    // single thread; bars[0..RING) are "piece landed in shared memory" barriers
     const int units = (ag.world - 1) * ag.blocks_per_rank;
     uint32_t issued = 0, stored = 0;         // piece counters over the whole kernel (ring position / phase)
     for (int u = comm_idx; u < units; u += ag.comm_ctas) {
-        const int src = (ag.rank + 1 + u / ag.blocks_per_rank) % ag.world;
+        const int dst = (ag.rank + ag.world - 1 - u / ag.blocks_per_rank) % ag.world;
         const int b = u % ag.blocks_per_rank;
-        if (!flag_wait(wc, ag.ready + src, ag.epoch)) return;
-        const size_t row0 = (size_t(src) * ag.blocks_per_rank + b) * 256;
+        const size_t row0 = (size_t(ag.rank) * ag.blocks_per_rank + b) * 256;
         // two contiguous spans: codes of 256 rows, scales of two 128-row blocks
         const size_t off[2] = {row0 * k_bytes, (row0 / 128) * sc_bytes_per_mblock};
         const size_t len[2] = {size_t(256) * k_bytes, size_t(2) * sc_bytes_per_mblock};
-        const uint8_t* sbase[2] = {ag.peer_codes[src], ag.peer_scales[src]};
-        uint8_t* dbase[2] = {ag.codes, ag.scales};
+        const uint8_t* sbase[2] = {ag.codes, ag.scales};
+        uint8_t* dbase[2] = {const_cast<uint8_t*>(ag.peer_codes[dst]), const_cast<uint8_t*>(ag.peer_scales[dst])};
         for (int span = 0; span < 2; span++) {
             const size_t n_pieces = (len[span] + PIECE - 1) / PIECE;
             size_t next_load = 0;
             for (size_t i = 0; i < n_pieces; i++) {
-                // keep up to RING loads in flight
                 while (next_load < n_pieces && issued - stored < RING) {
                     const uint32_t slot = issued % RING;
                     const size_t o = next_load * PIECE;
@@ -159,9 +163,9 @@ __device__ void ag_pull(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
                 stored++;
             }
         }
-        tma_store_wait<0>();                 // all bytes of this unit are in local memory
-        __threadfence();
-        st_release_gpu_u32(ag.arrived + src * ag.blocks_per_rank + b, ag.epoch);
+        tma_store_wait<0>();                 // all bytes of this unit have been written to the destination
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.peer_arrived[dst] + ag.rank * ag.blocks_per_rank + b), "r"(ag.epoch) : "memory");
     }
 }
 
@@ -175,7 +179,6 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, 
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
-
 
 // One comm CTA of the MoE kernel (all 320 threads): fills its share of the 128-row blocks of the local
 // activation buffer.  Per block: the 128 (source rank, source row) pairs of the dispatch list are pulled
@@ -307,7 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const bool is_comm = int(blockIdx.x) < comm_ctas;
     const int first_tile = (CTAS == 2 ? int(cluster_id_x()) : int(blockIdx.x)) - comm_units;
     const int tile_stride = (CTAS == 2 ? int(num_clusters_x()) : int(gridDim.x)) - comm_units;
-    const int tile_group = AG ? ag.blocks_per_rank : (MOE ? 1 : 8);
+    const int tile_group = AG ? ag.blocks_per_rank : (MOE ? 1 : p.group);
     const int tile_rot = AG ? ag.rank * ag.blocks_per_rank : 0;
 
     if (threadIdx.x == 0) {
@@ -328,6 +331,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
     WaitCtx wc{&s_abort, p.status};
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // successors launched with programmatic serialization wait on their own
 
     if constexpr (MOE) {
         if (is_comm) {
@@ -347,7 +351,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // reuse the (idle) "full" barriers of this CTA as piece barriers and the operand ring as staging
                 constexpr int PIECE = 32768;
                 constexpr int RING = (C::STAGES * C::STAGE_BYTES) / PIECE < C::STAGES ? (C::STAGES * C::STAGE_BYTES) / PIECE : C::STAGES;
-                ag_pull<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_full, wc);
+                ag_push<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_full, wc);
             }
             __syncthreads();
             cluster_sync();      // matches the teardown barrier of the compute clusters' code path below
@@ -377,7 +381,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if constexpr (AG) {
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
-                        if (!flag_wait(wc, ag.arrived + m_blk, ag.epoch)) { ok = false; break; }
+                        if (!flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk, ag.epoch)) { ok = false; break; }
                         fence_proxy_async_all();
                     }
                 }
@@ -484,6 +488,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (KIND == KIND_NVFP4) alpha = __fmul_rn(*p.sgA, *p.sgB);
         const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
         const uint32_t stage_box = sEpi + ew * C::EPI_WARP_BYTES;
+        const uint64_t d_policy = l2_policy_evict_first();     // D is written once and never read here: keep the operands in L2 instead
         uint32_t tile_phase = 0;
         bool ok = true;
         long long wait_tf = 0, drain = 0;
@@ -527,7 +532,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0 && row0 < p.M && col0 + 64 * h < p.N) {
-                    tma_store_2d(&tmD, stage_box, col0 + 64 * h, row0);
+                    tma_store_2d_hint(&tmD, stage_box, col0 + 64 * h, row0, d_policy);
                     tma_store_commit();
                 }
             }
@@ -572,7 +577,8 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, a.status, a.prof};
+    static const int group_env = getenv("TKB_GEMM_GROUP") ? atoi(getenv("TKB_GEMM_GROUP")) : 0;
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 8, a.status, a.prof};
     return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
 

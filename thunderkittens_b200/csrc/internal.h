@@ -25,8 +25,8 @@ struct AgParams {
     const uint8_t* peer_codes[kMaxWorld];    // base of every rank's gathered-codes buffer [M, K/2] (own entry = local)
     const uint8_t* peer_scales[kMaxWorld];   // base of every rank's gathered-scales buffer [M/128, K/64, 512]
     uint8_t* codes; uint8_t* scales;         // this rank's buffers (same as peer_*[rank], writable)
-    const unsigned int* ready;               // [world] written by peers: "my slice holds epoch e"
-    unsigned int* arrived;                   // [world * blocks_per_rank] written by the comm CTAs of this kernel
+    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs [world * blocks_per_rank]; entry (s, b) of rank r's
+                                             // array is written by rank s when block b of its slice has landed on rank r
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
 };

@@ -250,7 +250,8 @@ int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows,
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: bad rank/world");
     if (K % 256 || I % 128 || cap_rows % 128 || cap_rows < 128) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
-    if (K / 2 * 25 + (K / 16) * 256 > 190 * 1024) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
+    // dispatch staging per comm CTA: two copies of a block's scales (128 x K/16 bytes each), a zero row and >= 4 code-row slots
+    if (2 * 128 * (K / 16) + 5 * (K / 2) + 256 > 190 * 1024) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
     if (comm_ctas < 1 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [1, %d]", sm / 2);
     if (ldy == 0) ldy = I;
     GemmArgs g;

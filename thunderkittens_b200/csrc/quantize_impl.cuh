@@ -90,22 +90,28 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
         bool ok = true;
         while (*reinterpret_cast<volatile unsigned int*>(&ws->arrived) < gridDim.x) {
             if (clock64() - t0 > TKB_SPIN_LIMIT_CYCLES) { ok = false; break; }
-            __nanosleep(64);
         }
         __threadfence();
         float r = ok ? __uint_as_float(*reinterpret_cast<volatile unsigned int*>(&ws->amax_bits)) : -1.0f;
         if (!ok && status) atomicExch(status, 4 /* timeout */);
-        // the last block to leave restores the slot for the next call
-        if (atomicAdd(&ws->departed, 1u) == gridDim.x - 1) {
-            ws->amax_bits = 0u; ws->departed = 0u;
-            __threadfence();
-            ws->arrived = 0u;
-        }
         s_amax = r;
     }
     __syncthreads();
     return s_amax;
 }
+
+// Called by thread 0 of every block once it no longer needs the slot: the last block to leave restores
+// the slot for the next call (off the critical path of the quantization itself).
+__device__ __forceinline__ void grid_amax_depart(QuantWork* ws) {
+    if (atomicAdd(&ws->departed, 1u) == gridDim.x - 1) {
+        ws->amax_bits = 0u; ws->departed = 0u;
+        __threadfence();
+        ws->arrived = 0u;
+    }
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------ NVFP4 -----
 // Arith supplies:
@@ -113,7 +119,9 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
 //   static float block_scale(float amax16, float sg_enc)             value fed to the e4m3 conversion
 //   static float block_enc(float s_local_dec, float sg_dec)          multiplier applied to the inputs
 //   static float scale_value(float x, float s_enc)
-template <class Arith, bool SCALE_2D, bool FUSED_AMAX>
+// RESIDENT: the grid has one CTA per tile and the tile stays in registers between the amax pass and the
+// quantization (one read of the input); otherwise the grid is persistent and the input is read twice.
+template <class Arith, bool SCALE_2D, bool FUSED_AMAX, bool RESIDENT>
 __global__ void __launch_bounds__(Q_THREADS)
 nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
@@ -125,14 +133,23 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     const int num_tiles = tiles_m * tiles_n;
     const int k_chunks = K / 64;
 
+    // launched with programmatic stream serialization: everything above overlapped the previous kernel's tail
+    pdl_wait();
+    pdl_launch_dependents();
     float amax;
+    uint4 v[8];
     if constexpr (FUSED_AMAX) {
         float local = 0.f;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            uint4 v[8];
-            load_tile(A, lda, M, K, tile_coord(tile, tiles_n), warp, lane, v);
+        if constexpr (RESIDENT) {
+            load_tile(A, lda, M, K, tile_coord(blockIdx.x, tiles_n), warp, lane, v);
 #pragma unroll
             for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
+        } else {
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                load_tile(A, lda, M, K, tile_coord(tile, tiles_n), warp, lane, v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
+            }
         }
         amax = grid_amax_barrier(ws, local, status);
         if (amax < 0.f) return;
@@ -145,10 +162,9 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
 
     int buf = 0;
     // walk the tiles in reverse: the tail of the amax pass is the part most likely still in L2
-    for (int t = num_tiles - 1 - int(blockIdx.x); t >= 0; t -= gridDim.x, buf ^= 1) {
+    for (int t = RESIDENT ? int(blockIdx.x) : num_tiles - 1 - int(blockIdx.x); t >= 0; t -= RESIDENT ? num_tiles : int(gridDim.x), buf ^= 1) {
         const TileCoord tc = tile_coord(t, tiles_n);
-        uint4 v[8];
-        load_tile(A, lda, M, K, tc, warp, lane, v);
+        if (!(RESIDENT && FUSED_AMAX)) load_tile(A, lda, M, K, tc, warp, lane, v);
         float am[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -204,6 +220,9 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
         // the next iteration writes the other staging buffer; the one after that is fenced by the
         // __syncthreads() of the iteration in between
     }
+    if constexpr (FUSED_AMAX) {
+        if (threadIdx.x == 0) grid_amax_depart(ws);
+    }
 }
 
 } // namespace tkb
@@ -212,9 +231,9 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
 namespace tkb {
 
 
-template <class Arith, bool S2D, bool FUSED>
+template <class Arith, bool S2D, bool FUSED, bool RESIDENT>
 inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
-    auto kern = nvfp4_quantize_kernel<Arith, S2D, FUSED>;
+    auto kern = nvfp4_quantize_kernel<Arith, S2D, FUSED, RESIDENT>;
     const int tiles = ((a.M + QT_ROWS - 1) / QT_ROWS) * ((a.K + QT_COLS - 1) / QT_COLS);
     static int blocks_per_sm = 0;   // same for every instantiation's first call; cheap to query once each
     if (blocks_per_sm == 0) {
@@ -226,6 +245,10 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     int grid = a.sm_count * blocks_per_sm;
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
+    if (RESIDENT) {
+        if (tiles > grid) return cudaErrorInvalidConfiguration;   // caller checks nvfp4_quantize_resident_ok first
+        grid = tiles;
+    }
     const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(a.A);
     uint8_t* codes = static_cast<uint8_t*>(a.codes);
     uint8_t* sc = static_cast<uint8_t*>(a.sc);
@@ -233,16 +256,34 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
     int sc_rowmajor = a.sc_rowmajor;
     void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status, &sc_rowmajor};
-    static const bool coop = getenv("TKB_COOP") && atoi(getenv("TKB_COOP")) != 0;
-    if (FUSED && coop) return cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
-    return cudaLaunchKernel((const void*)kern, dim3(grid), dim3(Q_THREADS), params, 0, a.stream);
+    (void)params;
+    // Programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream drains;
+    // it executes griddepcontrol.wait before touching global memory.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(Q_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor);
+}
+
+// One tile per CTA with the whole grid resident (needed by the grid barrier)?
+inline bool nvfp4_quantize_resident_ok(const NvQuantArgs& a) {
+    const long long tiles = (long long)((a.M + QT_ROWS - 1) / QT_ROWS) * ((a.K + QT_COLS - 1) / QT_COLS);
+    return tiles <= (long long)a.sm_count * 2;
 }
 
 template <class Arith>
 inline cudaError_t launch_nvfp4_quantize(const NvQuantArgs& a) {
     const bool fused = a.amax_in == nullptr;
-    if (a.scale_2d) return fused ? launch_nvfp4_quantize_t<Arith, true, true>(a) : launch_nvfp4_quantize_t<Arith, true, false>(a);
-    return fused ? launch_nvfp4_quantize_t<Arith, false, true>(a) : launch_nvfp4_quantize_t<Arith, false, false>(a);
+    const bool res = fused && nvfp4_quantize_resident_ok(a);
+    if (a.scale_2d) {
+        if (res) return launch_nvfp4_quantize_t<Arith, true, true, true>(a);
+        return fused ? launch_nvfp4_quantize_t<Arith, true, true, false>(a) : launch_nvfp4_quantize_t<Arith, true, false, false>(a);
+    }
+    if (res) return launch_nvfp4_quantize_t<Arith, false, true, true>(a);
+    return fused ? launch_nvfp4_quantize_t<Arith, false, true, false>(a) : launch_nvfp4_quantize_t<Arith, false, false, false>(a);
 }
 
 } // namespace tkb

@@ -49,13 +49,16 @@ class TKParallelTensor:
         ptr = C.c_void_p()
         L.check(L.lib().tkb_dev_alloc(max(self.nbytes, 16), C.byref(ptr)))
         self._ptr = ptr.value
-        self.data_ = torch.as_tensor(_RawCuda(self._ptr, self.nbytes), device=torch.device("cuda", torch.cuda.current_device())) \
-            .view(dtype).view(self.shape_)
+        self.data_ = self._view()
         self._peer = [None] * self.local_world_size_
         self._peer[self.local_rank_] = self._ptr
         self._opened = []
         if self.local_world_size_ > 1:
             self._exchange()
+
+    def _view(self) -> torch.Tensor:
+        raw = torch.as_tensor(_RawCuda(self._ptr, self.nbytes), device=torch.device("cuda", torch.cuda.current_device()))
+        return raw.view(self.dtype_).view(self.shape_)
 
     def _exchange(self) -> None:
         handle = (C.c_ubyte * 64)()
@@ -100,9 +103,9 @@ class AllGatherMatmulNVFP4:
     """Column-parallel linear layer with NVFP4 operands: every rank owns M/world activation rows (bf16) and
     N_local = N/world weight rows (already NVFP4).  One call =
         amax(X_local) -> all-reduce(max) -> quantize into this rank's slice of the gathered buffers ->
-        signal peers -> fused kernel (a few CTAs pull the other slices over NVLink, the rest multiply).
-    Two buffer sets alternate between calls; a slice is overwritten only after every peer has acknowledged
-    that it finished reading the previous contents.
+        fused kernel (a few CTAs push the slice into every peer's buffers over NVLink, the rest multiply).
+    Two buffer sets alternate between calls; a set is written again only after every peer has acknowledged
+    that its kernel finished with the previous contents.
     """
 
     def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None):
@@ -117,10 +120,10 @@ class AllGatherMatmulNVFP4:
         mk = lambda shape, dt: TKParallelTensor(shape, dt, local_rank, local_world_size, False, group)
         self.codes = [mk((M, K // 2), torch.uint8) for _ in range(2)]
         self.scales = [mk((M // 128, K // 64, 512), torch.uint8) for _ in range(2)]
-        # flags[0:world] = ready epochs, flags[world:2*world] = done (acknowledge) epochs
-        self.flags = mk((2 * local_world_size,), torch.int32)
+        # flags[0:world] = done (acknowledge) epochs; arrived[set] = arrival epochs of the row blocks, written by their owners
+        self.flags = mk((local_world_size,), torch.int32)
         dev = self.flags.data_.device
-        self.arrived = [torch.zeros(M // 256, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.arrived = [mk((M // 256,), torch.int32) for _ in range(2)]
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
         self.epoch = 0
@@ -138,25 +141,23 @@ class AllGatherMatmulNVFP4:
         self.epoch += 1
         e, b, r, w, s = self.epoch, self.epoch % 2, self.rank, self.world, _stream()
         codes, scales = self.codes[b], self.scales[b]
-        # my slice of set b was last filled at epoch e-2: wait until every peer acknowledged reading it
+        # set b was last used at epoch e-2: every peer's kernel of that epoch must be finished before its buffers are written again
         if w > 1 and e > 2:
-            L.check(lib.tkb_wait_flags(self.flags.data_.data_ptr() + 4 * w, w, r, e - 2, s))
+            L.check(lib.tkb_wait_flags(self.flags.data_.data_ptr(), w, r, e - 2, s))
         ops.absmax_bf16(X_local, self.amax)
         if w > 1:
             dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
         my_codes = codes.data_[r * self.rows:(r + 1) * self.rows]
         my_scales = scales.data_[r * self.rows // 128:(r + 1) * self.rows // 128]
         ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, amax=self.amax)
-        if w > 1:
-            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))
         L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), self.sg.data_ptr(), W.data_ptr(), W_sc.data_ptr(),
-                                      W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.flags.data_.data_ptr(),
-                                      self.arrived[b].data_ptr(), e, self.num_comm_sms, s))
+                                      W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.arrived[b].peer_ptr_array(),
+                                      e, self.num_comm_sms, s))
         if w > 1:
-            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, w + r, e, 0, s))
+            L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))      # my kernel of epoch e is done
 
     def close(self) -> None:
-        for t in self.codes + self.scales + [self.flags]:
+        for t in self.codes + self.scales + self.arrived + [self.flags]:
             t.close()
 
 
