@@ -39,9 +39,10 @@ enum {
 
 /* NVFP4 quantizer arithmetic (see tkb_nvfp4_quantize) */
 enum {
-    TKB_NVFP4_SPEC = 0,        /* the reference's torch specification, IEEE fp32 (default) */
+    TKB_NVFP4_SPEC = 0,        /* the reference's torch specification (test_quantize.py:9-52), IEEE fp32; reproducible on a CPU */
     TKB_NVFP4_KERNEL_IEEE = 1, /* the reference kernel's operation order, IEEE fp32 */
-    TKB_NVFP4_KERNEL_FAST = 2  /* the reference kernel's operation order AND its --use_fast_math build */
+    TKB_NVFP4_KERNEL_FAST = 2  /* the reference kernel's operation order AND its --use_fast_math build: bit-identical to the
+                                  reference kernel's output on a B200 (what the Python layer uses by default) */
 };
 
 /* GEMM tile configuration override for tkb_*_gemm_ex (0 = library default) */

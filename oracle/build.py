@@ -82,6 +82,41 @@ def build_ref() -> str | None:
     return out
 
 
+def build_ref_gpu(which: str = "nvfp4") -> str | None:
+    """Compile the reference's own GPU kernels (nvfp4_b200 or mxfp8_b200: GEMM + quantizer) as the PyTorch extension the
+    reference's Makefile describes (kernels/common.mk `CONFIG := pytorch`, kernels/gemm/<dir>/Makefile), straight from the
+    reference tree with one nvcc command.  Output: oracle/_ref/tk_<which>/_C<ext>.so (git-ignored).  Used on the GPU box to
+    compare quantizer outputs bit-for-bit with the reference kernel and to time the reference beside this library.
+    Single-GPU use only: the reference kernels issue TMA loads with cluster multicast."""
+    import sysconfig
+    srcdir = os.path.join(REFERENCE, "kernels", "gemm", f"{which}_b200")
+    src = os.path.join(srcdir, f"{which}_b200_gemm.cu")
+    outdir = os.path.join(REF_OUT, f"tk_{which}")
+    out = os.path.join(outdir, "_C" + sysconfig.get_config_var("EXT_SUFFIX"))
+    if not os.path.exists(src):
+        return out if os.path.exists(out) else None
+    if _newer(out, [src, __file__]):
+        return out
+    os.makedirs(outdir, exist_ok=True)
+    from torch.utils.cpp_extension import include_paths, library_paths
+    import pybind11
+    cmd = ["nvcc", "-std=c++20", "-O3", "--use_fast_math", "--expt-extended-lambda", "--expt-relaxed-constexpr",
+           "-forward-unknown-to-host-compiler", "-Xcompiler=-Wno-psabi", "-Xcompiler=-fno-strict-aliasing", "-DNDEBUG", "-lineinfo",
+           "-DKITTENS_BLACKWELL", "-gencode", "arch=compute_100a,code=sm_100a", "-DTORCH_COMPILE", "-shared", "-fPIC",
+           "-diag-suppress", "3189", "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__",
+           "-D__CUDA_NO_BFLOAT16_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           "-DTORCH_EXTENSION_NAME=_C", "-I", os.path.join(REFERENCE, "include"), "-I", os.path.join(REFERENCE, "prototype"),
+           "-I", sysconfig.get_path("include"), "-I", pybind11.get_include()]
+    for pth in include_paths():
+        cmd += ["-I", pth]
+    for pth in library_paths() + [os.path.join(CUDA_HOME, "lib64", "stubs")]:
+        cmd += ["-L", pth]
+    cmd += ["-ltorch_python", "-ltorch_cuda", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-lc10", "-lcuda", "-lcudart_static", "-lrt",
+            "-lpthread", "-ldl", src, "-o", out]
+    _run(cmd)
+    return out
+
+
 def build_all() -> dict:
     return {"oracle": build_oracle(), "nvhost": build_nv_codecs(), "ref": build_ref()}
 

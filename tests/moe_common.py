@@ -18,6 +18,7 @@ def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=
     from thunderkittens_b200 import parallel, _lib
     Tl, El = T // world, E // world
     layer = parallel.MoELayerNVFP4(T, H, I, E, top_k, rank, world, num_comm_sms=comm_sms)
+    layer.arithmetic = _lib.NVFP4_SPEC          # the CPU-reproducible quantizer arithmetic
     ok = True
     for it in range(iters):
         X, logits, W = make_problem(T, H, I, E, seed=100 + it)

@@ -31,7 +31,7 @@ def _run(cuda, X, wq, config="skinny"):
     xc = torch.empty(M, K // 2, dtype=torch.uint8, device=cuda)
     xsc = torch.empty(1, K // 64, 512, dtype=torch.uint8, device=cuda)
     xsg = torch.empty(1, dtype=torch.float32, device=cuda)
-    ops.nvfp4_quantize(Xd, xc, xsc, xsg, False)          # activations quantized on the fly
+    ops.nvfp4_quantize(Xd, xc, xsc, xsg, False, "spec")          # activations quantized on the fly
     D = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda)
     ops.nvfp4_gemm(xc, xsc, xsg, to_dev_u8(wc, cuda), to_dev_u8(wsc, cuda), torch.from_numpy(wsg).to(cuda), D, config)
     torch.cuda.synchronize()

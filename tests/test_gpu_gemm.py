@@ -108,7 +108,7 @@ def test_full_size_gemm_properties(cuda, lib):
         codes = torch.empty(X.shape[0], K // 2, dtype=torch.uint8, device=cuda)
         sc = torch.empty(X.shape[0] // 128, K // 64, 512, dtype=torch.uint8, device=cuda)
         sg = torch.empty(1, dtype=torch.float32, device=cuda)
-        ops.nvfp4_quantize(X, codes, sc, sg, False)
+        ops.nvfp4_quantize(X, codes, sc, sg, False, "spec")
         return codes, sc, sg
     ac, asc, asg = q(A)
     bc, bsc, bsg = q(B)

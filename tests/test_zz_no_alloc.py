@@ -27,7 +27,7 @@ def _quantized_activation(cuda, M, K, seed):
     xc = torch.empty(M, K // 2, dtype=torch.uint8, device=cuda)
     xs = torch.empty(1, K // 64, 512, dtype=torch.uint8, device=cuda)
     xg = torch.empty(1, dtype=torch.float32, device=cuda)
-    ops.nvfp4_quantize(X, xc, xs, xg, False)
+    ops.nvfp4_quantize(X, xc, xs, xg, False, "spec")
     return xc, xs, xg
 
 

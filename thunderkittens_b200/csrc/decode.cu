@@ -306,6 +306,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     }
                 }
             }
+            if (head && !complete) {
+                // every epilogue thread has read the partial tiles: put the contributors' flags back to 0 so that a
+                // later launch that carries the same epoch (a replayed CUDA graph) does not mistake them for fresh
+                epi_barrier();
+                if (threadIdx.x == 64)
+                    for (int h = contrib_lo; h < contrib_hi; h++) st_release_gpu(p.flags + h, 0u);
+            }
             if (!head) {
                 // publish the partial tile: all four epilogue warps have stored, then one release
                 epi_barrier();

@@ -129,7 +129,10 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
 template <int RING, int PIECE>
 __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
                         const WaitCtx& wc) {
-    // single thread; bars[0..RING) are "piece landed in shared memory" barriers
+    // single thread; bars[0..RING) are "piece landed in shared memory" barriers.  Up to AHEAD loads are in flight in
+    // front of the store cursor and up to RING - AHEAD stores may still be reading their slots behind it.
+    constexpr int AHEAD = RING / 2;
+    static_assert(RING >= 4, "ring too small");
     const int units = (ag.world - 1) * ag.blocks_per_rank;
     uint32_t issued = 0, stored = 0;         // piece counters over the whole kernel (ring position / phase)
     for (int u = comm_idx; u < units; u += ag.comm_ctas) {
@@ -145,13 +148,17 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
             const size_t n_pieces = (len[span] + PIECE - 1) / PIECE;
             size_t next_load = 0;
             for (size_t i = 0; i < n_pieces; i++) {
-                while (next_load < n_pieces && issued - stored < RING) {
-                    const uint32_t slot = issued % RING;
-                    const size_t o = next_load * PIECE;
-                    const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
-                    mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
-                    bulk_load(smem + slot * PIECE, sbase[span] + off[span] + o, bytes, smem_u32(&bars[slot]));
-                    issued++; next_load++;
+                if (next_load < n_pieces && issued - stored < AHEAD) {
+                    // slots about to be refilled were last read by stores at least RING - AHEAD groups ago
+                    tma_store_wait_read<RING - AHEAD - 1>();
+                    while (next_load < n_pieces && issued - stored < AHEAD) {
+                        const uint32_t slot = issued % RING;
+                        const size_t o = next_load * PIECE;
+                        const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
+                        mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
+                        bulk_load(smem + slot * PIECE, sbase[span] + off[span] + o, bytes, smem_u32(&bars[slot]));
+                        issued++; next_load++;
+                    }
                 }
                 const uint32_t slot = stored % RING;
                 if (!mbar_wait(wc, smem_u32(&bars[slot]), (stored / RING) & 1)) return;
@@ -159,7 +166,6 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
                 const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
                 bulk_store(dbase[span] + off[span] + o, smem + slot * PIECE, bytes);
                 tma_store_commit();
-                tma_store_wait_read<0>();    // the slot may be refilled once the store has read it
                 stored++;
             }
         }
@@ -286,7 +292,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __shared__ __align__(8) uint64_t bar_tmem_empty;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : 1];   // comm CTAs of the MoE mode
+    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : (MODE == MODE_AG ? 10 : 1)];   // comm CTAs of the MoE / all-gather modes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0;
@@ -349,9 +355,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (is_comm) {
             if (threadIdx.x == 0) {
                 // reuse the (idle) "full" barriers of this CTA as piece barriers and the operand ring as staging
-                constexpr int PIECE = 32768;
-                constexpr int RING = (C::STAGES * C::STAGE_BYTES) / PIECE < C::STAGES ? (C::STAGES * C::STAGE_BYTES) / PIECE : C::STAGES;
-                ag_push<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_full, wc);
+                constexpr int PIECE = 16384;
+                constexpr int RING = 10;
+                static_assert(RING * PIECE <= C::STAGES * C::STAGE_BYTES, "staging ring does not fit");
+                for (int i = 0; i < RING; i++) mbar_init(smem_u32(&bar_comm[i]), 1);
+                fence_mbar_init();
+                ag_push<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_comm, wc);
             }
             __syncthreads();
             cluster_sync();      // matches the teardown barrier of the compute clusters' code path below

@@ -86,6 +86,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread until the phase completes or `ns` nanoseconds pass: a waiting
+// warp then costs no issue slots (and no power) instead of spinning.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Per-CTA abort state shared by all waits of one kernel.
 struct WaitCtx {
     volatile int* abort_flag;   // in shared memory; non-zero once any wait of this CTA gave up
@@ -97,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_sleep(bar, parity, 100000u)) return true;      // parked for up to 100 us per attempt
         if (*w.abort_flag) return false;
         if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
             *w.abort_flag = 1;

@@ -145,10 +145,18 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
 #pragma unroll
             for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
         } else {
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            // two tiles (256 bytes per thread) in flight per iteration
+            for (int tile = blockIdx.x; tile < num_tiles; tile += 2 * gridDim.x) {
+                uint4 v2[8];
+                const int tile2 = tile + gridDim.x;
                 load_tile(A, lda, M, K, tile_coord(tile, tiles_n), warp, lane, v);
+                if (tile2 < num_tiles) load_tile(A, lda, M, K, tile_coord(tile2, tiles_n), warp, lane, v2);
+                else {
 #pragma unroll
-                for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
+                    for (int i = 0; i < 8; i++) v2[i] = make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) local = fmaxf(local, fmaxf(amax8(v[i]), amax8(v2[i])));
             }
         }
         amax = grid_amax_barrier(ws, local, status);

@@ -18,8 +18,9 @@ _ARITH = {"spec": L.NVFP4_SPEC, "kernel_ieee": L.NVFP4_KERNEL_IEEE, "kernel_fast
 _CONFIG = {None: L.GEMM_DEFAULT, "default": L.GEMM_DEFAULT, "pair_n256": L.GEMM_PAIR_N256, "single_n256": L.GEMM_SINGLE_N256,
            "pair_n128": L.GEMM_PAIR_N128, "single_n128": L.GEMM_SINGLE_N128, "skinny": L.GEMM_SKINNY}
 
-#: default NVFP4 arithmetic (see include/tkb200.h)
-default_nvfp4_arithmetic = "spec"
+#: default NVFP4 arithmetic (see include/tkb200.h): the reference KERNEL's arithmetic, bit-exact with it on a B200;
+#: "spec" is the reference's torch specification (IEEE), reproducible on a CPU
+default_nvfp4_arithmetic = "kernel_fast"
 
 
 def _chk(t: torch.Tensor, name: str, dtypes, ndim=None) -> None:

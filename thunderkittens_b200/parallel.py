@@ -108,7 +108,8 @@ class AllGatherMatmulNVFP4:
     that its kernel finished with the previous contents.
     """
 
-    def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None):
+    def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None):
+        self.arithmetic = arithmetic      # NVFP4 quantizer arithmetic (None = ops.default_nvfp4_arithmetic)
         if M % (256 * local_world_size):
             raise RuntimeError("M must be a multiple of 256 * world size")
         if K % 64:
@@ -149,7 +150,7 @@ class AllGatherMatmulNVFP4:
             dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
         my_codes = codes.data_[r * self.rows:(r + 1) * self.rows]
         my_scales = scales.data_[r * self.rows // 128:(r + 1) * self.rows // 128]
-        ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, amax=self.amax)
+        ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, self.arithmetic, amax=self.amax)
         L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), self.sg.data_ptr(), W.data_ptr(), W_sc.data_ptr(),
                                       W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.arrived[b].peer_ptr_array(),
                                       e, self.num_comm_sms, s))
@@ -188,6 +189,7 @@ class MoELayerNVFP4:
         if T % w or E % w or H % 256 or I % 128:
             raise RuntimeError("need T and E divisible by world, H % 256 == 0, I % 128 == 0")
         self.T, self.H, self.I, self.E, self.top_k, self.rank, self.world, self.group = T, H, I, E, top_k, r, w, group
+        self.arithmetic = L.NVFP4_KERNEL_FAST   # NVFP4 quantizer arithmetic of the tokens (L.NVFP4_SPEC is the CPU-reproducible one)
         self.Tl, self.El = T // w, E // w
         if cap_rows is None:
             cap_rows = 2 * (T * top_k // w) + 128 * self.El
@@ -241,7 +243,7 @@ class MoELayerNVFP4:
         if w > 1:
             dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
         L.check(lib.tkb_nvfp4_quantize_rows(X_local.data_ptr(), 0, self.xq_codes[b].data_.data_ptr(), self.xq_rows[b].data_.data_ptr(),
-                                            self.sg.data_ptr(), self.amax.data_ptr(), self.Tl, self.H, L.NVFP4_SPEC, s))
+                                            self.sg.data_ptr(), self.amax.data_ptr(), self.Tl, self.H, self.arithmetic, s))
         if w > 1:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))
             # Y is rewritten below: every peer must have finished combining the previous layer call from it
