@@ -425,7 +425,7 @@ def run_ours(args) -> None:
         dt_e2e = float(t.item())
 
     extras = {}
-    if rank == 0:
+    if rank == 0 and not args.no_extra:
         extras = side_measurements(torch, ops, dev)
 
     if rank == 0:
@@ -449,7 +449,7 @@ def run_ours(args) -> None:
                     "path": "pinned host bf16 -> H2D -> tkb_mxfp8_quantize x2 -> tkb_mxfp8_gemm -> D2H"},
             "gpu_launches": args.steps, "clocks": clocks, "extra": extras,
         }
-        if world == 1:
+        if world == 1 and not args.no_extra:
             cb, _ = cpu_reference_gemm(3, 1, rows=16)
             line["cpu_baseline"] = cb
         print(json.dumps(line), flush=True)
@@ -571,6 +571,13 @@ def run_case(args) -> None:
         b = torch.empty(n, k, dtype=u8, device=dev); bsc = torch.empty((n + 127) // 128, k // 128, 512, dtype=u8, device=dev)
         ops.mxfp8_quantize(A, a, asc); ops.mxfp8_quantize(B, b, bsc)
         fn = (lambda: ops.mxfp8_gemm(a, asc, b, bsc, D, args.config)) if args.case == "mxfp8_gemm" else (lambda: ops.mxfp8_quantize(A, a, asc))
+    elif args.case == "decode":
+        # skinny-M NVFP4 GEMM: activations (m rows) against weights [n, k]
+        wc = torch.empty(n, k // 2, dtype=u8, device=dev); wsc = torch.empty((n + 127) // 128, k // 64, 512, dtype=u8, device=dev); wg = torch.empty(1, device=dev)
+        ops.nvfp4_quantize(B, wc, wsc, wg, False)
+        xc = torch.empty(m, k // 2, dtype=u8, device=dev); xs = torch.empty(1, k // 64, 512, dtype=u8, device=dev); xg = torch.empty(1, device=dev)
+        ops.nvfp4_quantize(A, xc, xs, xg, False)
+        fn = lambda: ops.nvfp4_gemm(xc, xs, xg, wc, wsc, wg, D)
     elif args.case == "bf16_gemm":
         fn = lambda: ops.bf16_gemm(A, B, D, args.config)
     else:
@@ -588,11 +595,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, help="run a single kernel only (for profiling): nvfp4_gemm, mxfp8_gemm, bf16_gemm, nvfp4_quantize, mxfp8_quantize")
+    ap.add_argument("--case", default=None, help="run a single kernel only (for profiling): nvfp4_gemm, mxfp8_gemm, bf16_gemm, nvfp4_quantize, mxfp8_quantize, decode")
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--k", type=int, default=None)
     ap.add_argument("--config", default=None)
+    ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "moe"], help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer")
     ap.add_argument("--comm-sms", type=int, default=8, help="CTAs of the tensor-parallel kernel that pull peer shards")
     args = ap.parse_args()

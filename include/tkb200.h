@@ -158,6 +158,21 @@ int tkb_signal_peers(void* const* peer_flags, int world, int rank, int index, un
  * Replaces wait / barrier_all (sync.cuh:311-327). */
 int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, void* stream);
 
+/* max over the ranks of one float per rank (the per-tensor amax of a row-sharded tensor) without a library
+ * collective: peer_slots[i] is rank i's array of `world` 64-bit slots (zero-initialised symmetric buffer), epoch a
+ * counter that grows by one per call.  About one NVLink round trip.  No counterpart in the reference, which keeps
+ * tensors whole. */
+int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned int epoch, const float* local, float* out, void* stream);
+
+/* Contiguous all-to-all over NVLink by pushes.  Replaces tk_all_to_all(output, input, barrier, scatter_axis,
+ * gather_axis) (kernels/parallel/all_to_all/all_to_all.cu:119-179) for the case where the scattered / gathered
+ * axis is the outermost one: chunk p of `in` (bytes_per_peer bytes; the same chunk for everyone if gather != 0,
+ * i.e. an all-gather) lands at offset rank * bytes_per_peer of peer p's output.  peer_counters[i] + counter_base:
+ * `world` 32-bit counters on rank i, zero-initialised; epoch grows by one per call on the same counters.  The call
+ * returns after enqueueing the pushes and a bounded wait for all incoming chunks. */
+int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer, int gather, int rank, int world, void* const* peer_counters,
+                   int counter_base, unsigned int epoch, void* stream);
+
 /* Tensor-parallel all-gather GEMM, NVFP4.  Replaces all_gather_matmul(A, B, C, barrier, num_comm_sms)
  * (kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305; the reference ships bf16 and fp8 variants only).
  *   D[M, N_local] = gather_rows(Xq)[M, K] . W_local[N_local, K]^T.

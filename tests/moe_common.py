@@ -32,7 +32,7 @@ def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=
         # ---- oracle
         experts, weights = O.moe_route(logits.numpy(), top_k)
         padded, pull, slot = O.moe_schedule(experts, E, Tl, rank * El, (rank + 1) * El)
-        g_exp = layer.experts_all.cpu().numpy()
+        g_exp = layer.experts_all.cpu().numpy()      # the gathered routing decisions of this call
         g_w = layer.weights.cpu().numpy()
         route_ok = np.array_equal(g_exp, experts) and np.allclose(g_w, weights[rank * Tl:(rank + 1) * Tl], rtol=1e-5, atol=1e-7)
         rows = pull.shape[0]

@@ -47,6 +47,8 @@ _SIGNATURES = {
     "tkb_ipc_close": ([_vp], _i),
     "tkb_signal_peers": ([C.POINTER(_vp), _i, _i, _i, C.c_uint, _i, _vp], _i),
     "tkb_wait_flags": ([_vp, _i, _i, C.c_uint, _vp], _i),
+    "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
+    "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.c_uint, _i, _vp], _i),
     "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),

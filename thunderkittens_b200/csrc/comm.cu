@@ -22,6 +22,7 @@ int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, 
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
 
 struct PeerPtrs { unsigned int* p[kMaxWorld]; };
+constexpr int kAllToAllParts = 4;      // CTAs per destination in tkb_all_to_all (part of its counter protocol)
 
 __global__ void signal_peers_kernel(PeerPtrs peers, int world, int rank, int index, unsigned int value, int include_self) {
     const int t = threadIdx.x;
@@ -46,6 +47,52 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip
             }
             __nanosleep(100);
         }
+    }
+}
+
+// Max all-reduce of one float across the ranks without a library collective: every rank stores (epoch, value
+// bits) into slot[rank] of every peer's slot array and then waits (bounded) until all of its own slots carry the
+// epoch.  About one NVLink round trip instead of a collective launch.
+struct PeerSlots { unsigned long long* p[kMaxWorld]; };
+__global__ void amax_allreduce_kernel(PeerSlots slots, int world, int rank, unsigned int epoch, const float* local, float* out, int* status) {
+    const int t = threadIdx.x;
+    float v = 0.f;
+    if (t < world) {
+        const unsigned long long mine = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(*local);
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(slots.p[t] + rank), "l"(mine) : "memory");
+        const long long t0 = clock64();
+        unsigned long long got;
+        while (true) {
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(slots.p[rank] + t) : "memory");
+            if (int(unsigned(got >> 32) - epoch) >= 0) break;
+            if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
+        }
+        v = __uint_as_float(unsigned(got & 0xffffffffu));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (t == 0) *out = v;
+}
+
+// Contiguous all-to-all by pushes: chunk p of `in` (bytes_per_peer each; the same chunk for everybody when
+// `gather` is set) goes to offset rank * bytes_per_peer of peer p's output; each CTA then bumps a counter on the
+// receiving side (system-scope release add).  blockIdx.y = destination, blockIdx.x = part of the chunk.
+struct PeerBytes { unsigned char* p[kMaxWorld]; };
+__global__ void all_to_all_push_kernel(PeerBytes out, const unsigned char* in, size_t bytes_per_peer, int gather, int rank, int world,
+                                       PeerPtrs counters, int counter_base) {
+    const int dst = blockIdx.y;
+    const unsigned char* src = in + (gather ? 0 : size_t(dst) * bytes_per_peer);
+    unsigned char* d = out.p[dst] + size_t(rank) * bytes_per_peer;
+    const size_t per = (bytes_per_peer / 16 + gridDim.x - 1) / gridDim.x;       // 16-byte vectors per CTA
+    const size_t v0 = size_t(blockIdx.x) * per, v1 = min(bytes_per_peer / 16, v0 + per);
+    for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x)
+        reinterpret_cast<uint4*>(d)[v] = __ldg(reinterpret_cast<const uint4*>(src) + v);
+    if (blockIdx.x == gridDim.x - 1)
+        for (size_t b = (bytes_per_peer / 16) * 16 + threadIdx.x; b < bytes_per_peer; b += blockDim.x) d[b] = src[b];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(counters.p[dst] + counter_base + rank), "r"(1u) : "memory");
     }
 }
 
@@ -108,6 +155,42 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
     if (!flags || count < 1 || count > 1024) return api_fail(TKB_ERR_INVALID_ARG, "wait_flags: bad arguments");
     wait_flags_kernel<<<1, ((count + 31) / 32) * 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(flags), count, skip,
                                                                                          value, status);
+    TKB_CUDA_C(cudaGetLastError());
+    return TKB_OK;
+}
+
+int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned int epoch, const float* local, float* out, void* stream) {
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    if (!peer_slots || !local || !out || world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+        return api_fail(TKB_ERR_INVALID_ARG, "amax_allreduce: bad arguments (world must be 1..%d)", kMaxWorld);
+    PeerSlots ps;
+    for (int i = 0; i < kMaxWorld; i++) ps.p[i] = i < world ? static_cast<unsigned long long*>(peer_slots[i]) : nullptr;
+    amax_allreduce_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps, world, rank, epoch, local, out, status);
+    TKB_CUDA_C(cudaGetLastError());
+    return TKB_OK;
+}
+
+int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer, int gather, int rank, int world, void* const* peer_counters,
+                   int counter_base, unsigned int epoch, void* stream) {
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    if (!peer_out || !in || !peer_counters || world < 1 || world > kMaxWorld || rank < 0 || rank >= world || bytes_per_peer == 0 || counter_base < 0)
+        return api_fail(TKB_ERR_INVALID_ARG, "all_to_all: bad arguments (world must be 1..%d)", kMaxWorld);
+    if ((reinterpret_cast<uintptr_t>(in) & 15u) || (bytes_per_peer & 15u))
+        return api_fail(TKB_ERR_BAD_ALIGNMENT, "all_to_all: input and chunk size must be 16-byte aligned");
+    PeerBytes pb; PeerPtrs pc;
+    for (int i = 0; i < kMaxWorld; i++) {
+        pb.p[i] = i < world ? static_cast<unsigned char*>(peer_out[i]) : nullptr;
+        pc.p[i] = i < world ? static_cast<unsigned int*>(peer_counters[i]) : nullptr;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int parts = kAllToAllParts;
+    all_to_all_push_kernel<<<dim3(parts, world), 256, 0, s>>>(pb, static_cast<const unsigned char*>(in), bytes_per_peer, gather, rank, world, pc,
+                                                              counter_base);
+    TKB_CUDA_C(cudaGetLastError());
+    // every sender adds `parts` to its counter per call: wait until all of them have reached epoch * parts
+    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base, world, -1, epoch * unsigned(parts), status);
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }

@@ -4,8 +4,8 @@ Mirrors the reference's Python-visible parallel API for this path:
   TKParallelTensor(shape, dtype, local_rank, local_world_size, multicast)   include/pyutils/parallel_tensor.cuh:320-336
   all_gather_matmul(A, B, C, barrier, num_comm_sms)                          kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305
 One process per GPU (torchrun); `torch.distributed` must be initialised — it carries the 64-byte CUDA IPC
-handles (the reference ships its own unix-socket broker for that) and the 4-byte amax all-reduce.  All data
-moves through kernels of libtkb200 over NVLink peer mappings; NCCL is never on the data path.
+handles (the reference ships its own unix-socket broker for that).  Everything else — data, flags, the per-tensor
+amax reduction, the gather of routing decisions — moves through kernels of libtkb200 over NVLink peer mappings.
 """
 from __future__ import annotations
 
@@ -18,7 +18,7 @@ import torch.distributed as dist
 from . import _lib as L
 from . import ops
 
-_DT_SIZE = {torch.uint8: 1, torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.int32: 4, torch.int: 4}
+_DT_SIZE = {torch.uint8: 1, torch.bfloat16: 2, torch.float16: 2, torch.float32: 4, torch.int32: 4, torch.int: 4, torch.int64: 8}
 
 
 class _RawCuda:
@@ -125,6 +125,7 @@ class AllGatherMatmulNVFP4:
         self.flags = mk((local_world_size,), torch.int32)
         dev = self.flags.data_.device
         self.arrived = [mk((M // 256,), torch.int32) for _ in range(2)]
+        self.slots = [mk((local_world_size,), torch.int64) for _ in range(2)]   # (epoch, amax bits) per rank, see tkb_amax_allreduce
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
         self.epoch = 0
@@ -147,7 +148,7 @@ class AllGatherMatmulNVFP4:
             L.check(lib.tkb_wait_flags(self.flags.data_.data_ptr(), w, r, e - 2, s))
         ops.absmax_bf16(X_local, self.amax)
         if w > 1:
-            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
+            L.check(lib.tkb_amax_allreduce(self.slots[b].peer_ptr_array(), w, r, e, self.amax.data_ptr(), self.amax.data_ptr(), s))
         my_codes = codes.data_[r * self.rows:(r + 1) * self.rows]
         my_scales = scales.data_[r * self.rows // 128:(r + 1) * self.rows // 128]
         ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, self.arithmetic, amax=self.amax)
@@ -158,7 +159,7 @@ class AllGatherMatmulNVFP4:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))      # my kernel of epoch e is done
 
     def close(self) -> None:
-        for t in self.codes + self.scales + self.arrived + [self.flags]:
+        for t in self.codes + self.scales + self.arrived + self.slots + [self.flags]:
             t.close()
 
 
@@ -202,13 +203,17 @@ class MoELayerNVFP4:
         self.xq_rows = [mk((self.Tl, H // 16), u8) for _ in range(2)]
         self.Y = mk((self.cap_rows, I), torch.bfloat16)
         self.flags = mk((3 * w,), i32)
+        # per parity of the call counter (a peer may run one call ahead, never two): amax all-reduce slots, everybody's
+        # chosen experts (gathered by pushes) and the arrival counters of that gather
+        self.slots = [mk((w,), torch.int64) for _ in range(2)]
+        self.experts_all_sym = [mk((T, top_k), i32) for _ in range(2)]
+        self.counters = mk((2 * w,), i32)
         dev = self.flags.data_.device
         z = lambda *shape, dt=i32: torch.zeros(*shape, dtype=dt, device=dev)
         self.codes = z(self.cap_rows, H // 2, dt=u8)
         self.scales = z(self.cap_rows // 128, H // 64, 512, dt=u8)
         self.experts_local = z(self.Tl, top_k)
         self.weights = z(self.Tl, top_k, dt=f32)
-        self.experts_all = z(T, top_k)
         self.counts, self.padded = z(E), z(E)
         self.pull_idx = z(self.cap_rows, 2)
         self.block_expert = z(self.cap_rows // 128)
@@ -229,19 +234,19 @@ class MoELayerNVFP4:
         fl = self.flags.data_.data_ptr()
         # routing of my tokens, then everybody's choices
         L.check(lib.tkb_moe_route(logits_local.data_ptr(), self.Tl, self.E, self.top_k, self.experts_local.data_ptr(), self.weights.data_ptr(), s))
-        if w > 1:
-            dist.all_gather_into_tensor(self.experts_all, self.experts_local, group=self.group)
-        else:
-            self.experts_all.copy_(self.experts_local)
+        # everything of parity b was last used at call e-2: all peers must be done with that call before it is overwritten
+        if w > 1 and e > 2:
+            L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 2, s))
+        self.experts_all = self.experts_all_sym[b].data_
+        L.check(lib.tkb_all_to_all(self.experts_all_sym[b].peer_ptr_array(), self.experts_local.data_ptr(), self.Tl * self.top_k * 4, 1, r, w,
+                                   self.counters.peer_ptr_array(), b * w, (e + 1) // 2, s))
         L.check(lib.tkb_moe_schedule(self.experts_all.data_ptr(), self.T, self.top_k, self.E, w, r, self.counts.data_ptr(), self.padded.data_ptr(),
                                      self.pull_idx.data_ptr(), self.block_expert.data_ptr(), self.num_blocks.data_ptr(),
                                      self.comb_idx.data_ptr(), self.cap_rows, s))
-        # quantize my tokens with the global amax into set b (peers finished reading its previous contents: done >= e-2)
-        if w > 1 and e > 2:
-            L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 2, s))
+        # quantize my tokens with the global amax into set b
         ops.absmax_bf16(X_local, self.amax)
         if w > 1:
-            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
+            L.check(lib.tkb_amax_allreduce(self.slots[b].peer_ptr_array(), w, r, e, self.amax.data_ptr(), self.amax.data_ptr(), s))
         L.check(lib.tkb_nvfp4_quantize_rows(X_local.data_ptr(), 0, self.xq_codes[b].data_.data_ptr(), self.xq_rows[b].data_.data_ptr(),
                                             self.sg.data_ptr(), self.amax.data_ptr(), self.Tl, self.H, self.arithmetic, s))
         if w > 1:
@@ -264,5 +269,5 @@ class MoELayerNVFP4:
         return self.out
 
     def close(self) -> None:
-        for t in self.xq_codes + self.xq_rows + [self.Y, self.flags]:
+        for t in self.xq_codes + self.xq_rows + self.slots + self.experts_all_sym + [self.Y, self.flags, self.counters]:
             t.close()
