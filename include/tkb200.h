@@ -84,11 +84,12 @@ int tkb_nvfp4_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, f
 int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M,
                                  int K, int scale_2d, int arithmetic, void* stream);
 
-/* Same arithmetic, but the block scales are written as plain rows sc_rows[M, K/16] instead of 512-byte chunks:
- * the form in which quantized rows travel between GPUs (MoE dispatch re-tiles them at the destination).
- * No counterpart in the reference, whose dispatch moves bf16 rows. */
-int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* codes, void* sc_rows, float* sg, const float* amax, int M, int K,
-                            int arithmetic, void* stream);
+/* Same arithmetic, but every row is written as one self-contained record rows[M, K/2 + K/16]: the row's K/2 code
+ * bytes followed by its K/16 scale bytes in K order.  This is the form in which quantized rows travel between GPUs
+ * (MoE dispatch re-tiles the scales into 512-byte chunks at the destination).  No counterpart in the reference,
+ * whose dispatch moves bf16 rows.  K % 256 == 0. */
+int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* sg, const float* amax, int M, int K, int arithmetic,
+                            void* stream);
 
 /* max |x| of a bf16 matrix into *amax (device float; overwritten).  Part of
  * nvfp4_quantize::absmax_kernel (nvfp4_b200_gemm.cu:360-418) exposed for sharded tensors. */
@@ -209,13 +210,13 @@ int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world,
                      int* pull_idx, int* block_expert, int* num_blocks, int* comb_idx, int cap_rows, void* stream);
 
 /* Dispatch fused with the grouped expert GEMM: Y[row, :] = Xq[src(row)] . W[expert(row)]^T for every row of this
- * rank's expert segments.  peer_codes[i] [T/world, K/2] and peer_scale_rows[i] [T/world, K/16] are rank i's
- * quantized tokens (tkb_nvfp4_quantize_rows with the all-reduced amax; X_sg is that common scale);
+ * rank's expert segments.  peer_rows[i] [T/world, K/2 + K/16] are rank i's quantized tokens
+ * (tkb_nvfp4_quantize_rows with the all-reduced amax; X_sg is that common scale);
  * codes [cap_rows, K/2] and scales [cap_rows/128, K/64, 512] are local operand buffers the kernel fills;
  * W [experts_local * I, K/2], W_sc [experts_local * I / 128, K/64, 512], W_sg[1]: the rank's stacked expert weights;
  * Y [cap_rows, I] bf16 (leading dimension ldy, 0 = I).  ready [world] / arrived [cap_rows/128]: epoch arrays.
  * comm_ctas CTAs pull rows over NVLink while the others multiply.  K % 256 == 0, I % 128 == 0. */
-int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows, const float* X_sg, void* codes, void* scales,
+int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes, void* scales,
                           const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
                           const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,
                           int I, int experts_local, int cap_rows, int rank, int world, int comm_ctas, void* stream);

@@ -50,10 +50,10 @@ _SIGNATURES = {
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.c_uint, _i, _vp], _i),
-    "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),
     "tkb_moe_schedule": ([_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
-    "tkb_moe_dispatch_gemm": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, C.c_uint,
+    "tkb_moe_dispatch_gemm": ([C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, C.c_uint,
                                _i, _i, _i, _i, _i, _i, _i, _vp], _i),
     "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),

@@ -246,8 +246,10 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
 
 static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
                                  int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0) {
+    // sc_rowmajor: codes and scales share one row of K/2 + K/16 bytes (codes first); `sc` is ignored
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
+    if (sc_rowmajor) sc = static_cast<uint8_t*>(codes) + K / 2;
     if (!A || !codes || !sc || !sg) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
     if (M < 1 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: need M >= 1 and K a positive multiple of 64 (got M=%d K=%d)", M, K);
     if (arithmetic < 0 || arithmetic > 2) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: unknown arithmetic %d", arithmetic);
@@ -255,7 +257,7 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: lda must be >= K and a multiple of 8 elements");
     if (!aligned16(A) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: buffers must be 16-byte aligned");
     NvQuantArgs a;
-    a.A = A; a.lda = lda; a.codes = codes; a.ldc = K / 2; a.sc = sc; a.sg = sg; a.amax_in = amax;
+    a.A = A; a.lda = lda; a.codes = codes; a.ldc = sc_rowmajor ? K / 2 + K / 16 : K / 2; a.ldsc = K / 2 + K / 16; a.sc = sc; a.sg = sg; a.amax_in = amax;
     a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
     a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
     a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count; a.sc_rowmajor = sc_rowmajor;
@@ -299,10 +301,10 @@ int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, v
     return nvfp4_quantize_common(A_bf16, lda, codes, sc, sg, amax, M, K, scale_2d, arithmetic, stream);
 }
 
-int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* codes, void* sc_rows, float* sg, const float* amax, int M, int K,
-                            int arithmetic, void* stream) {
+int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* sg, const float* amax, int M, int K, int arithmetic,
+                            void* stream) {
     if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_rows: null amax");
-    return nvfp4_quantize_common(A_bf16, lda, codes, sc_rows, sg, amax, M, K, 0, arithmetic, stream, 1);
+    return nvfp4_quantize_common(A_bf16, lda, rows, nullptr, sg, amax, M, K, 0, arithmetic, stream, 1);
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {

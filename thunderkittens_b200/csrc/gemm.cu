@@ -186,23 +186,26 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* map, 
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
-// One comm CTA of the MoE kernel (all 320 threads): fills its share of the 128-row blocks of the local
-// activation buffer.  Per block: the 128 (source rank, source row) pairs of the dispatch list are pulled
-// from the owners' quantized-token buffers — codes through a ring of row slots straight into the local
-// row, the 128 row-major scale rows into shared memory, where they are re-tiled into the 512-byte chunk
-// layout the tensor core wants and stored as one contiguous span.  Padding rows (-1) become zeros.
+// One comm CTA of the MoE kernel (all of its threads): fills its share of the 128-row blocks of the local
+// activation buffer.  A quantized token travels as ONE row of k_bytes of codes followed by sc_row_bytes of
+// scales.  Per block the 128 (source rank, source row) pairs of the dispatch list are pulled from the owners'
+// buffers through a ring of row slots; when a row has landed, thread 0 forwards its codes to the local operand
+// row with a bulk store and the other threads drop its scales into the 512-byte chunk layout the tensor core
+// wants, which is stored as one contiguous span at the end.  Padding rows (-1) become zeros.
 __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc_row_bytes, uint32_t smem, uint32_t smem_avail, uint64_t* bars,
                          const WaitCtx& wc) {
     extern __shared__ uint8_t smem_raw_[];
     uint8_t* sm = smem_raw_ + (smem - smem_u32(smem_raw_));
     const int num_blocks = *moe.num_blocks;
-    const int sc_block_bytes = sc_row_bytes * 128;                // one block's scales, either layout
-    uint8_t* sc_rm = sm;                                          // [128][sc_row_bytes] row-major, as pulled
-    uint8_t* sc_sw = sm + sc_block_bytes;                         // [sc_row_bytes/4][512] chunk layout, as stored
+    const int row_bytes = k_bytes + sc_row_bytes;
+    const int sc_block_bytes = sc_row_bytes * 128;
+    uint8_t* sc_sw = sm;                                          // [sc_row_bytes/4][512] chunk layout, as stored
     uint8_t* zero_row = sc_sw + sc_block_bytes;                   // k_bytes of zeros
-    const uint32_t ring0 = smem + 2 * sc_block_bytes + ((k_bytes + 127) & ~127);
-    const int ring = min(24, int((smem_avail - (ring0 - smem)) / uint32_t(k_bytes)));
+    const uint32_t ring0_off = uint32_t(sc_block_bytes + ((k_bytes + 127) & ~127));
+    const int ring = min(32, int((smem_avail - ring0_off) / uint32_t(row_bytes)));
+    const int ahead = ring - 16;                                  // loads in flight; the two batches of 8 slots behind may still be read by stores
     const int tid = threadIdx.x, nthr = blockDim.x;
+    const int groups = sc_row_bytes / 4;                          // 4 scale bytes (64 K-elements) per row per chunk
     for (int i = tid; i < k_bytes / 4; i += nthr) reinterpret_cast<uint32_t*>(zero_row)[i] = 0;
     fence_proxy_async();
     __syncthreads();
@@ -211,53 +214,50 @@ __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc
             if (pr != moe.rank && !flag_wait(wc, moe.ready + pr, moe.epoch)) break;
     }
     __syncthreads();
-    uint32_t issued = 0, stored = 0, sc_phase = 0;
-    const uint32_t sc_bar = smem_u32(&bars[0]);                   // bars[0]: scale rows landed; bars[1..]: ring slots
+    uint32_t issued = 0, done = 0;                                // rows over the whole kernel: ring position / phase
+    constexpr int BATCH = 8;                                      // rows handled between two CTA barriers
     for (int blk = comm_idx; blk < num_blocks; blk += moe.comm_ctas) {
         __syncthreads();
-        if (*wc.abort_flag) break;                                 // read by every thread right after the same barrier
+        if (*wc.abort_flag) break;                                // read by every thread right after the same barrier
         const int* idx = moe.pull_idx + size_t(blk) * 128 * 2;
-        if (tid == 0) {
-            // scale rows: one barrier for the block
-            uint32_t expect = 0;
-            for (int r = 0; r < 128; r++) if (idx[2 * r] >= 0) expect += sc_row_bytes;
-            mbar_arrive_expect_tx(sc_bar, expect);
-            for (int r = 0; r < 128; r++) {
-                const int src = idx[2 * r], row = idx[2 * r + 1];
-                if (src >= 0) bulk_load(smem_u32(sc_rm + r * sc_row_bytes), moe.peer_scales[src] + size_t(row) * sc_row_bytes, sc_row_bytes, sc_bar);
-            }
-            // code rows through the ring
-            int next = 0;
-            for (int r = 0; r < 128; r++) {
-                while (next < 128 && int(issued - stored) < ring) {
-                    const int src = idx[2 * next], row = idx[2 * next + 1];
-                    const uint32_t slot = issued % ring;
+        int next = 0;
+        for (int r0 = 0; r0 < 128; r0 += BATCH) {
+            // Top up the loads, one batch at a time; within a batch every row is issued by its own lane (a single
+            // thread cannot issue small bulk copies fast enough).  Slots of batches older than the previous one are
+            // free: their stores were waited for below.
+            while (next < 128 && int(issued - done) < ahead) {
+                if (tid >= 32 && tid < 32 + BATCH) {
+                    const int rr = next + (tid - 32);
+                    const int src = idx[2 * rr], row = idx[2 * rr + 1];
+                    const uint32_t slot = (issued + (tid - 32)) % ring;
                     if (src >= 0) {
-                        mbar_arrive_expect_tx(smem_u32(&bars[1 + slot]), k_bytes);
-                        bulk_load(ring0 + slot * k_bytes, moe.peer_codes[src] + size_t(row) * k_bytes, k_bytes, smem_u32(&bars[1 + slot]));
+                        mbar_arrive_expect_tx(smem_u32(&bars[slot]), row_bytes);
+                        bulk_load(smem + ring0_off + slot * row_bytes, moe.peer_rows[src] + size_t(row) * row_bytes, row_bytes, smem_u32(&bars[slot]));
                     } else {
-                        mbar_arrive(smem_u32(&bars[1 + slot]));      // keeps the slot's phase in step
+                        mbar_arrive(smem_u32(&bars[slot]));        // keeps the slot's phase in step
                     }
-                    issued++; next++;
                 }
-                const uint32_t slot = stored % ring;
-                if (!mbar_wait(wc, smem_u32(&bars[1 + slot]), (stored / ring) & 1)) break;
-                uint8_t* dst = moe.codes + (size_t(blk) * 128 + r) * k_bytes;
-                bulk_store(dst, idx[2 * r] >= 0 ? ring0 + slot * k_bytes : smem_u32(zero_row), k_bytes);
-                tma_store_commit();
-                tma_store_wait_read<0>();
-                stored++;
+                issued += BATCH; next += BATCH;
             }
+            for (int i = 0; i < BATCH; i++) mbar_wait(wc, smem_u32(&bars[(done + i) % ring]), ((done + i) / ring) & 1);
+            if (tid < BATCH) {
+                // one lane per row forwards the codes; its previous store (one batch ago) has long been read
+                const int r = r0 + tid;
+                const uint32_t slot = (done + tid) % ring;
+                tma_store_wait_read<0>();
+                bulk_store(moe.codes + (size_t(blk) * 128 + r) * k_bytes, idx[2 * r] >= 0 ? smem + ring0_off + slot * row_bytes : smem_u32(zero_row), k_bytes);
+                tma_store_commit();
+            }
+            for (int i = tid; i < BATCH * groups; i += nthr) {
+                const int rr = i / groups, kc = i % groups, r = r0 + rr;
+                const uint32_t slot = (done + rr) % ring;
+                const uint32_t v = idx[2 * r] >= 0 ? *reinterpret_cast<const uint32_t*>(sm + ring0_off + slot * row_bytes + k_bytes + kc * 4) : 0u;
+                *reinterpret_cast<uint32_t*>(sc_sw + kc * 512 + (r & 31) * 16 + (r >> 5) * 4) = v;
+            }
+            done += BATCH;
+            __syncthreads();       // scale bytes of the batch are read; code stores of the batch BEFORE it were waited for above
         }
-        // everybody: wait for the scale rows, re-tile them
-        mbar_wait(wc, sc_bar, sc_phase);
-        sc_phase ^= 1;
-        const int groups = sc_row_bytes / 4;                       // 4 scale bytes (64 K-elements) per row per chunk
-        for (int i = tid; i < 128 * groups; i += nthr) {
-            const int r = i / groups, kc = i % groups;
-            const uint32_t v = idx[2 * r] >= 0 ? *reinterpret_cast<const uint32_t*>(sc_rm + r * sc_row_bytes + kc * 4) : 0u;
-            *reinterpret_cast<uint32_t*>(sc_sw + kc * 512 + (r & 31) * 16 + (r >> 5) * 4) = v;
-        }
+        if (tid < BATCH) tma_store_wait<0>();                      // this block's code rows are in local memory
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) {
@@ -267,7 +267,6 @@ __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc
             __threadfence();
             st_release_gpu_u32(moe.arrived + blk, moe.epoch);
         }
-        __syncthreads();                                           // sc_rm / sc_sw are reused by the next block
     }
 }
 
@@ -346,7 +345,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 fence_mbar_init();
             }
             __syncthreads();
-            moe_pull(moe, int(blockIdx.x), p.K / 2, p.K / 16, smem_base, C::STAGES * C::STAGE_BYTES + C::EPI_BYTES, bar_comm, wc);
+            moe_pull(moe, int(blockIdx.x), p.K / 2, p.K / 16, smem_base, C::STAGES * C::STAGE_BYTES + C::EPI_BYTES, bar_comm, wc);   // needs 1 + K/64 <= blockDim.x
             __syncthreads();
             return;
         }

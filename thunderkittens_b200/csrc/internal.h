@@ -33,8 +33,7 @@ struct AgParams {
 
 // MoE mode: dispatch (pull of routed token rows from their home ranks) fused with the grouped expert GEMM.
 struct MoeParams {
-    const uint8_t* peer_codes[kMaxWorld];    // every rank's quantized tokens [tokens_per_rank, K/2]
-    const uint8_t* peer_scales[kMaxWorld];   // every rank's ROW-MAJOR token scales [tokens_per_rank, K/16]
+    const uint8_t* peer_rows[kMaxWorld];     // every rank's quantized tokens [tokens_per_rank, K/2 + K/16]: codes, then that row's scales
     uint8_t* codes; uint8_t* scales;         // local gathered activations [cap_rows, K/2], chunked scales [cap_rows/128, K/64, 512]
     const int* pull_idx;                     // [cap_rows][2] (source rank, source row), -1 = padding
     const int* block_expert;                 // [cap_rows/128] local expert of each 128-row block

@@ -7,8 +7,8 @@
 //   * everything data-dependent stays on the device: expert counts, padded segment sizes, the pull list, the
 //     number of row blocks and the combine map are produced by two small kernels, so a layer needs no host
 //     synchronisation;
-//   * rows travel as NVFP4 codes + row-major e4m3 scales (4032 bytes per 7168-wide token instead of 14336) and
-//     are pulled straight into the grouped GEMM's operand buffers by a few CTAs of the GEMM kernel;
+//   * rows travel as NVFP4 codes followed by their e4m3 scales (one 4032-byte row per 7168-wide token instead of
+//     14336 bytes of bf16) and are pulled straight into the grouped GEMM's operand buffers by some CTAs of the GEMM kernel;
 //   * within an expert segment rows are in ascending global token order (the reference walks source ranks as a
 //     ring starting at the local rank); segments are padded to 128 rows with (-1, -1) entries as in the reference;
 //   * combine (no counterpart in the reference): out[t] = bf16(sum_j w[t,j] * Y[row(t,j)]), fp32 accumulation in
@@ -239,19 +239,20 @@ int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world,
     return TKB_OK;
 }
 
-int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows, const float* X_sg, void* codes, void* scales,
+int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes, void* scales,
                           const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
                           const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,
                           int I, int experts_local, int cap_rows, int rank, int world, int comm_ctas, void* stream) {
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
-    if (!peer_codes || !peer_scale_rows || !X_sg || !codes || !scales || !W || !W_sc || !W_sg || !Y || !pull_idx || !block_expert ||
+    if (!peer_rows || !X_sg || !codes || !scales || !W || !W_sc || !W_sg || !Y || !pull_idx || !block_expert ||
         !num_blocks || !ready || !arrived)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: bad rank/world");
     if (K % 256 || I % 128 || cap_rows % 128 || cap_rows < 128) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
-    // dispatch staging per comm CTA: two copies of a block's scales (128 x K/16 bytes each), a zero row and >= 4 code-row slots
-    if (2 * 128 * (K / 16) + 5 * (K / 2) + 256 > 190 * 1024) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
+    // dispatch staging per comm CTA: a block's scales (128 x K/16 bytes), a zero row and at least 12 row slots; one thread per 64 K-elements
+    if (128 * (K / 16) + K / 2 + 128 + 12 * (K / 2 + K / 16) > 190 * 1024 || K / 64 + 1 > 320)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
     if (comm_ctas < 1 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [1, %d]", sm / 2);
     if (ldy == 0) ldy = I;
     GemmArgs g;
@@ -268,10 +269,7 @@ int tkb_moe_dispatch_gemm(void* const* peer_codes, void* const* peer_scale_rows,
     g.stream = static_cast<cudaStream_t>(stream);
     g.mode = MODE_MOE;
     MoeParams& m = g.comm.moe;
-    for (int i = 0; i < world; i++) {
-        m.peer_codes[i] = static_cast<const uint8_t*>(peer_codes[i]);
-        m.peer_scales[i] = static_cast<const uint8_t*>(peer_scale_rows[i]);
-    }
+    for (int i = 0; i < world; i++) m.peer_rows[i] = static_cast<const uint8_t*>(peer_rows[i]);
     m.codes = static_cast<uint8_t*>(codes); m.scales = static_cast<uint8_t*>(scales);
     m.pull_idx = pull_idx; m.block_expert = block_expert; m.num_blocks = num_blocks;
     m.ready = static_cast<const unsigned int*>(ready); m.arrived = static_cast<unsigned int*>(arrived);

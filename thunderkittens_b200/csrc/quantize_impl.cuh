@@ -125,7 +125,7 @@ template <class Arith, bool SCALE_2D, bool FUSED_AMAX, bool RESIDENT>
 __global__ void __launch_bounds__(Q_THREADS)
 nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
-                      int M, int K, int* status, int sc_rowmajor) {
+                      int M, int K, int* status, int sc_rowmajor, int64_t ldsc) {
     __shared__ __align__(16) uint8_t s_sc[2][2][512];   // [double buffer][chunk][byte]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
@@ -215,7 +215,7 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
             // plain [M, K/16] scale rows (used where rows travel individually, e.g. MoE dispatch)
             const int r = threadIdx.x >> 1, half = threadIdx.x & 1;     // 4 scale bytes (64 columns) per thread
             if (tc.row0 + r < M && tc.col0 + half * 64 < K)
-                *reinterpret_cast<uint32_t*>(sc + int64_t(tc.row0 + r) * (K / 16) + tc.col0 / 16 + half * 4) =
+                *reinterpret_cast<uint32_t*>(sc + int64_t(tc.row0 + r) * ldsc + tc.col0 / 16 + half * 4) =
                     reinterpret_cast<const uint32_t*>(&s_sc[buf][0][0])[r * 2 + half];
         } else {
             const int c = threadIdx.x >> 7, word = threadIdx.x & 127;
@@ -263,7 +263,8 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     int64_t lda = a.lda, ldc = a.ldc;
     float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
     int sc_rowmajor = a.sc_rowmajor;
-    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status, &sc_rowmajor};
+    int64_t ldsc = a.ldsc;
+    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status, &sc_rowmajor, &ldsc};
     (void)params;
     // Programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream drains;
     // it executes griddepcontrol.wait before touching global memory.
@@ -273,7 +274,7 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor);
+    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor, ldsc);
 }
 
 // One tile per CTA with the whole grid resident (needed by the grid barrier)?

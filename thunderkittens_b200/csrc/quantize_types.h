@@ -15,7 +15,8 @@ struct QuantWork {            // one slot of library-owned scratch per in-flight
 struct NvQuantArgs {
     const void* A; int64_t lda; void* codes; int64_t ldc; void* sc; float* sg; const float* amax_in; QuantWork* ws;
     int M, K, scale_2d; int* status; cudaStream_t stream; int sm_count;
-    int sc_rowmajor;   // 0: 512-byte chunk layout (GEMM operand); 1: plain [M, K/16] rows
+    int sc_rowmajor;   // 0: 512-byte chunk layout (GEMM operand); 1: plain scale rows of K/16 bytes, ldsc bytes apart
+    int64_t ldsc;
 };
 
 } // namespace tkb

@@ -199,8 +199,7 @@ class MoELayerNVFP4:
         mk = lambda shape, dt: TKParallelTensor(shape, dt, r, w, False, group)
         u8, i32, f32 = torch.uint8, torch.int32, torch.float32
         # symmetric: quantized tokens (two sets), expert outputs, flags [ready(w), y_ready(w), done(w)]
-        self.xq_codes = [mk((self.Tl, H // 2), u8) for _ in range(2)]
-        self.xq_rows = [mk((self.Tl, H // 16), u8) for _ in range(2)]
+        self.xq_rows = [mk((self.Tl, H // 2 + H // 16), u8) for _ in range(2)]     # per token: codes, then its scales
         self.Y = mk((self.cap_rows, I), torch.bfloat16)
         self.flags = mk((3 * w,), i32)
         # per parity of the call counter (a peer may run one call ahead, never two): amax all-reduce slots, everybody's
@@ -247,14 +246,14 @@ class MoELayerNVFP4:
         ops.absmax_bf16(X_local, self.amax)
         if w > 1:
             L.check(lib.tkb_amax_allreduce(self.slots[b].peer_ptr_array(), w, r, e, self.amax.data_ptr(), self.amax.data_ptr(), s))
-        L.check(lib.tkb_nvfp4_quantize_rows(X_local.data_ptr(), 0, self.xq_codes[b].data_.data_ptr(), self.xq_rows[b].data_.data_ptr(),
-                                            self.sg.data_ptr(), self.amax.data_ptr(), self.Tl, self.H, self.arithmetic, s))
+        L.check(lib.tkb_nvfp4_quantize_rows(X_local.data_ptr(), 0, self.xq_rows[b].data_.data_ptr(), self.sg.data_ptr(), self.amax.data_ptr(),
+                                            self.Tl, self.H, self.arithmetic, s))
         if w > 1:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))
             # Y is rewritten below: every peer must have finished combining the previous layer call from it
             if e > 1:
                 L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 1, s))
-        L.check(lib.tkb_moe_dispatch_gemm(self.xq_codes[b].peer_ptr_array(), self.xq_rows[b].peer_ptr_array(), self.sg.data_ptr(),
+        L.check(lib.tkb_moe_dispatch_gemm(self.xq_rows[b].peer_ptr_array(), self.sg.data_ptr(),
                                           self.codes.data_ptr(), self.scales.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
                                           self.Y.data_.data_ptr(), 0, self.pull_idx.data_ptr(), self.block_expert.data_ptr(),
                                           self.num_blocks.data_ptr(), fl, self.arrived.data_ptr(), e, self.H, self.I, self.El, self.cap_rows,
@@ -269,5 +268,5 @@ class MoELayerNVFP4:
         return self.out
 
     def close(self) -> None:
-        for t in self.xq_codes + self.xq_rows + self.slots + self.experts_all_sym + [self.Y, self.flags, self.counters]:
+        for t in self.xq_rows + self.slots + self.experts_all_sym + [self.Y, self.flags, self.counters]:
             t.close()
