@@ -188,6 +188,24 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
                       unsigned int epoch, int comm_ctas, void* stream);
 
+/* One call for a whole step of the column-parallel layer (amax of the local rows -> NVLink max all-reduce -> quantize
+ * into this rank's slice -> tkb_ag_gemm_nvfp4 -> acknowledge), so that the host spends one library call per step
+ * instead of six.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index [set][rank]);
+ * the set used is epoch % 2, and epoch must grow by one per call, starting at 1, on every rank alike.
+ * Host-side convenience over the entry points above; no counterpart in the reference. */
+typedef struct tkb_ag_state {
+    int rank, world, M, K;
+    void* codes[2][8];      /* [M, K/2] gathered codes */
+    void* scales[2][8];     /* [M/128, K/64, 512] gathered scales */
+    void* arrived[2][8];    /* [M/256] arrival epochs */
+    void* slots[2][8];      /* [world] 64-bit amax all-reduce slots */
+    void* done[8];          /* [world] 32-bit "my kernel of epoch e is finished" flags */
+    float* amax;            /* device scratch, 1 float */
+    float* sg;              /* device, 1 float: the per-tensor scale of the gathered activations */
+} tkb_ag_state;
+int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local_bf16, const void* W, const void* W_sc,
+                        const float* W_sg, void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream);
+
 /* ---- MoE layer -----------------------------------------------------------------------------------
  * Replaces moe_dispatch_gemm(pre_tokens, post_tokens, weights, outputs, padded_tokens_per_expert,
  * pull_dispatch_indices, barrier, num_comm_sms, num_padded_local_tokens)

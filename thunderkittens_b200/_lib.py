@@ -49,6 +49,7 @@ _SIGNATURES = {
     "tkb_wait_flags": ([_vp, _i, _i, C.c_uint, _vp], _i),
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
+    "tkb_ag_linear_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.c_uint, _i, _vp], _i),
     "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),
@@ -58,6 +59,13 @@ _SIGNATURES = {
     "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
+
+class AgState(C.Structure):
+    """Mirror of tkb_ag_state (include/tkb200.h)."""
+    _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("K", _i),
+                ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
+                ("done", _vp * 8), ("amax", _vp), ("sg", _vp)]
+
 
 _lib = None
 

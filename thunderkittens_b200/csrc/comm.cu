@@ -228,4 +228,26 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     return TKB_OK;
 }
 
+int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local, const void* W, const void* W_sc, const float* W_sg,
+                        void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream) {
+    if (!st || !X_local || epoch == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: null state/input or epoch 0");
+    const int w = st->world, r = st->rank, b = int(epoch % 2u);
+    if (w < 1 || w > kMaxWorld || r < 0 || r >= w || st->M % (256 * w)) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: bad world / rank / M");
+    const int rows = st->M / w;
+    // set b was last used at epoch - 2: every peer's kernel of that epoch must be finished before it is written again
+    if (w > 1 && epoch > 2)
+        if (int e = tkb_wait_flags(st->done[r], w, r, epoch - 2, stream)) return e;
+    if (int e = tkb_absmax_bf16(X_local, 0, rows, st->K, st->amax, stream)) return e;
+    if (w > 1)
+        if (int e = tkb_amax_allreduce(st->slots[b], w, r, epoch, st->amax, st->amax, stream)) return e;
+    uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
+    uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
+    if (int e = tkb_nvfp4_quantize_with_amax(X_local, 0, my_codes, my_scales, st->sg, st->amax, rows, st->K, 0, arithmetic, stream)) return e;
+    if (int e = tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b], epoch,
+                                  w > 1 ? comm_ctas : 0, stream)) return e;
+    if (w > 1)
+        if (int e = tkb_signal_peers(st->done, w, r, r, epoch, 0, stream)) return e;
+    return TKB_OK;
+}
+
 } // extern "C"

@@ -338,6 +338,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     WaitCtx wc{&s_abort, p.status};
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // successors launched with programmatic serialization wait on their own
 
+    if constexpr (MOE || AG) {
+        if (is_comm) asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
     if constexpr (MOE) {
         if (is_comm) {
             if (threadIdx.x == 0) {
@@ -373,6 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             long long waited = 0;
+            asm volatile("griddepcontrol.wait;" ::: "memory");      // operands may come from the previous kernel in the stream
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
@@ -492,6 +496,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int ew = warp - 2;
         const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
         const int col_base = (ew >> 2) * C::COLS_PER_EPI_WARP;
+        asm volatile("griddepcontrol.wait;" ::: "memory");          // D may still be read, and the scales written, by the previous kernel
         float alpha = 1.0f;
         if constexpr (KIND == KIND_NVFP4) alpha = __fmul_rn(*p.sgA, *p.sgB);
         const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
@@ -509,21 +514,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             wait_tf += t1 - t0;
             tile_phase ^= 1;
             tc_fence_after();
-            uint32_t packed[C::COLS_PER_EPI_WARP / 2];
-#pragma unroll
-            for (int c = 0; c < C::COLS_PER_EPI_WARP / 64; c++) {
-                uint32_t r[64];
-                tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 64 * c, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i++)
-                    packed[c * 32 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r[2 * i]), alpha), __fmul_rn(__uint_as_float(r[2 * i + 1]), alpha));
-            }
-            // accumulator drained: hand tensor memory back before touching global memory
+            // Drain: both halves of this warp's 128 accumulator columns are requested back to back and only waited
+            // for once; tensor memory goes back to the MMA warp before any arithmetic on the values.
+            uint32_t r0[64], r1[64];
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base, r0);
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 64, r1);
+            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 if constexpr (CTAS == 2) mbar_arrive_cluster(tmem_empty_leader); else mbar_arrive(tmem_empty_leader);
+            }
+            uint32_t packed[C::COLS_PER_EPI_WARP / 2];
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                packed[i] = pack_bf16x2(__fmul_rn(__uint_as_float(r0[2 * i]), alpha), __fmul_rn(__uint_as_float(r0[2 * i + 1]), alpha));
+                packed[32 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r1[2 * i]), alpha), __fmul_rn(__uint_as_float(r1[2 * i + 1]), alpha));
             }
             drain += clock64() - t1;
             const int row0 = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32;
@@ -581,12 +587,16 @@ static cudaError_t launch_t(const GemmArgs& a) {
     cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = a.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    // programmatic stream serialization: CTAs may be scheduled while the previous kernel drains (they set up barriers and
+    // tensor memory, then execute griddepcontrol.wait before touching global memory)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     static const int group_env = getenv("TKB_GEMM_GROUP") ? atoi(getenv("TKB_GEMM_GROUP")) : 0;
-    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 8, a.status, a.prof};
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof};
     return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
 

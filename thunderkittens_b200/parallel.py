@@ -130,10 +130,32 @@ class AllGatherMatmulNVFP4:
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
         self.epoch = 0
         self.rows = M // local_world_size
+        st = L.AgState()
+        st.rank, st.world, st.M, st.K = local_rank, local_world_size, M, K
+        for b in range(2):
+            for i in range(local_world_size):
+                st.codes[b][i] = self.codes[b].peer_ptr(i); st.scales[b][i] = self.scales[b].peer_ptr(i)
+                st.arrived[b][i] = self.arrived[b].peer_ptr(i); st.slots[b][i] = self.slots[b].peer_ptr(i)
+        for i in range(local_world_size):
+            st.done[i] = self.flags.peer_ptr(i)
+        st.amax, st.sg = self.amax.data_ptr(), self.sg.data_ptr()
+        self._state = st
         if local_world_size > 1:
             dist.barrier(group=group)
 
     def __call__(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
+        """One library call per step (tkb_ag_linear_nvfp4); `step_by_step` below is the same sequence spelled out."""
+        if tuple(X_local.shape) != (self.rows, self.K) or X_local.dtype != torch.bfloat16 or not X_local.is_contiguous():
+            raise RuntimeError("X_local must be a contiguous bf16 tensor of shape (M / world, K)")
+        n_local = W.shape[0]
+        if tuple(D.shape) != (self.M, n_local) or D.dtype != torch.bfloat16 or not D.is_contiguous():
+            raise RuntimeError("D must be a contiguous bf16 tensor of shape (M, N_local)")
+        self.epoch += 1
+        arith = ops._ARITH[self.arithmetic or ops.default_nvfp4_arithmetic]
+        L.check(L.lib().tkb_ag_linear_nvfp4(C.byref(self._state), self.epoch, X_local.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
+                                            D.data_ptr(), 0, n_local, self.num_comm_sms, arith, _stream()))
+
+    def step_by_step(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
         lib = L.lib()
         if tuple(X_local.shape) != (self.rows, self.K) or X_local.dtype != torch.bfloat16 or not X_local.is_contiguous():
             raise RuntimeError("X_local must be a contiguous bf16 tensor of shape (M / world, K)")
