@@ -249,6 +249,33 @@ def run_tp(args) -> None:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dt_e2e = float(t.item())
     barrier()
+    # The same whole problem on ONE GPU (quantize of all 8192 activation rows + the full-N GEMM, no exchange), measured on
+    # rank 0 while the other ranks idle: the T(1) of the strong-scaling curve.
+    single = None
+    if rank == 0 and not args.no_extra:
+        del sets
+        torch.cuda.empty_cache()
+        Xf = synth(torch, dev, Mt, Kt, 700)
+        Wf = synth(torch, dev, Nt, Kt, 800, std=0.02)
+        wcf = torch.empty(Nt, Kt // 2, dtype=u8, device=dev); wsf = torch.empty(Nt // 128, Kt // 64, 512, dtype=u8, device=dev)
+        wgf = torch.empty(1, dtype=torch.float32, device=dev)
+        ops.nvfp4_quantize(Wf, wcf, wsf, wgf, False)
+        del Wf
+        xcf = torch.empty(Mt, Kt // 2, dtype=u8, device=dev); xsf = torch.empty(Mt // 128, Kt // 64, 512, dtype=u8, device=dev)
+        xgf = torch.empty(1, dtype=torch.float32, device=dev)
+        Df = [torch.empty(Mt, Nt, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+
+        def one_gpu(i):
+            ops.nvfp4_quantize(Xf, xcf, xsf, xgf, False)
+            ops.nvfp4_gemm(xcf, xsf, xgf, wcf, wsf, wgf, Df[i % 2])
+
+        for i in range(3):
+            one_gpu(i)
+        t1 = event_time(torch, one_gpu, max(3, min(args.steps, 10)))
+        single = {"ms_per_step": t1 * 1e3, "tflops": 2.0 * Mt * Nt * Kt / t1 * 1e-12,
+                  "what": "tkb_nvfp4_quantize of the 8192 x 8192 activations + tkb_nvfp4_gemm with all 28672 weight rows on rank 0's GPU"}
+        del Xf, wcf, wsf, xcf, xsf, Df
+    barrier()
     if rank == 0:
         pk = measured_peaks()
         flops = 2.0 * Mt * Nt * Kt
@@ -259,8 +286,9 @@ def run_tp(args) -> None:
             "metric": "tensor-parallel NVFP4 GEMM throughput (M=8192 N=28672 K=8192)", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 x fp32, fp32 acc)", "data": "synthetic",
-            "config": {"workload": "TP NVFP4 GEMM M=8192 N=28672 K=8192: weights N-sharded, bf16 activation rows sharded, per step: amax all-reduce, "
-                                   "quantize, NVFP4 all-gather over NVLink fused with the tcgen05 GEMM", "parallelism": f"tp{world}",
+            "config": {"workload": "TP NVFP4 GEMM M=8192 N=28672 K=8192: weights N-sharded, bf16 activation rows sharded, per step two launches: "
+                                   "quantize with the amax max-reduced over NVLink inside the kernel, then the NVFP4 all-gather over NVLink "
+                                   "fused with the tcgen05 GEMM", "parallelism": f"tp{world}",
                        "l2": f"{GROUPS} rotating weight/activation/output sets", "comm_ctas": op.num_comm_sms},
             "roofline": {"bound": "tensor", "achieved": tf / world, "peak": 4.0 * pk["bf16_tflops"], "unit": "TFLOP/s per GPU",
                          "frac": tf / peak, "traffic": None, "kernel": "tkb::gemm_kernel<NVFP4, cta pair, N256, all-gather>",
@@ -269,7 +297,7 @@ def run_tp(args) -> None:
             "e2e": {"value": flops / dt_e2e * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": rows * Kt * 2 * world,
                     "d2h_bytes_per_step": Mt * n_local * 2 * world, "ms_per_step": dt_e2e * 1e3,
                     "path": "pinned host bf16 shard -> H2D -> AllGatherMatmulNVFP4 -> D2H of the rank's output columns"},
-            "gpu_launches": args.steps * 5 * world, "clocks": clocks,
+            "gpu_launches": args.steps * 2 * world, "clocks": clocks, "single_gpu_same_problem": single,
         }
         print(json.dumps(line), flush=True)
     op.close()
@@ -441,7 +469,9 @@ def run_ours(args) -> None:
                        "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
                        "l2": f"{GROUPS} rotating operand sets of 256 MiB (> 126 MB L2)"},
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                         "traffic": None, "kernel": "tkb::gemm_kernel<MXFP8, cta pair, N256>",
+                         "traffic": MXFP8_GEMM_DRAM_BYTES, "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/mxfp8_gemm_ncu.md)",
+                         "algorithmic_bytes": 2 * M * K + 2 * (M // 128) * (K // 128) * 512 + M * N * 2,
+                         "kernel": "tkb::gemm_kernel<MXFP8, cta pair, N256>",
                          "peak_source": f"2 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense FP8 ceiling)",
                          "frac_of_nominal_4500": tflops / NOMINAL["fp8"]},
             "e2e": {"value": FLOPS / dt_e2e * 1e-12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
@@ -455,6 +485,11 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 8192^3 MXFP8 GEMM (ncu capture summarised in
+# profiles/mxfp8_gemm_ncu.md): 348.0 MB read + 116.8 MB written.
+MXFP8_GEMM_DRAM_BYTES = 464.8e6
 
 
 def side_measurements(torch, ops, dev) -> dict:

@@ -91,6 +91,17 @@ int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, v
 int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* sg, const float* amax, int M, int K, int arithmetic,
                             void* stream);
 
+/* Quantize of a ROW-SHARDED tensor in one launch: every rank passes its own rows, the per-tensor amax is
+ * max-reduced across the ranks inside the kernel (the last CTA to reach the kernel's grid barrier trades the rank's
+ * maximum with the peers over NVLink: one posted store per peer, bounded polls), so all shards are quantized exactly
+ * like the whole tensor and *sg is the same on every rank.  peer_slots[i]: rank i's array of `world` zero-initialised
+ * 64-bit words in a symmetric buffer (as for tkb_amax_allreduce); epoch grows by one per call on a slot table and
+ * consecutive calls must alternate between two tables (a peer may be one call ahead).  layout 0: codes [M, K/2] +
+ * chunked scales `sc` (GEMM operand form); layout 1: self-contained rows as tkb_nvfp4_quantize_rows (`sc` unused).
+ * world == 1 is tkb_nvfp4_quantize.  Every rank must make the call.  No counterpart in the reference. */
+int tkb_nvfp4_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
+                               void* const* peer_slots, int world, int rank, unsigned int epoch, void* stream);
+
 /* max |x| of a bf16 matrix into *amax (device float; overwritten).  Part of
  * nvfp4_quantize::absmax_kernel (nvfp4_b200_gemm.cu:360-418) exposed for sharded tensors. */
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream);
@@ -181,27 +192,38 @@ int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer,
  * from this rank; entry `rank` is local.  Each rank quantizes its M/world rows (with the all-reduced per-tensor
  * amax, so X_sg is the same everywhere) into its own slice of its own buffers; comm_ctas CTAs of the kernel push
  * that slice into every peer's buffers over NVLink while the rest multiply, own rows first.  peer_arrived[i]: rank
- * i's array of M/256 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own row blocks
- * on every peer.  Before a buffer set is reused the caller must know that every peer finished reading it
- * (tkb_signal_peers / tkb_wait_flags).  M % (256 * world) == 0. */
+ * i's array of M/64 32-bit arrival epochs, one per 64 gathered rows (entry `rank` local); a rank writes the entries
+ * of its own rows on every peer.  Before a buffer set is reused every peer must have finished reading it:
+ *   - peer_done == NULL: the caller sees to that itself (tkb_signal_peers / tkb_wait_flags);
+ *   - else peer_done[i] is rank i's array of `world` 32-bit epochs and exit_counter a zeroed device word owned by
+ *     this rank: the kernel's last CTA stores `epoch` into entry `rank` of every peer's array, and its comm CTAs
+ *     wait (bounded) for entry d of the local array to reach epoch - 2 before they first write to rank d
+ *     (two buffer sets alternate, so epoch - 2 was the last reader of this one).
+ * M % (256 * world) == 0. */
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
-                      unsigned int epoch, int comm_ctas, void* stream);
+                      void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream);
 
-/* One call for a whole step of the column-parallel layer (amax of the local rows -> NVLink max all-reduce -> quantize
- * into this rank's slice -> tkb_ag_gemm_nvfp4 -> acknowledge), so that the host spends one library call per step
- * instead of six.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index [set][rank]);
+/* Diagnostics, host only (no GPU needed, no counterpart in the reference): enumerates, in order, the pieces that comm
+ * CTA `comm_idx` of `comm_ctas` pushes in tkb_ag_gemm_nvfp4 for the given problem and rank.  Six values per piece:
+ * destination rank, span (0 codes, 1 scales), byte offset in the gathered buffer, bytes, arrival-flag index, 1 if the
+ * piece completes its unit.  Returns the number of pieces (even if larger than max_pieces), or -code on bad arguments. */
+int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces);
+
+/* One call for a whole step of the column-parallel layer: two launches, tkb_nvfp4_quantize_sharded of the local rows
+ * into this rank's slice, then tkb_ag_gemm_nvfp4 with the epoch hand-shake inside the kernel.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index [set][rank]);
  * the set used is epoch % 2, and epoch must grow by one per call, starting at 1, on every rank alike.
  * Host-side convenience over the entry points above; no counterpart in the reference. */
 typedef struct tkb_ag_state {
     int rank, world, M, K;
     void* codes[2][8];      /* [M, K/2] gathered codes */
     void* scales[2][8];     /* [M/128, K/64, 512] gathered scales */
-    void* arrived[2][8];    /* [M/256] arrival epochs */
+    void* arrived[2][8];    /* [M/64] arrival epochs */
     void* slots[2][8];      /* [world] 64-bit amax all-reduce slots */
     void* done[8];          /* [world] 32-bit "my kernel of epoch e is finished" flags */
     float* amax;            /* device scratch, 1 float */
     float* sg;              /* device, 1 float: the per-tensor scale of the gathered activations */
+    void* exit_counter;     /* device, one zeroed 32-bit word */
 } tkb_ag_state;
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local_bf16, const void* W, const void* W_sc,
                         const float* W_sg, void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream);
@@ -243,6 +265,29 @@ int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes
  * accumulation in ascending j.  peer_Y[i]: rank i's Y buffer as seen from this rank. */
 int tkb_moe_combine(void* const* peer_Y, int64_t ldy, const int* comb_idx, const float* weights, void* out, int T_local, int top_k, int I,
                     int world, void* stream);
+
+/* One call for a whole layer: route -> exchange of the chosen experts -> schedule -> tkb_nvfp4_quantize_sharded of this
+ * rank's tokens (self-contained rows) -> dispatch fused with the grouped GEMM -> combine, with the epoch hand-shakes in
+ * between, all enqueued on `stream`.  `st` holds the symmetric buffers as seen from this rank (index [rank], or
+ * [set][rank] for the two alternating sets; set = epoch % 2) and the rank's local work buffers; epoch grows by one per
+ * call, starting at 1, on every rank alike.  logits_local [T/world, E] fp32, X_local [T/world, H] bf16, out [T/world, I]
+ * bf16.  Host-side convenience over the entry points above; no counterpart in the reference. */
+typedef struct tkb_moe_state {
+    int rank, world, T, H, I, E, top_k, cap_rows;
+    void* xq_rows[2][8];       /* [T/world, H/2 + H/16] quantized tokens */
+    void* slots[2][8];         /* [world] 64-bit amax exchange slots */
+    void* experts_all[2][8];   /* [T, top_k] int32: every token's chosen experts */
+    void* Y[8];                /* [cap_rows, I] bf16 expert outputs */
+    void* flags[8];            /* [3 * world] epochs: tokens quantized, expert outputs complete, call finished */
+    void* counters[8];         /* [2 * world] arrival counters of the expert exchange */
+    void* codes; void* scales; /* local operand buffers [cap_rows, H/2], [cap_rows/128, H/64, 512] */
+    void* experts_local; void* weights;                 /* [T/world, top_k] int32 / fp32 */
+    void* counts; void* padded;                         /* [E] int32 */
+    void* pull_idx; void* block_expert; void* num_blocks; void* comb_idx; void* arrived;   /* as in tkb_moe_schedule / dispatch */
+    float* sg;                 /* device, 1 float: per-tensor scale of the tokens */
+} tkb_moe_state;
+int tkb_moe_layer_nvfp4(const tkb_moe_state* st, unsigned int epoch, const float* logits_local, const void* X_local_bf16, const void* W,
+                        const void* W_sc, const float* W_sg, void* out, int comm_ctas, int arithmetic, void* stream);
 
 #ifdef __cplusplus
 }

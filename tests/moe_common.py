@@ -25,7 +25,9 @@ def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=
         # this rank's stacked expert weights, quantized as one tensor
         Wl = W[rank * El:(rank + 1) * El].reshape(El * I, H)
         wq = O.nvfp4_quantize(bf16_bits(Wl))
-        out = layer.forward(logits[rank * Tl:(rank + 1) * Tl].contiguous().to(dev), X[rank * Tl:(rank + 1) * Tl].contiguous().to(dev),
+        # both host paths of the layer on alternating calls: the single library call and the spelled-out sequence
+        step = layer.forward if it % 2 == 0 else layer.forward_step_by_step
+        out = step(logits[rank * Tl:(rank + 1) * Tl].contiguous().to(dev), X[rank * Tl:(rank + 1) * Tl].contiguous().to(dev),
                             to_dev_u8(wq[0], dev), to_dev_u8(wq[1], dev), torch.from_numpy(wq[2]).to(dev))
         torch.cuda.synchronize()
         st = _lib.device_status()

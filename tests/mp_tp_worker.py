@@ -29,10 +29,12 @@ def main():
     Wd, Wsc, Wsg = to_dev_u8(wq[0], dev), to_dev_u8(wq[1], dev), torch.from_numpy(wq[2]).to(dev)
     op = parallel.AllGatherMatmulNVFP4(M, K, local, world, num_comm_sms=4, arithmetic="spec")
     ok = True
-    for it in range(4):      # several calls: both buffer sets, acknowledgements, growing epochs
+    for it in range(6):      # several calls: both buffer sets, acknowledgements, growing epochs
         X = (torch.randn(M, K, generator=g) * (1.0 + it)).to(torch.bfloat16)
         D = torch.full((M, n_local), float("nan"), dtype=torch.bfloat16, device=dev)
-        op(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
+        # both host paths on alternating calls: the single library call (epoch hand-shake inside the kernels) and
+        # the spelled-out sequence (separate wait / signal launches)
+        (op if it % 2 == 0 else op.step_by_step)(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
         torch.cuda.synchronize()
         st = _lib.device_status()
         xq = O.nvfp4_quantize(bf16_bits(X), False, "spec")        # quantize(full X): what the shards must add up to

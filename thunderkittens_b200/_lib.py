@@ -50,12 +50,16 @@ _SIGNATURES = {
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_ag_linear_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp], _i),
-    "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.c_uint, _i, _vp], _i),
+    "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp,
+                           C.c_uint, _i, _vp], _i),
+    "tkb_debug_ag_schedule": ([_i, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong), _i], _i),
+    "tkb_nvfp4_quantize_sharded": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_vp), _i, _i, C.c_uint, _vp], _i),
     "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),
     "tkb_moe_schedule": ([_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
     "tkb_moe_dispatch_gemm": ([C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, C.c_uint,
                                _i, _i, _i, _i, _i, _i, _i, _vp], _i),
+    "tkb_moe_layer_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
@@ -64,7 +68,16 @@ class AgState(C.Structure):
     """Mirror of tkb_ag_state (include/tkb200.h)."""
     _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("K", _i),
                 ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
-                ("done", _vp * 8), ("amax", _vp), ("sg", _vp)]
+                ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp)]
+
+
+class MoeState(C.Structure):
+    """Mirror of tkb_moe_state (include/tkb200.h)."""
+    _fields_ = [(n, _i) for n in ("rank", "world", "T", "H", "I", "E", "top_k", "cap_rows")] + \
+               [("xq_rows", (_vp * 8) * 2), ("slots", (_vp * 8) * 2), ("experts_all", (_vp * 8) * 2),
+                ("Y", _vp * 8), ("flags", _vp * 8), ("counters", _vp * 8)] + \
+               [(n, _vp) for n in ("codes", "scales", "experts_local", "weights", "counts", "padded", "pull_idx", "block_expert", "num_blocks",
+                                   "comb_idx", "arrived", "sg")]
 
 
 _lib = None

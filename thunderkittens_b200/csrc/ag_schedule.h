@@ -1,0 +1,58 @@
+// Push schedule of the all-gather GEMM's comm CTAs: which bytes of this rank's quantized rows go where, in which
+// order, and which arrival flag each unit raises.  Plain integer arithmetic shared by the kernel (gemm.cu) and by a
+// host-side enumeration (tkb_debug_ag_schedule) that the CPU tests use to check coverage.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define TKB_HD __host__ __device__ __forceinline__
+#else
+#define TKB_HD inline
+#endif
+
+namespace tkb {
+
+constexpr int kAgPartsPerBlock = 4;          // a 256-row block travels as 4 independently flagged 64-row parts
+
+struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock; };
+struct AgCursor { int u; int span; uint32_t o; };                 // unit, span (0 = codes, 1 = scales), bytes done in the span
+struct AgPiece { size_t off; uint32_t bytes, span_len; int span, dst_rank, flag; };
+
+// A unit is one 64-row part of one of this rank's 256-row blocks for one destination.  Units are numbered
+// destination-major, destinations in the order in which they consume this rank's rows (rank-1 first).
+TKB_HD int ag_units(const AgGeometry& g) { return (g.world - 1) * g.blocks_per_rank * kAgPartsPerBlock; }
+
+// The next piece (at most piece_bytes) at the cursor.  `off` is a byte offset into the gathered codes (span 0) or
+// scales (span 1) buffer, the same on the source and on the destination; `flag` indexes the arrival array.
+TKB_HD AgPiece ag_piece(const AgGeometry& g, const AgCursor& c, uint32_t piece_bytes) {
+    AgPiece pc;
+    const int per_dst = g.blocks_per_rank * kAgPartsPerBlock;
+    pc.dst_rank = (g.rank + g.world - 1 - c.u / per_dst) % g.world;
+    const int in_dst = c.u % per_dst, b = in_dst / kAgPartsPerBlock, part = in_dst % kAgPartsPerBlock;
+    const size_t row0 = (size_t(g.rank) * g.blocks_per_rank + b) * 256;
+    pc.span = c.span;
+    if (c.span == 0) {                       // codes of 64 rows: contiguous
+        pc.span_len = uint32_t(64) * uint32_t(g.k_bytes);
+        pc.off = (row0 + size_t(part) * 64) * size_t(g.k_bytes) + c.o;
+    } else {                                 // a quarter of the bytes of the block's two 128-row scale blocks
+        pc.span_len = uint32_t(g.sc_bytes_per_mblock) / 2u;
+        pc.off = (row0 / 128) * size_t(g.sc_bytes_per_mblock) + size_t(part) * pc.span_len + c.o;
+    }
+    pc.bytes = piece_bytes < pc.span_len - c.o ? piece_bytes : pc.span_len - c.o;
+    pc.flag = (g.rank * g.blocks_per_rank + b) * kAgPartsPerBlock + part;
+    return pc;
+}
+
+// Moves the cursor past a piece; true when that piece was the last of its unit (comm CTA i owns units i, i + n, ...).
+TKB_HD bool ag_advance(AgCursor& c, const AgPiece& pc, int comm_ctas) {
+    c.o += pc.bytes;
+    if (c.o < pc.span_len) return false;
+    c.o = 0;
+    if (++c.span < 2) return false;
+    c.span = 0;
+    c.u += comm_ctas;
+    return true;
+}
+
+} // namespace tkb

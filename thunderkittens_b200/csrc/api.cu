@@ -245,7 +245,7 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
 }
 
 static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
-                                 int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0) {
+                                 int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0, const QuantExchange* xch = nullptr) {
     // sc_rowmajor: codes and scales share one row of K/2 + K/16 bytes (codes first); `sc` is ignored
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
@@ -261,6 +261,11 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
     a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
     a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count; a.sc_rowmajor = sc_rowmajor;
+    memset(&a.xch, 0, sizeof(a.xch));
+    if (xch) {
+        if (amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: the cross-rank amax exchange belongs to the fused-amax kernel (no amax input)");
+        a.xch = *xch;
+    }
     TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
     return TKB_OK;
 }
@@ -305,6 +310,21 @@ int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* 
                             void* stream) {
     if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_rows: null amax");
     return nvfp4_quantize_common(A_bf16, lda, rows, nullptr, sg, amax, M, K, 0, arithmetic, stream, 1);
+}
+
+int tkb_nvfp4_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
+                               void* const* peer_slots, int world, int rank, unsigned int epoch, void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: world must be 1..8 and 0 <= rank < world");
+    if (layout != 0 && layout != 1) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: layout must be 0 (operand) or 1 (self-contained rows)");
+    if (world > 1 && (!peer_slots || epoch == 0)) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot table or epoch 0");
+    QuantExchange x;
+    memset(&x, 0, sizeof(x));
+    x.world = world; x.rank = rank; x.epoch = epoch;
+    for (int i = 0; i < world && world > 1; i++) {
+        if (!peer_slots[i]) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot array for rank %d", i);
+        x.slots[i] = static_cast<unsigned long long*>(peer_slots[i]);
+    }
+    return nvfp4_quantize_common(A_bf16, lda, codes, layout ? nullptr : sc, sg, nullptr, M, K, 0, arithmetic, stream, layout, world > 1 ? &x : nullptr);
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {

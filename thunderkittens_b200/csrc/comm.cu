@@ -13,6 +13,7 @@
 #include "../../include/tkb200.h"
 #include "internal.h"
 #include "ptx.cuh"
+#include "ag_schedule.h"
 
 namespace tkb {
 
@@ -197,7 +198,7 @@ int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer,
 
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
-                      unsigned int epoch, int comm_ctas, void* stream) {
+                      void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream) {
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
     if (!peer_codes || !peer_scales || !X_sg || !W || !W_sc || !W_sg || !D || !peer_arrived)
@@ -207,6 +208,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     if (K % 64 || N_local % 8) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: K %% 64 and N %% 8 must be 0");
     if (comm_ctas < 0 || comm_ctas % 2 || comm_ctas > sm - 2) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: comm_ctas must be even and leave compute CTAs");
     if (world > 1 && comm_ctas == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world > 1 needs comm_ctas >= 2");
+    if (peer_done && !exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: peer_done needs an exit counter");
     GemmArgs g;
     memset(&g, 0, sizeof(g));
     g.kind = KIND_NVFP4; g.config = 0;
@@ -222,10 +224,37 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     g.comm.ag.codes = static_cast<uint8_t*>(peer_codes[rank]);
     g.comm.ag.scales = static_cast<uint8_t*>(peer_scales[rank]);
     for (int i = 0; i < world; i++) g.comm.ag.peer_arrived[i] = static_cast<unsigned int*>(peer_arrived[i]);
+    if (peer_done) {
+        for (int i = 0; i < world; i++) {
+            if (!peer_done[i]) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: null done array for rank %d", i);
+            g.comm.ag.peer_done[i] = static_cast<unsigned int*>(peer_done[i]);
+        }
+        g.comm.ag.exit_counter = static_cast<unsigned int*>(exit_counter);
+    }
     g.comm.ag.epoch = epoch; g.comm.ag.rank = rank; g.comm.ag.world = world; g.comm.ag.blocks_per_rank = M / world / 256;
     g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
     TKB_CUDA_C(launch_gemm(g));
     return TKB_OK;
+}
+
+int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces) {
+    if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || M < 1 || M % (256 * world) || K < 64 || K % 64 || comm_ctas < 1 ||
+        comm_idx < 0 || comm_idx >= comm_ctas || piece_bytes < 16 || piece_bytes % 16 || (!out && max_pieces > 0))
+        return -api_fail(TKB_ERR_INVALID_ARG, "debug_ag_schedule: bad arguments");
+    const AgGeometry geo{rank, world, M / world / 256, K / 2, (K / 64) * 512};
+    const int units = ag_units(geo);
+    AgCursor c{comm_idx, 0, 0u};
+    int n = 0;
+    while (c.u < units) {
+        const AgPiece pc = ag_piece(geo, c, uint32_t(piece_bytes));
+        const bool last = ag_advance(c, pc, comm_ctas);
+        if (n < max_pieces) {
+            long long* o = out + size_t(n) * 6;
+            o[0] = pc.dst_rank; o[1] = pc.span; o[2] = (long long)pc.off; o[3] = pc.bytes; o[4] = pc.flag; o[5] = last ? 1 : 0;
+        }
+        n++;
+    }
+    return n;
 }
 
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local, const void* W, const void* W_sc, const float* W_sg,
@@ -234,20 +263,15 @@ int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* 
     const int w = st->world, r = st->rank, b = int(epoch % 2u);
     if (w < 1 || w > kMaxWorld || r < 0 || r >= w || st->M % (256 * w)) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: bad world / rank / M");
     const int rows = st->M / w;
-    // set b was last used at epoch - 2: every peer's kernel of that epoch must be finished before it is written again
-    if (w > 1 && epoch > 2)
-        if (int e = tkb_wait_flags(st->done[r], w, r, epoch - 2, stream)) return e;
-    if (int e = tkb_absmax_bf16(X_local, 0, rows, st->K, st->amax, stream)) return e;
-    if (w > 1)
-        if (int e = tkb_amax_allreduce(st->slots[b], w, r, epoch, st->amax, st->amax, stream)) return e;
+    if (!st->exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: null exit counter");
     uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
     uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
-    if (int e = tkb_nvfp4_quantize_with_amax(X_local, 0, my_codes, my_scales, st->sg, st->amax, rows, st->K, 0, arithmetic, stream)) return e;
-    if (int e = tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b], epoch,
-                                  w > 1 ? comm_ctas : 0, stream)) return e;
-    if (w > 1)
-        if (int e = tkb_signal_peers(st->done, w, r, r, epoch, 0, stream)) return e;
-    return TKB_OK;
+    // This rank's slice of its own buffers is only read by its own kernels (earlier in this stream); what the peers
+    // read are the copies the comm CTAs push, and those wait for the peers' epoch - 2 kernels themselves.
+    if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, stream))
+        return e;
+    return tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
+                             st->done, st->exit_counter, epoch, w > 1 ? comm_ctas : 0, stream);
 }
 
 } // extern "C"

@@ -28,6 +28,7 @@
 #include <cstdlib>
 #include "ptx.cuh"
 #include "internal.h"
+#include "ag_schedule.h"
 
 namespace tkb {
 
@@ -121,57 +122,109 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
                  ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
 }
 
-// One comm CTA: PUSHES its share of the (destination rank, 256-row block of this rank's slice) units into the
-// destinations' buffers.  Reads are local (fast), the NVLink side is posted writes, so a handful of CTAs can
-// fill the links; a pull over NVLink is limited per SM by the read round trip.  Destinations are served in
-// the order in which they will consume this rank's rows (rank-1 first).  After a unit's bytes are complete a
-// system-scope release store publishes the epoch in the destination's `arrived` array.
+// One comm CTA (a single thread of it): PUSHES its share of this rank's quantized rows into the peers' buffers.
+// Reads are local (fast), the NVLink side is posted writes, so a handful of CTAs can fill the links; a pull over
+// NVLink is limited per SM by the read round trip.
+//   * A unit is one 64-row part of a 256-row block for one destination: the codes of those rows (contiguous) and
+//     a quarter of the block's scale bytes.  Units are numbered destination-major, destinations in the order in
+//     which they will consume this rank's rows (rank-1 first), and dealt round-robin to the comm CTAs, so all of
+//     them work for the destination that needs the data first.
+//   * Pieces of up to PIECE bytes flow through a ring in shared memory: loads run up to AHEAD pieces in front of
+//     the store cursor across span and unit boundaries, so the pipe never drains between units.
+//   * When all bytes of a unit have been written (bulk-group completion, a few stores later so that the pipe
+//     keeps moving), a system-scope release store publishes the epoch in the destination's `arrived` array.
+//   * With peer_done set, the first store to a destination waits until that rank's kernel of epoch-2 (the last
+//     reader of the buffer set being overwritten) has finished.
 template <int RING, int PIECE>
 __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
                         const WaitCtx& wc) {
-    // single thread; bars[0..RING) are "piece landed in shared memory" barriers.  Up to AHEAD loads are in flight in
-    // front of the store cursor and up to RING - AHEAD stores may still be reading their slots behind it.
-    constexpr int AHEAD = RING / 2;
-    static_assert(RING >= 4, "ring too small");
-    const int units = (ag.world - 1) * ag.blocks_per_rank;
+    // bars[0..RING) are "piece landed in shared memory" barriers.  Up to AHEAD loads are in flight in front of the
+    // store cursor and up to RING - AHEAD stores may still be reading their slots behind it.
+    constexpr int AHEAD = RING - 3;
+    constexpr int LAG = 3;                    // a unit is published once LAG younger stores have been issued
+    constexpr int PEND = 4;
+    static_assert(RING >= 6, "ring too small");
+    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock};
+    const int units = ag_units(geo);
+    const unsigned int* done = ag.peer_done[ag.rank];
+    AgCursor lc{comm_idx, 0, 0u}, sc{comm_idx, 0, 0u};
     uint32_t issued = 0, stored = 0;         // piece counters over the whole kernel (ring position / phase)
-    for (int u = comm_idx; u < units; u += ag.comm_ctas) {
-        const int dst = (ag.rank + ag.world - 1 - u / ag.blocks_per_rank) % ag.world;
-        const int b = u % ag.blocks_per_rank;
-        const size_t row0 = (size_t(ag.rank) * ag.blocks_per_rank + b) * 256;
-        // two contiguous spans: codes of 256 rows, scales of two 128-row blocks
-        const size_t off[2] = {row0 * k_bytes, (row0 / 128) * sc_bytes_per_mblock};
-        const size_t len[2] = {size_t(256) * k_bytes, size_t(2) * sc_bytes_per_mblock};
-        const uint8_t* sbase[2] = {ag.codes, ag.scales};
-        uint8_t* dbase[2] = {const_cast<uint8_t*>(ag.peer_codes[dst]), const_cast<uint8_t*>(ag.peer_scales[dst])};
-        for (int span = 0; span < 2; span++) {
-            const size_t n_pieces = (len[span] + PIECE - 1) / PIECE;
-            size_t next_load = 0;
-            for (size_t i = 0; i < n_pieces; i++) {
-                if (next_load < n_pieces && issued - stored < AHEAD) {
-                    // slots about to be refilled were last read by stores at least RING - AHEAD groups ago
-                    tma_store_wait_read<RING - AHEAD - 1>();
-                    while (next_load < n_pieces && issued - stored < AHEAD) {
-                        const uint32_t slot = issued % RING;
-                        const size_t o = next_load * PIECE;
-                        const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
-                        mbar_arrive_expect_tx(smem_u32(&bars[slot]), bytes);
-                        bulk_load(smem + slot * PIECE, sbase[span] + off[span] + o, bytes, smem_u32(&bars[slot]));
-                        issued++; next_load++;
-                    }
-                }
-                const uint32_t slot = stored % RING;
-                if (!mbar_wait(wc, smem_u32(&bars[slot]), (stored / RING) & 1)) return;
-                const size_t o = i * PIECE;
-                const uint32_t bytes = uint32_t(min(size_t(PIECE), len[span] - o));
-                bulk_store(dbase[span] + off[span] + o, smem + slot * PIECE, bytes);
-                tma_store_commit();
-                stored++;
+    uint32_t pend_at[PEND]; unsigned int* pend_flag[PEND];
+    int pend_head = 0, pend_n = 0;
+    int checked_dst = -1;
+    bool ok = true;
+    while (sc.u < units) {
+        if (lc.u < units && issued - stored < AHEAD) {
+            // slots about to be refilled were last read by stores at least RING - AHEAD groups ago
+            tma_store_wait_read<RING - AHEAD - 1>();
+            while (lc.u < units && issued - stored < AHEAD) {
+                const AgPiece pc = ag_piece(geo, lc, PIECE);
+                const uint32_t slot = issued % RING;
+                mbar_arrive_expect_tx(smem_u32(&bars[slot]), pc.bytes);
+                bulk_load(smem + slot * PIECE, (pc.span == 0 ? ag.codes : ag.scales) + pc.off, pc.bytes, smem_u32(&bars[slot]));
+                issued++;
+                ag_advance(lc, pc, ag.comm_ctas);
             }
         }
-        tma_store_wait<0>();                 // all bytes of this unit have been written to the destination
+        const AgPiece pc = ag_piece(geo, sc, PIECE);
+        if (done != nullptr && pc.dst_rank != checked_dst) {
+            if (ag.epoch > 2u && !flag_wait(wc, done + pc.dst_rank, ag.epoch - 2u)) { ok = false; break; }
+            checked_dst = pc.dst_rank;
+        }
+        const uint32_t slot = stored % RING;
+        if (!mbar_wait(wc, smem_u32(&bars[slot]), (stored / RING) & 1)) { ok = false; break; }
+        bulk_store(const_cast<uint8_t*>(pc.span == 0 ? ag.peer_codes[pc.dst_rank] : ag.peer_scales[pc.dst_rank]) + pc.off, smem + slot * PIECE, pc.bytes);
+        tma_store_commit();
+        stored++;
+        if (ag_advance(sc, pc, ag.comm_ctas)) {
+            if (pend_n == PEND) {                       // cannot happen with units of more than one piece; keeps the queue safe
+                tma_store_wait<0>();
+                __threadfence_system();
+                while (pend_n > 0) {
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
+                    pend_head = (pend_head + 1) % PEND; pend_n--;
+                }
+            }
+            const int tail = (pend_head + pend_n) % PEND;
+            pend_at[tail] = stored;
+            pend_flag[tail] = ag.peer_arrived[pc.dst_rank] + pc.flag;
+            pend_n++;
+        }
+        if (pend_n > 0 && stored - pend_at[pend_head] >= uint32_t(LAG)) {
+            tma_store_wait<LAG>();                      // every store older than the LAG youngest has been written
+            __threadfence_system();
+            while (pend_n > 0 && stored - pend_at[pend_head] >= uint32_t(LAG)) {
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
+                pend_head = (pend_head + 1) % PEND; pend_n--;
+            }
+        }
+    }
+    if (!ok) {
+        // gave up on a wait: let the copies that are still in flight into this CTA's shared memory land before leaving
+        for (uint32_t i = stored; i < issued; i++) mbar_wait(wc, smem_u32(&bars[i % RING]), (i / RING) & 1);
+    }
+    tma_store_wait<0>();
+    if (ok && pend_n > 0) {
         __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.peer_arrived[dst] + ag.rank * ag.blocks_per_rank + b), "r"(ag.epoch) : "memory");
+        while (pend_n > 0) {
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
+            pend_head = (pend_head + 1) % PEND; pend_n--;
+        }
+    }
+}
+
+// Every CTA of the all-gather kernel calls this (one thread) when it has finished: the last one to arrive tells the
+// peers that this rank no longer reads the buffer set of this epoch.
+__device__ __forceinline__ void ag_exit(const AgParams& ag) {
+    if (ag.exit_counter == nullptr) return;
+    __threadfence();
+    const unsigned int prev = atomicAdd(ag.exit_counter, 1u);
+    if (prev == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned int*>(ag.exit_counter) = 0u;       // ready for the next launch
+        __threadfence_system();
+        for (int pr = 0; pr < ag.world; pr++)
+            if (pr != ag.rank && ag.peer_done[pr] != nullptr)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.peer_done[pr] + ag.rank), "r"(ag.epoch) : "memory");
     }
 }
 
@@ -291,7 +344,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __shared__ __align__(8) uint64_t bar_tmem_empty;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : (MODE == MODE_AG ? 10 : 1)];   // comm CTAs of the MoE / all-gather modes
+    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : (MODE == MODE_AG ? 13 : 1)];   // comm CTAs of the MoE / all-gather modes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0;
@@ -356,13 +409,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if constexpr (AG) {
         if (is_comm) {
             if (threadIdx.x == 0) {
-                // reuse the (idle) "full" barriers of this CTA as piece barriers and the operand ring as staging
+                // the (idle) operand ring and epilogue staging of this CTA serve as the piece ring
                 constexpr int PIECE = 16384;
-                constexpr int RING = 10;
-                static_assert(RING * PIECE <= C::STAGES * C::STAGE_BYTES, "staging ring does not fit");
+                constexpr int RING = 13;
+                static_assert(RING * PIECE <= C::STAGES * C::STAGE_BYTES + C::EPI_BYTES, "staging ring does not fit");
                 for (int i = 0; i < RING; i++) mbar_init(smem_u32(&bar_comm[i]), 1);
                 fence_mbar_init();
                 ag_push<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_comm, wc);
+                ag_exit(ag);
             }
             __syncthreads();
             cluster_sync();      // matches the teardown barrier of the compute clusters' code path below
@@ -393,7 +447,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if constexpr (AG) {
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
-                        if (!flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk, ag.epoch)) { ok = false; break; }
+                        for (int part = 0; part < kAgPartsPerBlock && ok; part++)
+                            ok = flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk * kAgPartsPerBlock + part, ag.epoch);
+                        if (!ok) break;
                         fence_proxy_async_all();
                     }
                 }
@@ -562,6 +618,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, C::TMEM_COLS);
+    }
+    if constexpr (AG) {
+        if (threadIdx.x == 0) ag_exit(ag);      // after the barrier: this CTA's operand loads and output stores are complete
     }
 }
 

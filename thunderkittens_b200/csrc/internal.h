@@ -25,8 +25,11 @@ struct AgParams {
     const uint8_t* peer_codes[kMaxWorld];    // base of every rank's gathered-codes buffer [M, K/2] (own entry = local)
     const uint8_t* peer_scales[kMaxWorld];   // base of every rank's gathered-scales buffer [M/128, K/64, 512]
     uint8_t* codes; uint8_t* scales;         // this rank's buffers (same as peer_*[rank], writable)
-    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs [world * blocks_per_rank]; entry (s, b) of rank r's
-                                             // array is written by rank s when block b of its slice has landed on rank r
+    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs, one per 64 gathered rows ([M / 64]); the entries of
+                                             // rank s's rows in rank r's array are written by rank s when those rows have landed on r
+    unsigned int* peer_done[kMaxWorld];      // optional (all null = the caller orders the epochs itself): every rank's [world] array of
+                                             // "kernel finished" epochs; entry s of rank r's array is written by rank s
+    unsigned int* exit_counter;              // with peer_done: zeroed device word, counts the CTAs that have left the kernel
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
 };

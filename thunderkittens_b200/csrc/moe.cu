@@ -290,4 +290,45 @@ int tkb_moe_combine(void* const* peer_Y, int64_t ldy, const int* comb_idx, const
     return TKB_OK;
 }
 
+int tkb_moe_layer_nvfp4(const tkb_moe_state* st, unsigned int epoch, const float* logits_local, const void* X_local, const void* W,
+                        const void* W_sc, const float* W_sg, void* out, int comm_ctas, int arithmetic, void* stream) {
+    if (!st || !logits_local || !X_local || !W || !W_sc || !W_sg || !out || epoch == 0)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_layer: null pointer or epoch 0");
+    const int w = st->world, r = st->rank, b = int(epoch % 2u);
+    if (w < 1 || w > kMaxWorld || r < 0 || r >= w || st->T % w || st->E % w) return api_fail(TKB_ERR_INVALID_ARG, "moe_layer: bad world / rank / T / E");
+    const int Tl = st->T / w, El = st->E / w;
+    // flag array of every rank: [0, w) tokens quantized ("ready"), [w, 2w) expert outputs complete, [2w, 3w) layer call finished
+    unsigned int* fl = static_cast<unsigned int*>(st->flags[r]);
+    if (int e = tkb_moe_route(logits_local, Tl, st->E, st->top_k, static_cast<int*>(st->experts_local), static_cast<float*>(st->weights), stream)) return e;
+    // everything of parity b was last used by call epoch - 2: every peer must have finished that call before it is overwritten
+    if (w > 1 && epoch > 2)
+        if (int e = tkb_wait_flags(fl + 2 * w, w, r, epoch - 2, stream)) return e;
+    if (int e = tkb_all_to_all(st->experts_all[b], st->experts_local, size_t(Tl) * st->top_k * 4, 1, r, w, st->counters, b * w, (epoch + 1) / 2, stream))
+        return e;
+    if (int e = tkb_moe_schedule(static_cast<const int*>(st->experts_all[b][r]), st->T, st->top_k, st->E, w, r, static_cast<int*>(st->counts),
+                                 static_cast<int*>(st->padded), static_cast<int*>(st->pull_idx), static_cast<int*>(st->block_expert),
+                                 static_cast<int*>(st->num_blocks), static_cast<int*>(st->comb_idx), st->cap_rows, stream)) return e;
+    // this rank's tokens, quantized with the amax of all tokens (exchanged inside the kernel), as self-contained rows
+    if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, st->xq_rows[b][r], nullptr, st->sg, Tl, st->H, 1, arithmetic, st->slots[b], w, r, epoch, stream))
+        return e;
+    if (w > 1) {
+        if (int e = tkb_signal_peers(st->flags, w, r, r, epoch, 0, stream)) return e;
+        // Y is rewritten below: every peer must have finished combining the previous call from it
+        if (epoch > 1)
+            if (int e = tkb_wait_flags(fl + 2 * w, w, r, epoch - 1, stream)) return e;
+    }
+    if (int e = tkb_moe_dispatch_gemm(st->xq_rows[b], st->sg, st->codes, st->scales, W, W_sc, W_sg, st->Y[r], 0, static_cast<const int*>(st->pull_idx),
+                                      static_cast<const int*>(st->block_expert), static_cast<const int*>(st->num_blocks), fl, st->arrived, epoch,
+                                      st->H, st->I, El, st->cap_rows, r, w, comm_ctas, stream)) return e;
+    if (w > 1) {
+        if (int e = tkb_signal_peers(st->flags, w, r, w + r, epoch, 0, stream)) return e;      // my expert outputs are complete
+        if (int e = tkb_wait_flags(fl + w, w, r, epoch, stream)) return e;                    // everybody's are
+    }
+    if (int e = tkb_moe_combine(st->Y, 0, static_cast<const int*>(st->comb_idx), static_cast<const float*>(st->weights), out, Tl, st->top_k, st->I, w, stream))
+        return e;
+    if (w > 1)
+        if (int e = tkb_signal_peers(st->flags, w, r, 2 * w + r, epoch, 0, stream)) return e;   // done with the peers' tokens and outputs
+    return TKB_OK;
+}
+
 } // extern "C"

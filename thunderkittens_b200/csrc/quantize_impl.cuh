@@ -70,8 +70,12 @@ __device__ __forceinline__ void load_tile(const __nv_bfloat16* A, int64_t lda, i
 }
 
 // Bounded grid barrier on a QuantWork slot.  Returns the agreed per-tensor amax, or a negative
-// value when the wait ran out (status receives the timeout code).
-__device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status) {
+// value when a wait ran out (status receives the timeout code).
+// With an exchange (xch.world > 1) the last block to arrive also trades this GPU's maximum with the other
+// ranks over NVLink (one posted 64-bit store per peer, then bounded polls of its own slots) before it
+// releases the grid, so a row-sharded tensor is quantized with the amax of the whole tensor in one launch.
+constexpr unsigned int kAmaxFailed = 0xffffffffu;      // never a maximum of bf16 magnitudes (NaNs are dropped)
+__device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status, const QuantExchange& xch) {
     __shared__ float s_amax;
     __shared__ float s_warp[Q_THREADS / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -85,16 +89,40 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
         for (int w = 1; w < Q_THREADS / 32; w++) m = fmaxf(m, s_warp[w]);
         atomicMax(&ws->amax_bits, __float_as_uint(m));
         __threadfence();
-        atomicAdd(&ws->arrived, 1u);
+        const unsigned int prev = atomicAdd(&ws->arrived, 1u);
+        const bool exchange = xch.world > 1;
+        const unsigned int target = gridDim.x + (exchange ? 1u : 0u);
         const long long t0 = clock64();
+        if (exchange && prev == gridDim.x - 1) {
+            __threadfence();
+            float g = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(&ws->amax_bits));
+            const unsigned long long mine = (static_cast<unsigned long long>(xch.epoch) << 32) | __float_as_uint(g);
+            for (int pr = 0; pr < xch.world; pr++)
+                if (pr != xch.rank) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(xch.slots[pr] + xch.rank), "l"(mine) : "memory");
+            bool got_all = true;
+            for (int pr = 0; pr < xch.world && got_all; pr++) {
+                if (pr == xch.rank) continue;
+                unsigned long long got;
+                while (true) {
+                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(xch.slots[xch.rank] + pr) : "memory");
+                    if (int(unsigned(got >> 32) - xch.epoch) >= 0) break;
+                    if (clock64() - t0 > TKB_SPIN_LIMIT_CYCLES) { got_all = false; break; }
+                }
+                if (got_all) g = fmaxf(g, __uint_as_float(unsigned(got & 0xffffffffu)));
+            }
+            atomicMax(&ws->amax_bits, got_all ? __float_as_uint(g) : kAmaxFailed);
+            __threadfence();
+            atomicAdd(&ws->arrived, 1u);
+        }
         bool ok = true;
-        while (*reinterpret_cast<volatile unsigned int*>(&ws->arrived) < gridDim.x) {
-            if (clock64() - t0 > TKB_SPIN_LIMIT_CYCLES) { ok = false; break; }
+        while (*reinterpret_cast<volatile unsigned int*>(&ws->arrived) < target) {
+            if (clock64() - t0 > 2 * TKB_SPIN_LIMIT_CYCLES) { ok = false; break; }
         }
         __threadfence();
-        float r = ok ? __uint_as_float(*reinterpret_cast<volatile unsigned int*>(&ws->amax_bits)) : -1.0f;
+        const unsigned int bits = *reinterpret_cast<volatile unsigned int*>(&ws->amax_bits);
+        if (bits == kAmaxFailed) ok = false;
         if (!ok && status) atomicExch(status, 4 /* timeout */);
-        s_amax = r;
+        s_amax = ok ? __uint_as_float(bits) : -1.0f;
     }
     __syncthreads();
     return s_amax;
@@ -125,7 +153,7 @@ template <class Arith, bool SCALE_2D, bool FUSED_AMAX, bool RESIDENT>
 __global__ void __launch_bounds__(Q_THREADS)
 nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
-                      int M, int K, int* status, int sc_rowmajor, int64_t ldsc) {
+                      int M, int K, int* status, int sc_rowmajor, int64_t ldsc, const QuantExchange xch) {
     __shared__ __align__(16) uint8_t s_sc[2][2][512];   // [double buffer][chunk][byte]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
@@ -159,8 +187,11 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
                 for (int i = 0; i < 8; i++) local = fmaxf(local, fmaxf(amax8(v[i]), amax8(v2[i])));
             }
         }
-        amax = grid_amax_barrier(ws, local, status);
-        if (amax < 0.f) return;
+        amax = grid_amax_barrier(ws, local, status, xch);
+        if (amax < 0.f) {
+            if (threadIdx.x == 0) grid_amax_depart(ws);      // keep the slot usable for later calls
+            return;
+        }
     } else {
         amax = *amax_in;
     }
@@ -264,8 +295,7 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     float* sg = a.sg; const float* amax_in = a.amax_in; QuantWork* ws = a.ws; int M = a.M, K = a.K; int* status = a.status;
     int sc_rowmajor = a.sc_rowmajor;
     int64_t ldsc = a.ldsc;
-    void* params[] = {&A, &lda, &codes, &ldc, &sc, &sg, &amax_in, &ws, &M, &K, &status, &sc_rowmajor, &ldsc};
-    (void)params;
+    const QuantExchange xch = a.xch;
     // Programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream drains;
     // it executes griddepcontrol.wait before touching global memory.
     cudaLaunchConfig_t cfg = {};
@@ -274,7 +304,7 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor, ldsc);
+    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor, ldsc, xch);
 }
 
 // One tile per CTA with the whole grid resident (needed by the grid barrier)?

@@ -12,11 +12,20 @@ struct QuantWork {            // one slot of library-owned scratch per in-flight
     unsigned int pad;
 };
 
+// Row-sharded tensors: the per-tensor amax is max-reduced across the GPUs inside the quantize kernel (world <= 1: off).
+// slots[p] = rank p's array of `world` 64-bit words (epoch << 32 | amax bits), word r written by rank r.
+struct QuantExchange {
+    unsigned long long* slots[8];
+    int world, rank;
+    unsigned int epoch;
+};
+
 struct NvQuantArgs {
     const void* A; int64_t lda; void* codes; int64_t ldc; void* sc; float* sg; const float* amax_in; QuantWork* ws;
     int M, K, scale_2d; int* status; cudaStream_t stream; int sm_count;
     int sc_rowmajor;   // 0: 512-byte chunk layout (GEMM operand); 1: plain scale rows of K/16 bytes, ldsc bytes apart
     int64_t ldsc;
+    QuantExchange xch;
 };
 
 } // namespace tkb

@@ -124,10 +124,11 @@ class AllGatherMatmulNVFP4:
         # flags[0:world] = done (acknowledge) epochs; arrived[set] = arrival epochs of the row blocks, written by their owners
         self.flags = mk((local_world_size,), torch.int32)
         dev = self.flags.data_.device
-        self.arrived = [mk((M // 256,), torch.int32) for _ in range(2)]
+        self.arrived = [mk((M // 64,), torch.int32) for _ in range(2)]     # one arrival epoch per 64 gathered rows
         self.slots = [mk((local_world_size,), torch.int64) for _ in range(2)]   # (epoch, amax bits) per rank, see tkb_amax_allreduce
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.exit_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.epoch = 0
         self.rows = M // local_world_size
         st = L.AgState()
@@ -138,13 +139,15 @@ class AllGatherMatmulNVFP4:
                 st.arrived[b][i] = self.arrived[b].peer_ptr(i); st.slots[b][i] = self.slots[b].peer_ptr(i)
         for i in range(local_world_size):
             st.done[i] = self.flags.peer_ptr(i)
-        st.amax, st.sg = self.amax.data_ptr(), self.sg.data_ptr()
+        st.amax, st.sg, st.exit_counter = self.amax.data_ptr(), self.sg.data_ptr(), self.exit_counter.data_ptr()
         self._state = st
         if local_world_size > 1:
             dist.barrier(group=group)
 
     def __call__(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
-        """One library call per step (tkb_ag_linear_nvfp4); `step_by_step` below is the same sequence spelled out."""
+        """One library call, two launches per step (tkb_ag_linear_nvfp4): the quantize kernel max-reduces the amax across
+        the ranks itself and the GEMM kernel does the epoch hand-shake; `step_by_step` below spells the same step out
+        with one entry point per phase."""
         if tuple(X_local.shape) != (self.rows, self.K) or X_local.dtype != torch.bfloat16 or not X_local.is_contiguous():
             raise RuntimeError("X_local must be a contiguous bf16 tensor of shape (M / world, K)")
         n_local = W.shape[0]
@@ -176,7 +179,7 @@ class AllGatherMatmulNVFP4:
         ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, self.arithmetic, amax=self.amax)
         L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), self.sg.data_ptr(), W.data_ptr(), W_sc.data_ptr(),
                                       W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.arrived[b].peer_ptr_array(),
-                                      e, self.num_comm_sms, s))
+                                      None, None, e, self.num_comm_sms, s))
         if w > 1:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))      # my kernel of epoch e is done
 
@@ -244,10 +247,33 @@ class MoELayerNVFP4:
         self.amax, self.sg = z(1, dt=f32), z(1, dt=f32)
         self.out = torch.empty(self.Tl, I, dtype=torch.bfloat16, device=dev)
         self.epoch = 0
+        st = L.MoeState()
+        st.rank, st.world, st.T, st.H, st.I, st.E, st.top_k, st.cap_rows = r, w, T, H, I, E, top_k, self.cap_rows
+        for i in range(w):
+            for b in range(2):
+                st.xq_rows[b][i] = self.xq_rows[b].peer_ptr(i); st.slots[b][i] = self.slots[b].peer_ptr(i)
+                st.experts_all[b][i] = self.experts_all_sym[b].peer_ptr(i)
+            st.Y[i] = self.Y.peer_ptr(i); st.flags[i] = self.flags.peer_ptr(i); st.counters[i] = self.counters.peer_ptr(i)
+        for name in ("codes", "scales", "experts_local", "weights", "counts", "padded", "pull_idx", "block_expert", "num_blocks", "comb_idx",
+                     "arrived", "sg"):
+            setattr(st, name, getattr(self, name).data_ptr())
+        self._state = st
         if w > 1:
             dist.barrier(group=group)
 
     def forward(self, logits_local: torch.Tensor, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor) -> torch.Tensor:
+        """One library call per layer (tkb_moe_layer_nvfp4); `forward_step_by_step` spells the same sequence out."""
+        if tuple(logits_local.shape) != (self.Tl, self.E) or logits_local.dtype != torch.float32 or not logits_local.is_contiguous():
+            raise RuntimeError("logits_local must be a contiguous fp32 tensor of shape (T / world, E)")
+        if tuple(X_local.shape) != (self.Tl, self.H) or X_local.dtype != torch.bfloat16 or not X_local.is_contiguous():
+            raise RuntimeError("X_local must be a contiguous bf16 tensor of shape (T / world, H)")
+        self.epoch += 1
+        self.experts_all = self.experts_all_sym[self.epoch % 2].data_
+        L.check(L.lib().tkb_moe_layer_nvfp4(C.byref(self._state), self.epoch, logits_local.data_ptr(), X_local.data_ptr(), W.data_ptr(),
+                                            W_sc.data_ptr(), W_sg.data_ptr(), self.out.data_ptr(), self.num_comm_sms, self.arithmetic, _stream()))
+        return self.out
+
+    def forward_step_by_step(self, logits_local: torch.Tensor, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor) -> torch.Tensor:
         lib, s = L.lib(), _stream()
         w, r = self.world, self.rank
         self.epoch += 1
