@@ -195,7 +195,9 @@ def run_tp(args) -> None:
     n_local, rows = Nt // world, Mt // world
     u8 = torch.uint8
     GROUPS = 3
-    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=args.comm_sms)
+    # comm CTAs: 20 at 4 and 8 GPUs leaves 64 CTA pairs, which divide the 896 / 448 output tiles of a rank into whole waves
+    comm = args.comm_sms if args.comm_sms > 0 else (8 if world <= 2 else 20)
+    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=comm)
     sets = []
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     for gi in range(GROUPS):
@@ -321,7 +323,7 @@ def run_moe(args) -> None:
     T, H, I, E, k = 16384, 7168, 2048, 128, 8
     Tl, El = T // world, E // world
     u8 = torch.uint8
-    layer = parallel.MoELayerNVFP4(T, H, I, E, k, local_rank, world, num_comm_sms=args.comm_sms if args.comm_sms != 8 else 16)
+    layer = parallel.MoELayerNVFP4(T, H, I, E, k, local_rank, world, num_comm_sms=args.comm_sms if args.comm_sms > 0 else 32)
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     wc = torch.empty(El * I, H // 2, dtype=u8, device=dev); ws = torch.empty(El * I // 128, H // 64, 512, dtype=u8, device=dev)
     wg = torch.empty(1, dtype=torch.float32, device=dev)
@@ -637,7 +639,7 @@ def main() -> None:
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "moe"], help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer")
-    ap.add_argument("--comm-sms", type=int, default=8, help="CTAs of the tensor-parallel kernel that pull peer shards")
+    ap.add_argument("--comm-sms", type=int, default=0, help="CTAs of the multi-GPU kernels that move data over NVLink (0 = per-workload default)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

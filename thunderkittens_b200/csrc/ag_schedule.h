@@ -14,13 +14,16 @@
 namespace tkb {
 
 constexpr int kAgPartsPerBlock = 4;          // a 256-row block travels as 4 independently flagged 64-row parts
+constexpr int kAgFanOut = 4;                 // destinations served at the same time (one GPU pair alone did not fill the links:
+                                             // about 220 GB/s measured with every comm CTA writing to the same peer)
 
 struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock; };
 struct AgCursor { int u; int span; uint32_t o; };                 // unit, span (0 = codes, 1 = scales), bytes done in the span
 struct AgPiece { size_t off; uint32_t bytes, span_len; int span, dst_rank, flag; };
 
-// A unit is one 64-row part of one of this rank's 256-row blocks for one destination.  Units are numbered
-// destination-major, destinations in the order in which they consume this rank's rows (rank-1 first).
+// A unit is one 64-row part of one of this rank's 256-row blocks for one destination.  Destinations are taken in the
+// order in which they consume this rank's rows (rank-1 first), kAgFanOut of them at a time; inside such a group the
+// units alternate between the destinations, so consecutive comm CTAs write to different peers.
 TKB_HD int ag_units(const AgGeometry& g) { return (g.world - 1) * g.blocks_per_rank * kAgPartsPerBlock; }
 
 // The next piece (at most piece_bytes) at the cursor.  `off` is a byte offset into the gathered codes (span 0) or
@@ -28,8 +31,11 @@ TKB_HD int ag_units(const AgGeometry& g) { return (g.world - 1) * g.blocks_per_r
 TKB_HD AgPiece ag_piece(const AgGeometry& g, const AgCursor& c, uint32_t piece_bytes) {
     AgPiece pc;
     const int per_dst = g.blocks_per_rank * kAgPartsPerBlock;
-    pc.dst_rank = (g.rank + g.world - 1 - c.u / per_dst) % g.world;
-    const int in_dst = c.u % per_dst, b = in_dst / kAgPartsPerBlock, part = in_dst % kAgPartsPerBlock;
+    const int first = (c.u / (kAgFanOut * per_dst)) * kAgFanOut;          // first destination (consumption order) of the unit's group
+    const int gsize = g.world - 1 - first < kAgFanOut ? g.world - 1 - first : kAgFanOut;
+    const int v = c.u - first * per_dst;                                  // unit inside the group
+    pc.dst_rank = (g.rank + g.world - 1 - (first + v % gsize)) % g.world;
+    const int in_dst = v / gsize, b = in_dst / kAgPartsPerBlock, part = in_dst % kAgPartsPerBlock;
     const size_t row0 = (size_t(g.rank) * g.blocks_per_rank + b) * 256;
     pc.span = c.span;
     if (c.span == 0) {                       // codes of 64 rows: contiguous

@@ -199,6 +199,8 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
     return TKB_OK;
 }
 
+unsigned long long* api_profile_buffer() { return g_prof; }
+
 int api_device(int* sm_count, int** status) {
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;

@@ -18,7 +18,8 @@
 namespace tkb {
 
 int api_fail(int code, const char* fmt, ...);          // api.cu
-int api_device(int* sm_count, int** status);           // api.cu
+int api_device(int* sm_count, int** status);
+unsigned long long* api_profile_buffer();             // api.cu: tkb_gemm_set_profile_buffer           // api.cu
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
 
@@ -217,6 +218,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     g.sgA = X_sg; g.sgB = W_sg; g.M = M; g.N = N_local; g.K = K; g.status = status; g.sm_count = sm;
     g.stream = static_cast<cudaStream_t>(stream);
     g.mode = MODE_AG;
+    g.prof = api_profile_buffer();
     for (int i = 0; i < world; i++) {
         g.comm.ag.peer_codes[i] = static_cast<const uint8_t*>(peer_codes[i]);
         g.comm.ag.peer_scales[i] = static_cast<const uint8_t*>(peer_scales[i]);

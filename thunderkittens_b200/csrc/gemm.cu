@@ -122,95 +122,80 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
                  ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
 }
 
-// One comm CTA (a single thread of it): PUSHES its share of this rank's quantized rows into the peers' buffers.
-// Reads are local (fast), the NVLink side is posted writes, so a handful of CTAs can fill the links; a pull over
-// NVLink is limited per SM by the read round trip.
+// One comm CTA: PUSHES its share of this rank's quantized rows into the peers' buffers with plain loads (local) and
+// stores (NVLink, posted).  The load/store units keep far more remote writes in flight per SM than the bulk-copy engine
+// does (measured here: about 11 GB/s per CTA with 16 KB bulk stores to a peer), so a handful of CTAs can fill the links;
+// a pull over NVLink would be limited per SM by the read round trip.
 //   * A unit is one 64-row part of a 256-row block for one destination: the codes of those rows (contiguous) and
-//     a quarter of the block's scale bytes.  Units are numbered destination-major, destinations in the order in
-//     which they will consume this rank's rows (rank-1 first), and dealt round-robin to the comm CTAs, so all of
-//     them work for the destination that needs the data first.
-//   * Pieces of up to PIECE bytes flow through a ring in shared memory: loads run up to AHEAD pieces in front of
-//     the store cursor across span and unit boundaries, so the pipe never drains between units.
-//   * When all bytes of a unit have been written (bulk-group completion, a few stores later so that the pipe
-//     keeps moving), a system-scope release store publishes the epoch in the destination's `arrived` array.
+//     a quarter of the block's scale bytes.  Destinations are served in the order in which they will consume this
+//     rank's rows (rank-1 first), four at a time, and the units are dealt round-robin to the comm CTAs, so
+//     neighbouring CTAs write to different peers (ag_schedule.h).
+//   * Warps 1.. copy (16 bytes per lane, UNROLL loads in flight per lane); warp 0 publishes: after the CTA barrier
+//     that ends a unit, its lane 0 makes the unit's stores visible system-wide (fence) and stores the epoch into the
+//     destination's `arrived` array while the other warps already copy the next unit.
 //   * With peer_done set, the first store to a destination waits until that rank's kernel of epoch-2 (the last
 //     reader of the buffer set being overwritten) has finished.
-template <int RING, int PIECE>
-__device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, uint32_t smem, uint64_t* bars,
-                        const WaitCtx& wc) {
-    // bars[0..RING) are "piece landed in shared memory" barriers.  Up to AHEAD loads are in flight in front of the
-    // store cursor and up to RING - AHEAD stores may still be reading their slots behind it.
-    constexpr int AHEAD = RING - 3;
-    constexpr int LAG = 3;                    // a unit is published once LAG younger stores have been issued
-    constexpr int PEND = 4;
-    static_assert(RING >= 6, "ring too small");
+// prof (optional, 8 counters of this CTA, written by thread 0): [0] total cycles, [1] waiting for done flags,
+// [2] fence + flag store.
+__device__ __forceinline__ uint4 ld_nc_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void ag_copy_span(const uint8_t* src, uint8_t* dst, uint32_t bytes, int t, int nthr) {
+    constexpr int UNROLL = 16;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const uint32_t n = bytes / 16;
+    for (uint32_t base = 0; base < n; base += uint32_t(nthr) * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int i = 0; i < UNROLL; i++) {
+            const uint32_t idx = base + uint32_t(i * nthr + t);
+            if (idx < n) v[i] = ld_nc_v4(s4 + idx);
+        }
+#pragma unroll
+        for (int i = 0; i < UNROLL; i++) {
+            const uint32_t idx = base + uint32_t(i * nthr + t);
+            if (idx < n) d4[idx] = v[i];
+        }
+    }
+}
+__device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, const WaitCtx& wc, unsigned long long* prof) {
     const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock};
     const int units = ag_units(geo);
     const unsigned int* done = ag.peer_done[ag.rank];
-    AgCursor lc{comm_idx, 0, 0u}, sc{comm_idx, 0, 0u};
-    uint32_t issued = 0, stored = 0;         // piece counters over the whole kernel (ring position / phase)
-    uint32_t pend_at[PEND]; unsigned int* pend_flag[PEND];
-    int pend_head = 0, pend_n = 0;
+    const int tid = threadIdx.x, nthr = int(blockDim.x) - 32;
+    long long t_done = 0, t_pub = 0;
+    const long long t_begin = clock64();
     int checked_dst = -1;
-    bool ok = true;
-    while (sc.u < units) {
-        if (lc.u < units && issued - stored < AHEAD) {
-            // slots about to be refilled were last read by stores at least RING - AHEAD groups ago
-            tma_store_wait_read<RING - AHEAD - 1>();
-            while (lc.u < units && issued - stored < AHEAD) {
-                const AgPiece pc = ag_piece(geo, lc, PIECE);
-                const uint32_t slot = issued % RING;
-                mbar_arrive_expect_tx(smem_u32(&bars[slot]), pc.bytes);
-                bulk_load(smem + slot * PIECE, (pc.span == 0 ? ag.codes : ag.scales) + pc.off, pc.bytes, smem_u32(&bars[slot]));
-                issued++;
-                ag_advance(lc, pc, ag.comm_ctas);
+    for (int u = comm_idx; u < units; u += ag.comm_ctas) {
+        // whole spans as single pieces: the cursor arithmetic is the one the host-side enumeration checks
+        const AgPiece codes = ag_piece(geo, AgCursor{u, 0, 0u}, 0xffffffffu);
+        const AgPiece scales = ag_piece(geo, AgCursor{u, 1, 0u}, 0xffffffffu);
+        if (codes.dst_rank != checked_dst) {                 // uniform over the CTA
+            if (tid == 0 && done != nullptr && ag.epoch > 2u) {
+                const long long t0 = clock64();
+                flag_wait(wc, done + codes.dst_rank, ag.epoch - 2u);      // on timeout: abort flag + status, read below
+                t_done += clock64() - t0;
             }
+            __syncthreads();
+            if (*wc.abort_flag) break;                        // every thread reads it after the same barrier
+            checked_dst = codes.dst_rank;
         }
-        const AgPiece pc = ag_piece(geo, sc, PIECE);
-        if (done != nullptr && pc.dst_rank != checked_dst) {
-            if (ag.epoch > 2u && !flag_wait(wc, done + pc.dst_rank, ag.epoch - 2u)) { ok = false; break; }
-            checked_dst = pc.dst_rank;
+        if (tid >= 32) {
+            ag_copy_span(ag.codes + codes.off, const_cast<uint8_t*>(ag.peer_codes[codes.dst_rank]) + codes.off, codes.bytes, tid - 32, nthr);
+            ag_copy_span(ag.scales + scales.off, const_cast<uint8_t*>(ag.peer_scales[scales.dst_rank]) + scales.off, scales.bytes, tid - 32, nthr);
         }
-        const uint32_t slot = stored % RING;
-        if (!mbar_wait(wc, smem_u32(&bars[slot]), (stored / RING) & 1)) { ok = false; break; }
-        bulk_store(const_cast<uint8_t*>(pc.span == 0 ? ag.peer_codes[pc.dst_rank] : ag.peer_scales[pc.dst_rank]) + pc.off, smem + slot * PIECE, pc.bytes);
-        tma_store_commit();
-        stored++;
-        if (ag_advance(sc, pc, ag.comm_ctas)) {
-            if (pend_n == PEND) {                       // cannot happen with units of more than one piece; keeps the queue safe
-                tma_store_wait<0>();
-                __threadfence_system();
-                while (pend_n > 0) {
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
-                    pend_head = (pend_head + 1) % PEND; pend_n--;
-                }
-            }
-            const int tail = (pend_head + pend_n) % PEND;
-            pend_at[tail] = stored;
-            pend_flag[tail] = ag.peer_arrived[pc.dst_rank] + pc.flag;
-            pend_n++;
-        }
-        if (pend_n > 0 && stored - pend_at[pend_head] >= uint32_t(LAG)) {
-            tma_store_wait<LAG>();                      // every store older than the LAG youngest has been written
-            __threadfence_system();
-            while (pend_n > 0 && stored - pend_at[pend_head] >= uint32_t(LAG)) {
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
-                pend_head = (pend_head + 1) % PEND; pend_n--;
-            }
+        __syncthreads();                                      // the unit's stores have been issued by every copy warp
+        if (tid == 0) {
+            const long long t0 = clock64();
+            __threadfence_system();                           // cumulative over the stores ordered before the barrier
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.peer_arrived[codes.dst_rank] + codes.flag), "r"(ag.epoch) : "memory");
+            t_pub += clock64() - t0;
         }
     }
-    if (!ok) {
-        // gave up on a wait: let the copies that are still in flight into this CTA's shared memory land before leaving
-        for (uint32_t i = stored; i < issued; i++) mbar_wait(wc, smem_u32(&bars[i % RING]), (i / RING) & 1);
-    }
-    tma_store_wait<0>();
-    if (ok && pend_n > 0) {
-        __threadfence_system();
-        while (pend_n > 0) {
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pend_flag[pend_head]), "r"(ag.epoch) : "memory");
-            pend_head = (pend_head + 1) % PEND; pend_n--;
-        }
-    }
+    if (prof && tid == 0) { prof[0] = clock64() - t_begin; prof[1] = t_done; prof[2] = t_pub; prof[3] = 0; prof[4] = 0; }
 }
 
 // Every CTA of the all-gather kernel calls this (one thread) when it has finished: the last one to arrive tells the
@@ -344,7 +329,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __shared__ __align__(8) uint64_t bar_tmem_empty;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : (MODE == MODE_AG ? 13 : 1)];   // comm CTAs of the MoE / all-gather modes
+    __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : 1];   // comm CTAs of the MoE / all-gather modes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0;
@@ -408,17 +393,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     if constexpr (AG) {
         if (is_comm) {
-            if (threadIdx.x == 0) {
-                // the (idle) operand ring and epilogue staging of this CTA serve as the piece ring
-                constexpr int PIECE = 16384;
-                constexpr int RING = 13;
-                static_assert(RING * PIECE <= C::STAGES * C::STAGE_BYTES + C::EPI_BYTES, "staging ring does not fit");
-                for (int i = 0; i < RING; i++) mbar_init(smem_u32(&bar_comm[i]), 1);
-                fence_mbar_init();
-                ag_push<RING, PIECE>(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, smem_base, bar_comm, wc);
-                ag_exit(ag);
-            }
+            ag_push(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, wc, p.prof ? p.prof + blockIdx.x * 8 : nullptr);
             __syncthreads();
+            if (threadIdx.x == 0) ag_exit(ag);
             cluster_sync();      // matches the teardown barrier of the compute clusters' code path below
             return;
         }
@@ -429,7 +406,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            long long waited = 0;
+            long long waited = 0, waited_flags = 0;
             asm volatile("griddepcontrol.wait;" ::: "memory");      // operands may come from the previous kernel in the stream
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
@@ -447,10 +424,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if constexpr (AG) {
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
+                        const long long t0 = clock64();
                         for (int part = 0; part < kAgPartsPerBlock && ok; part++)
                             ok = flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk * kAgPartsPerBlock + part, ag.epoch);
                         if (!ok) break;
                         fence_proxy_async_all();
+                        waited_flags += clock64() - t0;
                     }
                 }
                 for (int kb = 0; kb < num_kb; kb++) {
@@ -485,7 +464,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            if (p.prof) { p.prof[blockIdx.x * 8 + 0] = waited; p.prof[blockIdx.x * 8 + 1] = clock64() - t_begin; }
+            if (p.prof) { p.prof[blockIdx.x * 8 + 0] = waited; p.prof[blockIdx.x * 8 + 1] = clock64() - t_begin; p.prof[blockIdx.x * 8 + 7] = waited_flags; }
             // tail: do not leave while stage releases from the MMA thread may still be in flight
             for (int s = 0; s < C::STAGES && ok; s++) {
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);

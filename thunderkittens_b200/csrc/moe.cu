@@ -22,6 +22,7 @@ namespace tkb {
 
 int api_fail(int code, const char* fmt, ...);
 int api_device(int* sm_count, int** status);
+unsigned long long* api_profile_buffer();             // api.cu: tkb_gemm_set_profile_buffer
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);
 
@@ -268,6 +269,7 @@ int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes
     g.sgA = X_sg; g.sgB = W_sg; g.M = cap_rows; g.N = I; g.K = K; g.status = status; g.sm_count = sm;
     g.stream = static_cast<cudaStream_t>(stream);
     g.mode = MODE_MOE;
+    g.prof = api_profile_buffer();
     MoeParams& m = g.comm.moe;
     for (int i = 0; i < world; i++) m.peer_rows[i] = static_cast<const uint8_t*>(peer_rows[i]);
     m.codes = static_cast<uint8_t*>(codes); m.scales = static_cast<uint8_t*>(scales);
