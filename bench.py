@@ -44,63 +44,66 @@ def measured_peaks() -> dict:
 
 # ----------------------------------------------------------------------------- clocks ------
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons through NVML (read-only) from a background thread while a
-    timed region runs; the timed loops here last only milliseconds, too short for `nvidia-smi -lms`."""
+    """SM clock, power and throttle reasons through NVML (read-only), sampled DURING the timed region by the measuring
+    thread itself: between the moment the timed loop has been enqueued and the moment its end event completes, while
+    the GPU is still working through the queue.  Nothing is sampled while the host is launching: NVML queries take a
+    driver lock that delays kernel launches (a background sampler at 0.5 ms made a two-launch step of the tensor-parallel
+    loop about 100 us slower)."""
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, nvml=None):
         self.index = index
-        self.samples = []          # (sm_mhz, power_w, reasons_mask)
+        self.samples = []          # (sm_mhz, power_w, reasons_mask), all taken while the timed work was in flight
+        self.idle_sample = None    # one sample after the region, used only if the region was too short to catch any
         self.max_mhz = None
-        self._stop = False
-        self._thread = None
         self._h = None
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            if nvml is None:
+                import pynvml as nvml
+                nvml.nvmlInit()
+            self._nv = nvml
+            self._h = nvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(nvml.nvmlDeviceGetMaxClockInfo(self._h, nvml.NVML_CLOCK_SM))
         except Exception:
             self._h = None
 
-    def _loop(self):
+    def _read(self):
         nv = self._nv
-        while not self._stop:
-            try:
-                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
-                pw = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
-                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
-                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-                self.samples.append((float(mhz), pw, int(rs)))
-            except Exception:
-                break
-            time.sleep(0.0005)
+        mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+        pw = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+        rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+            else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+        return (float(mhz), float(pw), int(rs))
+
+    def poll_until(self, done, limit_s: float = 120.0) -> None:
+        """Samples until done() is true (the end event of the timed loop has completed)."""
+        if self._h is None:
+            return
+        t0 = time.time()
+        try:
+            while not done() and time.time() - t0 < limit_s:
+                self.samples.append(self._read())
+            self.idle_sample = self._read()
+        except Exception:
+            self._h = None
 
     def __enter__(self):
-        if self._h is not None:
-            import threading
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
         return self
 
     def __exit__(self, *a):
-        self._stop = True
-        if self._thread is not None:
-            self._thread.join(timeout=2)
+        return False
 
     def summary(self) -> dict:
-        if not self.samples:
+        use = self.samples or ([self.idle_sample] if self.idle_sample else [])
+        if not use:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
-        power = [p for _, p, _ in self.samples]
-        thr = (min(power) + max(power)) / 2
-        loaded = [c for c, p, _ in self.samples if p >= thr] or [c for c, _, _ in self.samples]
         mask = 0
-        for _, _, r in self.samples:
+        for _, _, r in use:
             mask |= r
-        return {"sm_mhz": statistics.median(loaded), "sm_min_mhz": min(c for c, _, _ in self.samples), "sm_max_mhz": self.max_mhz,
+        return {"sm_mhz": statistics.median(c for c, _, _ in use), "sm_min_mhz": min(c for c, _, _ in use), "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(n for b, n in self.REASONS.items() if mask & b), "samples": len(self.samples),
-                "power_w_max": max(power)}
+                "power_w_max": max(p for _, p, _ in use),
+                "when": "while the timed loop was executing on the GPU" if self.samples else "right after the timed loop (too short to sample)"}
 
 
 # ----------------------------------------------------------------------------- CPU arm -----
@@ -164,7 +167,7 @@ def synth(torch, dev, rows, cols, seed, std=1.0, outliers=0.0):
     return x.to(torch.bfloat16)
 
 
-def event_time(torch, fn, steps, cooldown=0.5):
+def event_time(torch, fn, steps, cooldown=0.5, sampler=None):
     """CUDA-event time per step on the current stream.  A 500 ms idle period precedes the timed loop, as in the
     reference's own protocol (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:673-700), so the loop starts from the
     same thermal/power state every time."""
@@ -175,6 +178,8 @@ def event_time(torch, fn, steps, cooldown=0.5):
     for i in range(steps):
         fn(i)
     e.record()
+    if sampler is not None:
+        sampler.poll_until(e.query)       # clocks while the GPU works through the queue; the host launches are over
     torch.cuda.synchronize()
     return s.elapsed_time(e) * 1e-3 / steps
 
@@ -226,8 +231,8 @@ def run_tp(args) -> None:
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
-    with ClockSampler(local_rank) as cs:
-        dt = event_time(torch, step, args.steps)
+    cs = ClockSampler(local_rank)
+    dt = event_time(torch, step, args.steps, sampler=cs)
     clocks = cs.summary()
     assert _lib.device_status() == 0, "a device-side wait timed out"
     t = torch.tensor([dt], device=dev, dtype=torch.float64)
@@ -378,9 +383,90 @@ def run_moe(args) -> None:
         dist.destroy_process_group()
 
 
+def run_tp_timeline(args) -> None:
+    """Diagnostic for the tensor-parallel step (N > 1, torchrun): CUDA events around each of the two launches of a step
+    inside a free-running loop, plus the kernels' own wait counters (tkb_gemm_set_profile_buffer) for the last step of
+    the loop.  Prints one JSON line from rank 0 and one from rank world/2.  Not a benchmark line."""
+    import ctypes
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib as L, parallel
+
+    rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    Mt, Nt, Kt = 8192, 28672, 8192
+    nl, rows = Nt // world, Mt // world
+    lib, s = L.lib(), torch.cuda.current_stream().cuda_stream
+    comm = args.comm_sms if args.comm_sms > 0 else (8 if world <= 2 else 20)
+    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local, world, num_comm_sms=comm)
+    X = synth(torch, dev, rows, Kt, 700 + rank)
+    W = synth(torch, dev, nl, Kt, 800 + rank, std=0.02)
+    u8 = torch.uint8
+    wc = torch.empty(nl, Kt // 2, dtype=u8, device=dev); ws = torch.empty((nl + 127) // 128, Kt // 64, 512, dtype=u8, device=dev)
+    wg = torch.empty(1, dtype=torch.float32, device=dev)
+    ops.nvfp4_quantize(W, wc, ws, wg, False)
+    D = torch.empty(Mt, nl, dtype=torch.bfloat16, device=dev)
+    arith = ops._ARITH[ops.default_nvfp4_arithmetic]
+
+    def two(ev=None):       # the two launches of tkb_ag_linear_nvfp4, issued one by one so that an event fits in between
+        op.epoch += 1
+        e, b = op.epoch, op.epoch % 2
+        codes, scales = op.codes[b], op.scales[b]
+        mc = codes.data_[rank * rows:(rank + 1) * rows]; ms = scales.data_[rank * rows // 128:(rank + 1) * rows // 128]
+        if ev:
+            ev[0].record()
+        L.check(lib.tkb_nvfp4_quantize_sharded(X.data_ptr(), 0, mc.data_ptr(), ms.data_ptr(), op.sg.data_ptr(), rows, Kt, 0, arith,
+                                               op.slots[b].peer_ptr_array(), world, rank, e, s))
+        if ev:
+            ev[1].record()
+        L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), op.sg.data_ptr(), wc.data_ptr(), ws.data_ptr(), wg.data_ptr(),
+                                      D.data_ptr(), 0, Mt, nl, Kt, rank, world, op.arrived[b].peer_ptr_array(), op.flags.peer_ptr_array(),
+                                      op.exit_counter.data_ptr(), e, op.num_comm_sms, s))
+        if ev:
+            ev[2].record()
+
+    for _ in range(max(args.warmup, 3)):
+        two()
+    torch.cuda.synchronize(); dist.barrier()
+    prof = torch.zeros(148 * 8, dtype=torch.int64, device=dev)
+    setp = L.bind("tkb_gemm_set_profile_buffer", [ctypes.c_void_p])
+    setp(prof.data_ptr())
+    steps = max(args.steps, 4)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for i in range(steps):
+        two(evs[i])
+    torch.cuda.synchronize()
+    setp(None)
+    q = np.array([evs[i][0].elapsed_time(evs[i][1]) for i in range(steps)]) * 1e3
+    g = np.array([evs[i][1].elapsed_time(evs[i][2]) for i in range(steps)]) * 1e3
+    pr = prof.cpu().numpy().reshape(148, 8)
+    lead = pr[op.num_comm_sms::2]
+    lead = lead[lead[:, 4] > 0]
+    if len(lead) == 0:
+        lead = np.zeros((1, 8), np.int64)
+    med = lambda a: float(np.median(a))
+    out = {"rank": rank, "n_gpus": world, "comm_ctas": op.num_comm_sms, "step_us": evs[0][0].elapsed_time(evs[-1][2]) * 1e3 / steps,
+           "quantize_us_median_max": [med(q), float(q.max())], "ag_gemm_us_median_max": [med(g), float(g.max())],
+           "cycles_of_last_step": {"mma_total": med(lead[:, 4]), "mma_waiting_for_operands": med(lead[:, 3]), "mma_waiting_for_drain": med(lead[:, 2]),
+                                   "producer_waiting_for_remote_rows": med(lead[:, 7]), "comm_cta_total": med(pr[:op.num_comm_sms, 0]),
+                                   "comm_cta_waiting_done_flags": med(pr[:op.num_comm_sms, 1]), "comm_cta_fence_and_flag": med(pr[:op.num_comm_sms, 2])},
+           "device_status": L.device_status()}
+    if rank in (0, world // 2):
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    op.close()
+    dist.destroy_process_group()
+
+
 def run_ours(args) -> None:
     if args.workload == "moe":
         return run_moe(args)
+    if args.workload == "tp_timeline":
+        return run_tp_timeline(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         return run_tp(args)
     import torch
@@ -423,8 +509,8 @@ def run_ours(args) -> None:
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
-    with ClockSampler(local_rank) as cs:
-        dt = event_time(torch, step, args.steps)
+    cs = ClockSampler(local_rank)
+    dt = event_time(torch, step, args.steps, sampler=cs)
     clocks = cs.summary()
     assert _lib.device_status() == 0, "a device-side wait timed out"
     if world > 1:
@@ -638,7 +724,8 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=None)
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
-    ap.add_argument("--workload", default="auto", choices=["auto", "moe"], help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer")
+    ap.add_argument("--workload", default="auto", choices=["auto", "moe", "tp_timeline"],
+                    help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
     ap.add_argument("--comm-sms", type=int, default=0, help="CTAs of the multi-GPU kernels that move data over NVLink (0 = per-workload default)")
     args = ap.parse_args()
     if args.case:
