@@ -8,8 +8,11 @@ One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one
           UE8M0 scales, fp32 accumulate, bf16 out).  `value` = TFLOP/s of the GEMM with operands resident in HBM;
           `e2e` = the same FLOPs through the C-ABI calls a user makes, starting from bf16 matrices in pinned HOST
           memory: H2D copies, both quantize launches, the GEMM and the D2H copy of D are all inside the timed region.
-  N > 1   workload = tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192 (tp.py), strong scaling; until a rank count is
-          supported by the TP path the ranks run independent replicas of the N=1 workload ("replicas", weak).
+  N > 1   workload = tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192 (weights N-sharded, activation rows sharded and
+          all-gathered over NVLink inside the GEMM kernel), strong scaling; the line also carries the time of the same
+          whole problem on one GPU.  `--workload moe` runs the expert-parallel MoE layer instead.
+  `--case <kernel>` runs one kernel only (the commands of the ncu summaries under profiles/), `--workload tp_timeline`
+  prints per-launch times and the kernels' wait counters of the tensor-parallel step.
 
 `--impl reference` times the reference's CPU implementation of the same GEMM arithmetic — its own naive kernels from
 kernels/gemm/common.cuh compiled for the host (oracle/_ref) when that build exists, otherwise the oracle's C++
@@ -543,6 +546,9 @@ def run_ours(args) -> None:
     extras = {}
     if rank == 0 and not args.no_extra:
         extras = side_measurements(torch, ops, dev)
+        if world == 1:
+            torch.cuda.synchronize()
+            extras["reference_gpu_kernels_8192"] = reference_gpu_kernels()
 
     if rank == 0:
         pk = measured_peaks()
@@ -578,6 +584,71 @@ def run_ours(args) -> None:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 8192^3 MXFP8 GEMM (ncu capture summarised in
 # profiles/mxfp8_gemm_ncu.md): 348.0 MB read + 116.8 MB written.
 MXFP8_GEMM_DRAM_BYTES = 464.8e6
+
+
+# The reference's own GPU kernels (built from its tree into oracle/_ref/tk_<which> by oracle/build.py:build_ref_gpu) timed with
+# the same protocol as this library's (CUDA events, 3 rotating operand sets, 500 ms idle first).  Runs in a child process: the
+# reference's modules are both called `_C`.  Single-GPU only (the reference kernels issue cluster-multicast TMA loads).
+REF_GPU_CHILD = r"""
+import sys, os, json, glob, time, importlib.util
+ROOT, which = sys.argv[1], sys.argv[2]
+import torch
+so = glob.glob(os.path.join(ROOT, "oracle", "_ref", f"tk_{which}", "_C*.so"))[0]
+spec = importlib.util.spec_from_file_location("_C", so); ref = importlib.util.module_from_spec(spec); spec.loader.exec_module(ref)
+dev = torch.device("cuda:0"); u8 = torch.uint8
+M = N = K = 8192
+def timed(fn, steps=10):
+    for i in range(3): fn(i)
+    s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(); time.sleep(0.5)
+    s.record()
+    for i in range(steps): fn(i)
+    e.record(); torch.cuda.synchronize()
+    return s.elapsed_time(e) * 1e3 / steps
+sets = []
+for gi in range(3):
+    g = torch.Generator(device=dev).manual_seed(21 + gi)
+    A = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+    B = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    if which == "nvfp4":
+        def q(X):
+            c = torch.empty(X.shape[0], K // 2, dtype=torch.float4_e2m1fn_x2, device=dev); sc = torch.empty(X.shape[0] // 128, K // 64, 512, dtype=torch.float8_e4m3fn, device=dev)
+            gg = torch.empty(1, device=dev); ref.nvfp4_quantize(X, c, sc, gg, False); return c, sc, gg
+    else:
+        def q(X):
+            c = torch.empty(X.shape[0], K, dtype=torch.float8_e4m3fn, device=dev); sc = torch.empty(X.shape[0] // 128, K // 128, 32, 16, dtype=u8, device=dev)
+            ref.mxfp8_quantize(X, c, sc); return c, sc
+    sets.append((A, q(A), q(B), torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+    del B
+torch.cuda.synchronize()
+out = {}
+if which == "nvfp4":
+    out["gemm_us"] = timed(lambda i: ref.nvfp4_gemm(*sets[i % 3][1], *sets[i % 3][2], sets[i % 3][3]))
+    out["quantize_us"] = timed(lambda i: ref.nvfp4_quantize(sets[i % 3][0], *sets[i % 3][1], False))
+else:
+    out["gemm_us"] = timed(lambda i: ref.mxfp8_gemm(*sets[i % 3][1], *sets[i % 3][2], sets[i % 3][3]))
+    out["quantize_us"] = timed(lambda i: ref.mxfp8_quantize(sets[i % 3][0], *sets[i % 3][1]))
+out["gemm_tflops"] = 2.0 * M * N * K / out["gemm_us"] * 1e-6
+print("RESULT " + json.dumps(out))
+"""
+
+
+def reference_gpu_kernels() -> dict:
+    """8192^3 GEMM and 8192 x 8192 quantize times of the reference's own sm_100a kernels, when they were built."""
+    import glob
+    import subprocess
+    out = {}
+    for which in ("nvfp4", "mxfp8"):
+        if not glob.glob(os.path.join(ROOT, "oracle", "_ref", f"tk_{which}", "_C*.so")):
+            out[which] = {"unavailable": "reference GPU kernels not built (oracle/build.py:build_ref_gpu needs the reference tree)"}
+            continue
+        try:
+            r = subprocess.run([sys.executable, "-c", REF_GPU_CHILD, ROOT, which], capture_output=True, text=True, timeout=240)
+            lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+            out[which] = json.loads(lines[-1][7:]) if r.returncode == 0 and lines else {"unavailable": (r.stderr or "no output")[-300:]}
+        except Exception as e:      # a comparison aid: never fails the benchmark line
+            out[which] = {"unavailable": repr(e)[:300]}
+    return out
 
 
 def side_measurements(torch, ops, dev) -> dict:
