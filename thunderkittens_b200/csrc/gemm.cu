@@ -74,9 +74,10 @@ struct GemmParams {
 
 // All-gather mode (tensor-parallel GEMM): the A operand is row-sharded over `world` GPUs.  Every rank
 // keeps a full-size buffer for the gathered codes and scales and quantizes its own shard into its own
-// slice; `comm_ctas` CTAs of this kernel pull the other slices from the owners' buffers over NVLink
-// (plain bulk copies through shared memory, no multicast) while the remaining CTAs multiply, own rows
-// first, then the other shards in the order they are pulled.
+// slice; `comm_ctas` CTAs of this kernel push that slice into every peer's buffers over NVLink (plain
+// loads and stores, no multicast) while the remaining CTAs multiply, own rows first, then the other
+// shards in the order in which they arrive.
+
 // tile index -> (row block, column block).  `group` row-blocks share a sweep over the columns (L2
 // reuse); `rot` rotates the row-block order (all-gather mode starts with the rank's own rows).
 __device__ __forceinline__ void tile_to_block(int tile, int tiles_m, int tiles_n, int group, int rot, int& m_blk, int& n_blk) {
