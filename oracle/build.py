@@ -73,12 +73,14 @@ def build_ref() -> str | None:
     # host driver never calls; strip it so that g++ can parse the file.  Kernel bodies are untouched.
     text = open(common).read()
     stripped = re.sub(r"<<<[^>]*>>>", "", text)
-    gen = os.path.join(REF_OUT, "common_host.cuh")
-    with open(gen, "w") as f:
-        f.write(stripped)
-    _run(["g++", "-O2", "-march=x86-64-v3", "-ffp-contract=fast", "-fopenmp", "-shared", "-fPIC", "-std=c++20",
-          "-x", "c++", "-I", os.path.join(HERE, "ref_shim"), "-I", os.path.join(CUDA_HOME, "include"),
-          f'-DREF_COMMON_CUH="{gen}"', driver, "-o", out])
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:     # the stripped copy of the reference header never stays in this tree
+        gen = os.path.join(tmp, "common_host.cuh")
+        with open(gen, "w") as f:
+            f.write(stripped)
+        _run(["g++", "-O2", "-march=x86-64-v3", "-ffp-contract=fast", "-fopenmp", "-shared", "-fPIC", "-std=c++20",
+              "-x", "c++", "-I", os.path.join(HERE, "ref_shim"), "-I", os.path.join(CUDA_HOME, "include"),
+              f'-DREF_COMMON_CUH="{gen}"', driver, "-o", out])
     return out
 
 
