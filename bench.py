@@ -643,7 +643,7 @@ def reference_gpu_kernels() -> dict:
             out[which] = {"unavailable": "reference GPU kernels not built (oracle/build.py:build_ref_gpu needs the reference tree)"}
             continue
         try:
-            r = subprocess.run([sys.executable, "-c", REF_GPU_CHILD, ROOT, which], capture_output=True, text=True, timeout=240)
+            r = subprocess.run([sys.executable, "-c", REF_GPU_CHILD, ROOT, which], capture_output=True, text=True, timeout=150)
             lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
             out[which] = json.loads(lines[-1][7:]) if r.returncode == 0 and lines else {"unavailable": (r.stderr or "no output")[-300:]}
         except Exception as e:      # a comparison aid: never fails the benchmark line
