@@ -1,6 +1,6 @@
 """Generates the committed golden fixtures in this folder from the REFERENCE's own Python specs.
 
-Run once, in a container where the ThunderKittens tree is mounted (default /root/reference):
+Run once, in a container where the ThunderKittens tree is mounted (its location: environment variable TK_REFERENCE):
 
     python tests/golden/make_golden.py
 
