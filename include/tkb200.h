@@ -153,6 +153,14 @@ int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* 
 int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
                      int config, void* stream);
 
+/* Replaces the standalone dense fp8 GEMM (kernels/gemm/fp8_b200/fp8_b200_gemm.cu: the bf16 kernel with e4m3 operands,
+ * checked at l.298 against reference_gemm<fp8e4m3, bf16>).  A [M, K], B [N, K] e4m3 bytes, lda/ldb in bytes (0 = K),
+ * fp32 accumulation, bf16 out; K % 16 == 0, N % 8 == 0.
+ * State: written and compiled, not yet run on a GPU; no GPU test covers it yet. */
+int tkb_fp8_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream);
+int tkb_fp8_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
+                    int config, void* stream);
+
 /* ---- single-node multi-GPU plumbing ------------------------------------------------------------
  * Replaces, for this path, TKParallelTensor / KittensBroker (include/pyutils/parallel_tensor.cuh:23-336,
  * include/pyutils/broker.cuh:340-547) and the device-side signal / wait helpers

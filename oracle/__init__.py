@@ -55,6 +55,7 @@ def lib():
         L.tko_nvfp4_gemm_f32.argtypes = [_u8p, _u8p, _f32p, _u8p, _u8p, _f32p, _f32p] + [C.c_int] * 4
         L.tko_mxfp8_gemm.argtypes = [_u8p, _u8p, _u8p, _u8p, _u16p] + [C.c_int] * 5
         L.tko_bf16_gemm.argtypes = [_u16p, _u16p, _u16p] + [C.c_int] * 5
+        L.tko_fp8_gemm.argtypes = [_u8p, _u8p, _u16p] + [C.c_int] * 5
         L.tko_moe_route.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _i32p, _f32p]
         L.tko_moe_schedule.restype = C.c_int
         L.tko_moe_schedule.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p,
@@ -91,6 +92,7 @@ def ref_host():
         L.tkref_nvfp4_gemm.argtypes = [_u8p, _u8p, _f32p, _u8p, _u8p, _f32p, _u16p] + [C.c_int] * 3
         L.tkref_mxfp8_gemm.argtypes = [_u8p, _u8p, _u8p, _u8p, _u16p] + [C.c_int] * 3
         L.tkref_bf16_gemm.argtypes = [_u16p, _u16p, _u16p] + [C.c_int] * 3
+        L.tkref_fp8_gemm.argtypes = [_u8p, _u8p, _u16p] + [C.c_int] * 3
         L.tkref_fill_uniform_f32.argtypes = [_f32p, C.c_size_t, C.c_uint64, C.c_float, C.c_float]
         L.tkref_scale_swizzle_idx.restype = C.c_int
         L.tkref_scale_swizzle_idx.argtypes = [C.c_int] * 3
@@ -241,6 +243,16 @@ def bf16_gemm(A, B, row0: int = 0, nrows: int | None = None) -> np.ndarray:
     nrows = M - row0 if nrows is None else nrows
     D = np.empty((nrows, N), np.uint16)
     lib().tko_bf16_gemm(np.ascontiguousarray(A, np.uint16), np.ascontiguousarray(B, np.uint16), D, M, N, K, row0, nrows)
+    return D
+
+
+def fp8_gemm(A, B, row0: int = 0, nrows: int | None = None) -> np.ndarray:
+    """Dense e4m3 x e4m3 GEMM, fp32 accumulation in ascending k, bf16 out (tko_fp8_gemm)."""
+    M, K = A.shape
+    N = B.shape[0]
+    nrows = M - row0 if nrows is None else nrows
+    D = np.empty((nrows, N), np.uint16)
+    lib().tko_fp8_gemm(np.ascontiguousarray(A, np.uint8), np.ascontiguousarray(B, np.uint8), D, M, N, K, row0, nrows)
     return D
 
 

@@ -5,11 +5,12 @@
 // thread of the <<<grid, block>>> launch becomes one iteration of a loop that sets the emulated
 // blockIdx/threadIdx.  common.cuh is compiled from where it lies in the reference tree; the only
 // change is made on the fly by oracle/build.py, which strips the `<<<...>>>` launch syntax
-// from the (unused here) launcher wrappers so a host compiler can parse the file.  The generated
-// intermediate and the shared object go to oracle/_ref/ and are never committed.
+// from the (unused here) launcher wrappers so a host compiler can parse the file.  The stripped
+// intermediate lives in a temporary directory; the shared object goes to oracle/_ref/ and is never
+// committed.
 #define KITTENS_BLACKWELL 1
 #include "kittens.cuh"
-#include REF_COMMON_CUH   // set by the build recipe to the stripped copy under oracle/_ref/
+#include REF_COMMON_CUH   // set by the build recipe to the stripped temporary copy
 
 thread_local dim3 blockIdx, threadIdx, blockDim, gridDim;
 
@@ -54,6 +55,14 @@ void tkref_bf16_gemm(const void* A, const void* B, void* D, int M, int N, int K)
     launch2d(M, N, [&] {
         reference_gemm_kernel<__nv_bfloat16, __nv_bfloat16, true>((__nv_bfloat16*)D, (const __nv_bfloat16*)A,
                                                                   (const __nv_bfloat16*)B, M, N, K);
+    });
+}
+
+// fp8 (e4m3) dense GEMM as kernels/gemm/fp8_b200/fp8_b200_gemm.cu:298 checks it
+void tkref_fp8_gemm(const void* A, const void* B, void* D, int M, int N, int K) {
+    launch2d(M, N, [&] {
+        reference_gemm_kernel<__nv_fp8_e4m3, __nv_bfloat16, true>((__nv_bfloat16*)D, (const __nv_fp8_e4m3*)A,
+                                                                  (const __nv_fp8_e4m3*)B, M, N, K);
     });
 }
 

@@ -417,6 +417,16 @@ void tko_bf16_gemm(const uint16_t* A, const uint16_t* B, uint16_t* D, int M, int
     gemm_slab(D, N, K, row0, nrows, 1.0f, deq(A), deq(B));
 }
 
+// reference_gemm_kernel<fp8e4m3, bf16, transpose_b=true>: the oracle of the reference's dense fp8 GEMM
+// (kernels/gemm/fp8_b200/fp8_b200_gemm.cu:298 over kernels/gemm/common.cuh:73-98)
+void tko_fp8_gemm(const uint8_t* A, const uint8_t* B, uint16_t* D, int M, int N, int K, int row0, int nrows) {
+    (void)M;
+    auto deq = [K](const uint8_t* X) {
+        return [=](int row, float* out) { for (int k = 0; k < K; k++) out[k] = e4m3_to_f32(X[size_t(row) * K + k]); };
+    };
+    gemm_slab(D, N, K, row0, nrows, 1.0f, deq(A), deq(B));
+}
+
 // Same arithmetic as tko_nvfp4_gemm with fp32 output (no final rounding) — used for the relative
 // Frobenius-error gate, where the reference result is "dequantize then fp32 accumulate".
 void tko_nvfp4_gemm_f32(const uint8_t* A, const uint8_t* A_sc, const float* A_sg,

@@ -51,6 +51,16 @@ def test_bf16_gemm_bit_exact_vs_reference_kernel(ref):
     assert np.array_equal(D, Dr)
 
 
+def test_fp8_gemm_bit_exact_vs_reference_kernel(ref):
+    rng = np.random.default_rng(16)
+    A = O.f32_to_e4m3(rng.standard_normal((96, 256)).astype(np.float32))
+    B = O.f32_to_e4m3((rng.standard_normal((80, 256)) * 0.5).astype(np.float32))
+    D = O.fp8_gemm(A, B)
+    Dr = np.empty((96, 80), np.uint16)
+    ref.tkref_fp8_gemm(A, B, Dr, 96, 80, 256)
+    assert np.array_equal(D, Dr)
+
+
 def test_slab_equals_full(ref):
     A, B = _inputs(256, 128, 256, 14)
     ac, asc, asg = O.nvfp4_quantize(A)

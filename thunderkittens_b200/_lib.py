@@ -61,6 +61,8 @@ _SIGNATURES = {
                                _i, _i, _i, _i, _i, _i, _i, _vp], _i),
     "tkb_moe_layer_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
+    "tkb_fp8_gemm": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp], _i),
+    "tkb_fp8_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
 

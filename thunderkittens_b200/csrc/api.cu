@@ -179,7 +179,7 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
     const uint64_t inner = kind == KIND_NVFP4 ? uint64_t(K / 2) : uint64_t(K);
     if (int e = make_operand_map(&g.tmA, A, dt, elem_bytes, inner, M, lda_bytes, 128)) return e;
     if (int e = make_operand_map(&g.tmB, B, dt, elem_bytes, inner, N, ldb_bytes, bn / ctas)) return e;
-    if (kind != KIND_BF16) {
+    if (kind == KIND_NVFP4 || kind == KIND_MXFP8) {
         const int kc = kind == KIND_NVFP4 ? K / 64 : K / 128;
         const int per_stage = kind == KIND_NVFP4 ? 4 : 1;
         if (int e = make_scale_map(&g.tmSA, A_sc, (M + 127) / 128, kc, per_stage)) return e;
@@ -219,14 +219,14 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
     if (config < 0 || config > TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
     if (config == TKB_GEMM_SKINNY && (kind != KIND_NVFP4 || M > 128))
         return fail(TKB_ERR_INVALID_ARG, "gemm: the skinny-M kernel needs NVFP4 operands and M <= 128");
-    const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : 8);
+    const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : (kind == KIND_FP8 ? 16 : 8));
     if (K % kmult) return fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
     if (N % 8) return fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
     if (ldd == 0) ldd = N;
     if (ldd < N || ldd % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
     if (!aligned16(A) || !aligned16(B) || !aligned16(D) || lda_bytes % 16 || ldb_bytes % 16)
         return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
-    if (kind != KIND_BF16) {
+    if (kind == KIND_NVFP4 || kind == KIND_MXFP8) {
         if (!A_sc || !B_sc) return fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
         if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
     }
@@ -398,6 +398,17 @@ int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, voi
 }
 int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {
     return tkb_bf16_gemm_ex(A, lda, B, ldb, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
+}
+int tkb_fp8_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, int config,
+                    void* stream) {
+    if (lda == 0) lda = K;
+    if (ldb == 0) ldb = K;
+    if (lda < K || ldb < K) return fail(TKB_ERR_INVALID_ARG, "fp8_gemm: lda/ldb must be >= K");
+    if (config == TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "fp8_gemm: no skinny-M kernel for this format");
+    return gemm_common(KIND_FP8, A, lda, nullptr, nullptr, B, ldb, nullptr, nullptr, D, ldd, M, N, K, config, stream);
+}
+int tkb_fp8_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {
+    return tkb_fp8_gemm_ex(A, lda, B, ldb, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
 }
 
 } // extern "C"

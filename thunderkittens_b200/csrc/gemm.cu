@@ -5,6 +5,7 @@
 //   KIND_MXFP8 : e4m3 codes, one ue8m0 scale per 32 K-elements
 //                (replaces mxfp8_gemm::kernel, kernels/gemm/mxfp8_b200/mxfp8_b200_gemm.cu:83-292)
 //   KIND_BF16  : dense control (replaces kernel<C>, kernels/gemm/bf16_b200/bf16_b200_gemm.cu:61-253)
+//   KIND_FP8   : dense e4m3 (replaces kernels/gemm/fp8_b200/fp8_b200_gemm.cu, the bf16 kernel with 8-bit operands)
 //
 // Design (one CTA per SM, persistent over output tiles):
 //   * A stage of the operand ring always holds exactly 128 bytes of K per row (64 bf16, 128 e4m3,
@@ -38,7 +39,7 @@ struct GemmCfg {
     static_assert(BN == 128 || BN == 256, "");
     static constexpr int BM = 128 * CTAS;                 // rows of D per cluster tile
     static constexpr int BN_CTA = BN / CTAS;              // rows of B each CTA loads
-    static constexpr int KB = KIND == KIND_BF16 ? 64 : (KIND == KIND_MXFP8 ? 128 : 256);   // K elements per stage
+    static constexpr int KB = KIND == KIND_BF16 ? 64 : (KIND == KIND_NVFP4 ? 256 : 128);   // K elements per stage (128 bytes)
     static constexpr int A_BYTES = 128 * 128;
     static constexpr int B_BYTES = BN_CTA * 128;
     static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP8 ? 1 : 0);  // 512-byte chunks per 128 rows per stage
@@ -315,7 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
             const __grid_constant__ CUtensorMap tmD, const GemmParams p, const CommParams cp) {
     using C = GemmCfg<KIND, CTAS, BN>;
-    constexpr bool SCALED = KIND != KIND_BF16;
+    constexpr bool SCALED = KIND == KIND_NVFP4 || KIND == KIND_MXFP8;
     constexpr bool AG = MODE == MODE_AG;
     constexpr bool MOE = MODE == MODE_MOE;
     static_assert(!AG || (KIND == KIND_NVFP4 && CTAS == 2 && BN == 256), "all-gather mode: NVFP4, CTA pairs, N tile 256");
@@ -510,6 +511,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         // +32 bytes of K inside the 128-byte swizzle panel = +2 in the (addr >> 4) field
                         if constexpr (KIND == KIND_BF16) {
                             mma_f16<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::BM, BN), acc);
+                        } else if constexpr (KIND == KIND_FP8) {
+                            mma_f8<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_fp8(C::BM, BN), acc);
                         } else if constexpr (KIND == KIND_MXFP8) {
                             mma_mxfp8<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::BM, BN, j), acc, sfa_t, sfb_t);
                         } else {
@@ -659,6 +662,7 @@ cudaError_t launch_gemm(const GemmArgs& a) {
         case KIND_BF16: return launch_k<KIND_BF16>(a);
         case KIND_MXFP8: return launch_k<KIND_MXFP8>(a);
         case KIND_NVFP4: return launch_k<KIND_NVFP4>(a);
+        case KIND_FP8: return launch_k<KIND_FP8>(a);
         default: return cudaErrorInvalidValue;
     }
 }

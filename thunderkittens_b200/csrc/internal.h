@@ -6,7 +6,7 @@
 
 namespace tkb {
 
-enum GemmKind : int { KIND_BF16 = 0, KIND_MXFP8 = 1, KIND_NVFP4 = 2 };
+enum GemmKind : int { KIND_BF16 = 0, KIND_MXFP8 = 1, KIND_NVFP4 = 2, KIND_FP8 = 3 };   // FP8: dense e4m3, no scales
 
 struct QuantWork;
 struct NvQuantArgs;
@@ -50,7 +50,7 @@ enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2 };
 struct CommParams { AgParams ag; MoeParams moe; };
 
 struct GemmArgs {
-    int kind;                 // 0 bf16, 1 mxfp8, 2 nvfp4
+    int kind;                 // GemmKind
     int config;               // bit 0: 0 = CTA pair (cta_group::2), 1 = single CTA; bit 1: 0 = N tile 256, 1 = N tile 128
     CUtensorMap tmA, tmB, tmSA, tmSB, tmD;   // tmD: bf16 output, box 64 columns x 32 rows, 128-byte swizzle
     const float* sgA; const float* sgB;

@@ -138,3 +138,14 @@ def bf16_gemm(A, B, D, config: str | None = None) -> None:
     if B.shape[1] != K or tuple(D.shape) != (M, N):
         raise RuntimeError("shape mismatch: A (M,K), B (N,K), D (M,N)")
     L.check(L.lib().tkb_bf16_gemm_ex(A.data_ptr(), 0, B.data_ptr(), 0, D.data_ptr(), 0, M, N, K, _CONFIG[config], _stream()))
+
+
+def fp8_gemm(A, B, D, config: str | None = None) -> None:
+    """D = A @ B.T with dense e4m3 operands (kernels/gemm/fp8_b200 in the reference; standalone-only there)."""
+    e4m3 = (torch.uint8, torch.float8_e4m3fn)
+    _chk(A, "A", e4m3, 2); _chk(B, "B", e4m3, 2); _chk(D, "D", (torch.bfloat16,), 2)
+    M, K = A.shape
+    N = B.shape[0]
+    if B.shape[1] != K or tuple(D.shape) != (M, N):
+        raise RuntimeError("shape mismatch: A (M,K), B (N,K), D (M,N)")
+    L.check(L.lib().tkb_fp8_gemm_ex(A.data_ptr(), 0, B.data_ptr(), 0, D.data_ptr(), 0, M, N, K, _CONFIG[config], _stream()))
