@@ -458,6 +458,34 @@ def run_tp_timeline(args) -> None:
                                    "producer_waiting_for_remote_rows": med(lead[:, 7]), "comm_cta_total": med(pr[:op.num_comm_sms, 0]),
                                    "comm_cta_waiting_done_flags": med(pr[:op.num_comm_sms, 1]), "comm_cta_fence_and_flag": med(pr[:op.num_comm_sms, 2])},
            "device_status": L.device_status()}
+    # The exchange alone: the same two launches with only 256 weight rows, so that the multiplying CTAs have next to
+    # nothing to do and the fused kernel lasts as long as the pushes (bytes in per GPU: (world-1)/world * M * K * 0.5625).
+    n_small = 256
+    Ds = torch.empty(Mt, n_small, dtype=torch.bfloat16, device=dev)
+
+    def push_only(ev):
+        op.epoch += 1
+        e, b = op.epoch, op.epoch % 2
+        codes, scales = op.codes[b], op.scales[b]
+        mc = codes.data_[rank * rows:(rank + 1) * rows]; ms = scales.data_[rank * rows // 128:(rank + 1) * rows // 128]
+        L.check(lib.tkb_nvfp4_quantize_sharded(X.data_ptr(), 0, mc.data_ptr(), ms.data_ptr(), op.sg.data_ptr(), rows, Kt, 0, arith,
+                                               op.slots[b].peer_ptr_array(), world, rank, e, s))
+        ev[0].record()
+        L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), op.sg.data_ptr(), wc.data_ptr(), ws.data_ptr(), wg.data_ptr(),
+                                      Ds.data_ptr(), 0, Mt, n_small, Kt, rank, world, op.arrived[b].peer_ptr_array(), op.flags.peer_ptr_array(),
+                                      op.exit_counter.data_ptr(), e, op.num_comm_sms, s))
+        ev[1].record()
+
+    dist.barrier()
+    pe = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(6)]
+    for i in range(6):
+        push_only(pe[i])
+    torch.cuda.synchronize()
+    pt = np.array([pe[i][0].elapsed_time(pe[i][1]) for i in range(2, 6)]) * 1e3
+    bytes_in = (world - 1) / world * Mt * (Kt // 2 + Kt // 16)
+    out["exchange_alone_us_median"] = med(pt)
+    out["exchange_alone_gbs_in_per_gpu"] = bytes_in / (med(pt) * 1e-6) * 1e-9
+    out["device_status"] = L.device_status()
     if rank in (0, world // 2):
         print(json.dumps(out), flush=True)
     dist.barrier()
