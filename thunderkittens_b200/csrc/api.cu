@@ -212,8 +212,7 @@ int api_device(int* sm_count, int** status) {
 static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A_sc, const float* A_sg, const void* B,
                        int64_t ldb_bytes, const void* B_sc, const float* B_sg, void* D, int64_t ldd, int M, int N, int K, int config,
                        void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
+    // pure argument errors first: they are reported the same way with or without a device
     if (!A || !B || !D) return fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
     if (M < 1 || N < 1 || K < 1) return fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (config < 0 || config > TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
@@ -231,6 +230,8 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
         if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
     }
     if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
 
     if (kind == KIND_NVFP4 && M <= 128 && (config == TKB_GEMM_DEFAULT || config == TKB_GEMM_SKINNY))
         return decode_common(c, A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, stream);
@@ -249,8 +250,6 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
 static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
                                  int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0, const QuantExchange* xch = nullptr) {
     // sc_rowmajor: codes and scales share one row of K/2 + K/16 bytes (codes first); `sc` is ignored
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
     if (sc_rowmajor) sc = static_cast<uint8_t*>(codes) + K / 2;
     if (!A || !codes || !sc || !sg) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
     if (M < 1 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: need M >= 1 and K a positive multiple of 64 (got M=%d K=%d)", M, K);
@@ -258,16 +257,16 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     if (lda == 0) lda = K;
     if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: lda must be >= K and a multiple of 8 elements");
     if (!aligned16(A) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: buffers must be 16-byte aligned");
+    if (xch && amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: the cross-rank amax exchange belongs to the fused-amax kernel (no amax input)");
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
     NvQuantArgs a;
     a.A = A; a.lda = lda; a.codes = codes; a.ldc = sc_rowmajor ? K / 2 + K / 16 : K / 2; a.ldsc = K / 2 + K / 16; a.sc = sc; a.sg = sg; a.amax_in = amax;
     a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
     a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
     a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count; a.sc_rowmajor = sc_rowmajor;
     memset(&a.xch, 0, sizeof(a.xch));
-    if (xch) {
-        if (amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: the cross-rank amax exchange belongs to the fused-amax kernel (no amax input)");
-        a.xch = *xch;
-    }
+    if (xch) a.xch = *xch;
     TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
     return TKB_OK;
 }
@@ -330,12 +329,12 @@ int tkb_nvfp4_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, voi
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
     if (!A_bf16 || !amax) return fail(TKB_ERR_INVALID_ARG, "absmax: null pointer");
     if (M < 1 || K < 8 || K % 8) return fail(TKB_ERR_INVALID_ARG, "absmax: need M >= 1 and K a positive multiple of 8");
     if (lda == 0) lda = K;
     if (lda < K || lda % 8 || !aligned16(A_bf16)) return fail(TKB_ERR_BAD_ALIGNMENT, "absmax: A must be 16-byte aligned with lda %% 8 == 0");
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     TKB_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), s));
     TKB_CUDA(launch_absmax(A_bf16, lda, M, K, reinterpret_cast<unsigned int*>(amax), c->sm_count, s));
@@ -343,32 +342,32 @@ int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, 
 }
 
 int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, int M, int K, void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
     if (!A_bf16 || !codes || !sc) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: null pointer");
     if (M < 1 || K < 128 || K % 128) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: need M >= 1 and K a positive multiple of 128 (got M=%d K=%d)", M, K);
     if (lda == 0) lda = K;
     if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: lda must be >= K and a multiple of 8 elements");
     if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
     TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
     return TKB_OK;
 }
 
 int tkb_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
     if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp32_to_fp4x2: null pointer");
     if (reinterpret_cast<uintptr_t>(in) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp32_to_fp4x2: input must be 8-byte aligned");
     if (n_pairs == 0) return TKB_OK;
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
     TKB_CUDA(launch_fp32_to_fp4x2(in, out, n_pairs, static_cast<cudaStream_t>(stream)));
     return TKB_OK;
 }
 int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream) {
-    DeviceCtx* c;
-    if (int e = get_ctx(&c)) return e;
     if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp4x2_to_fp32: null pointer");
     if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp4x2_to_fp32: output must be 8-byte aligned");
     if (n_pairs == 0) return TKB_OK;
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
     TKB_CUDA(launch_fp4x2_to_fp32(in, out, n_pairs, static_cast<cudaStream_t>(stream)));
     return TKB_OK;
 }

@@ -152,9 +152,9 @@ int tkb_signal_peers(void* const* peer_flags, int world, int rank, int index, un
 }
 
 int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, void* stream) {
+    if (!flags || count < 1 || count > 1024) return api_fail(TKB_ERR_INVALID_ARG, "wait_flags: bad arguments");
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
-    if (!flags || count < 1 || count > 1024) return api_fail(TKB_ERR_INVALID_ARG, "wait_flags: bad arguments");
     wait_flags_kernel<<<1, ((count + 31) / 32) * 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(flags), count, skip,
                                                                                          value, status);
     TKB_CUDA_C(cudaGetLastError());
@@ -162,10 +162,10 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
 }
 
 int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned int epoch, const float* local, float* out, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!peer_slots || !local || !out || world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
         return api_fail(TKB_ERR_INVALID_ARG, "amax_allreduce: bad arguments (world must be 1..%d)", kMaxWorld);
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     PeerSlots ps;
     for (int i = 0; i < kMaxWorld; i++) ps.p[i] = i < world ? static_cast<unsigned long long*>(peer_slots[i]) : nullptr;
     amax_allreduce_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps, world, rank, epoch, local, out, status);
@@ -175,12 +175,12 @@ int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned in
 
 int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer, int gather, int rank, int world, void* const* peer_counters,
                    int counter_base, unsigned int epoch, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!peer_out || !in || !peer_counters || world < 1 || world > kMaxWorld || rank < 0 || rank >= world || bytes_per_peer == 0 || counter_base < 0)
         return api_fail(TKB_ERR_INVALID_ARG, "all_to_all: bad arguments (world must be 1..%d)", kMaxWorld);
     if ((reinterpret_cast<uintptr_t>(in) & 15u) || (bytes_per_peer & 15u))
         return api_fail(TKB_ERR_BAD_ALIGNMENT, "all_to_all: input and chunk size must be 16-byte aligned");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     PeerBytes pb; PeerPtrs pc;
     for (int i = 0; i < kMaxWorld; i++) {
         pb.p[i] = i < world ? static_cast<unsigned char*>(peer_out[i]) : nullptr;
@@ -200,13 +200,13 @@ int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer,
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
                       void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!peer_codes || !peer_scales || !X_sg || !W || !W_sc || !W_sg || !D || !peer_arrived)
         return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world must be 1..%d", kMaxWorld);
-    if (M % (256 * world)) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: M=%d must be a multiple of 256 * world", M);
-    if (K % 64 || N_local % 8) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: K %% 64 and N %% 8 must be 0");
+    if (M < 1 || M % (256 * world)) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: M=%d must be a positive multiple of 256 * world", M);
+    if (K < 64 || K % 64 || N_local < 8 || N_local % 8) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: K %% 64 and N %% 8 must be 0");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     if (comm_ctas < 0 || comm_ctas % 2 || comm_ctas > sm - 2) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: comm_ctas must be even and leave compute CTAs");
     if (world > 1 && comm_ctas == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world > 1 needs comm_ctas >= 2");
     if (peer_done && !exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: peer_done needs an exit counter");

@@ -203,11 +203,11 @@ using namespace tkb;
 extern "C" {
 
 int tkb_moe_route(const float* logits, int T, int E, int top_k, int* experts, float* weights, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!logits || !experts || !weights) return api_fail(TKB_ERR_INVALID_ARG, "moe_route: null pointer");
     if (T < 1 || E % 32 || E < 32 || E > 256 || top_k < 1 || top_k > 32 || top_k > E)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_route: need E in {32,..,256} (multiple of 32) and 1 <= top_k <= 32");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int blocks = (T + 7) / 8;
     switch (E / 32) {
@@ -226,12 +226,12 @@ int tkb_moe_route(const float* logits, int T, int E, int top_k, int* experts, fl
 
 int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world, int rank, int* counts, int* padded_per_expert,
                      int* pull_idx, int* block_expert, int* num_blocks, int* comb_idx, int cap_rows, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!experts_all || !counts || !padded_per_expert || !pull_idx || !block_expert || !num_blocks || !comb_idx)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_schedule: null pointer");
-    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E % world || T % world || cap_rows % 128 || top_k < 1)
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E < 1 || T < 1 || E % world || T % world || cap_rows % 128 || top_k < 1)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_schedule: E and T must divide by world (<= %d), cap_rows by 128", kMaxWorld);
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     moe_count_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, counts, padded_per_expert);
     moe_assign_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, top_k, E, world, rank, T / world, counts, padded_per_expert, pull_idx,
@@ -244,13 +244,14 @@ int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes
                           const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
                           const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,
                           int I, int experts_local, int cap_rows, int rank, int world, int comm_ctas, void* stream) {
-    int sm; int* status;
-    if (int e = api_device(&sm, &status)) return e;
     if (!peer_rows || !X_sg || !codes || !scales || !W || !W_sc || !W_sg || !Y || !pull_idx || !block_expert ||
         !num_blocks || !ready || !arrived)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: bad rank/world");
-    if (K % 256 || I % 128 || cap_rows % 128 || cap_rows < 128) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
+    if (K < 256 || K % 256 || I < 128 || I % 128 || cap_rows % 128 || cap_rows < 128)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
     // dispatch staging per comm CTA: a block's scales (128 x K/16 bytes), a zero row and at least 12 row slots; one thread per 64 K-elements
     if (128 * (K / 16) + K / 2 + 128 + 12 * (K / 2 + K / 16) > 190 * 1024 || K / 64 + 1 > 320)
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
