@@ -298,6 +298,10 @@ typedef struct tkb_moe_state {
 int tkb_moe_layer_nvfp4(const tkb_moe_state* st, unsigned int epoch, const float* logits_local, const void* X_local_bf16, const void* W,
                         const void* W_sc, const float* W_sg, void* out, int comm_ctas, int arithmetic, void* stream);
 
+/* For bindings that mirror the state structs by hand (ctypes, cgo, JNI ...): which = 0 tkb_ag_state, 1 tkb_moe_state;
+ * field 0 = sizeof, field i >= 1 = offsetof the i-th member in declaration order; -1 past the last member.  Host only. */
+int tkb_debug_struct_layout(int which, int field);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,3 +43,17 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text and "tk_oracle" not in text, f
+
+
+def test_ctypes_mirrors_of_the_state_structs_match_the_header(lib):
+    """thunderkittens_b200/_lib.py mirrors tkb_ag_state and tkb_moe_state by hand: size and every member offset must
+    equal what the C compiler laid out (tkb_debug_struct_layout)."""
+    from thunderkittens_b200 import _lib
+    f = lib.tkb_debug_struct_layout
+    f.argtypes = [ctypes.c_int, ctypes.c_int]
+    f.restype = ctypes.c_int
+    for which, mirror in ((0, _lib.AgState), (1, _lib.MoeState)):
+        assert f(which, 0) == ctypes.sizeof(mirror)
+        for i, (name, *_rest) in enumerate(mirror._fields_, start=1):
+            assert f(which, i) == getattr(mirror, name).offset, (mirror.__name__, name)
+        assert f(which, len(mirror._fields_) + 1) == -1      # the mirror lists every member

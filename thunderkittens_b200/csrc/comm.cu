@@ -9,6 +9,7 @@
 //     Python layer), so there are no fixed shared-memory or socket names to collide on;
 //   * flags are 32-bit epochs in those buffers, written across GPUs with system-scope release stores
 //     and read with bounded acquire spins; nothing uses multicast or multimem.
+#include <cstddef>
 #include <cstring>
 #include "../../include/tkb200.h"
 #include "internal.h"
@@ -237,6 +238,37 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
     TKB_CUDA_C(launch_gemm(g));
     return TKB_OK;
+}
+
+int tkb_debug_struct_layout(int which, int field) {
+    // sizeof / offsetof of the state structs of the C ABI, for bindings that mirror them by hand
+#define TKB_OFF(T, m) case __COUNTER__ - base: return int(offsetof(T, m));
+    if (which == 0) {
+        if (field == 0) return int(sizeof(tkb_ag_state));
+        enum { base = __COUNTER__ };
+        switch (field) {
+            TKB_OFF(tkb_ag_state, rank) TKB_OFF(tkb_ag_state, world) TKB_OFF(tkb_ag_state, M) TKB_OFF(tkb_ag_state, K)
+            TKB_OFF(tkb_ag_state, codes) TKB_OFF(tkb_ag_state, scales) TKB_OFF(tkb_ag_state, arrived) TKB_OFF(tkb_ag_state, slots)
+            TKB_OFF(tkb_ag_state, done) TKB_OFF(tkb_ag_state, amax) TKB_OFF(tkb_ag_state, sg) TKB_OFF(tkb_ag_state, exit_counter)
+            default: return -1;
+        }
+    }
+    if (which == 1) {
+        if (field == 0) return int(sizeof(tkb_moe_state));
+        enum { base = __COUNTER__ };
+        switch (field) {
+            TKB_OFF(tkb_moe_state, rank) TKB_OFF(tkb_moe_state, world) TKB_OFF(tkb_moe_state, T) TKB_OFF(tkb_moe_state, H)
+            TKB_OFF(tkb_moe_state, I) TKB_OFF(tkb_moe_state, E) TKB_OFF(tkb_moe_state, top_k) TKB_OFF(tkb_moe_state, cap_rows)
+            TKB_OFF(tkb_moe_state, xq_rows) TKB_OFF(tkb_moe_state, slots) TKB_OFF(tkb_moe_state, experts_all) TKB_OFF(tkb_moe_state, Y)
+            TKB_OFF(tkb_moe_state, flags) TKB_OFF(tkb_moe_state, counters) TKB_OFF(tkb_moe_state, codes) TKB_OFF(tkb_moe_state, scales)
+            TKB_OFF(tkb_moe_state, experts_local) TKB_OFF(tkb_moe_state, weights) TKB_OFF(tkb_moe_state, counts) TKB_OFF(tkb_moe_state, padded)
+            TKB_OFF(tkb_moe_state, pull_idx) TKB_OFF(tkb_moe_state, block_expert) TKB_OFF(tkb_moe_state, num_blocks)
+            TKB_OFF(tkb_moe_state, comb_idx) TKB_OFF(tkb_moe_state, arrived) TKB_OFF(tkb_moe_state, sg)
+            default: return -1;
+        }
+    }
+#undef TKB_OFF
+    return -1;
 }
 
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces) {
