@@ -55,6 +55,17 @@ class FakeLib:
     def tkb_last_error(self):
         return b""
 
+    # the single-call entry points: record what the host layer hands to the library
+    def tkb_ag_linear_nvfp4(self, st, epoch, X, W, W_sc, W_sg, D, ldd, n_local, comm, arith, stream):
+        self.calls = getattr(self, "calls", []) + [("ag_linear", int(epoch), int(n_local), int(comm), int(arith))]
+        self.last_state = st._obj
+        return 0
+
+    def tkb_moe_layer_nvfp4(self, st, epoch, logits, X, W, W_sc, W_sg, out, comm, arith, stream):
+        self.calls = getattr(self, "calls", []) + [("moe_layer", int(epoch), int(comm), int(arith))]
+        self.last_state = st._obj
+        return 0
+
 
 def _worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
@@ -112,6 +123,39 @@ def _worker(rank, world, port, q):
     arr = t.peer_ptr_array()
     res["peer_array"] = [int(arr[i]) for i in range(world)]
     t.close.__func__   # exists
+    # ---- 4. the layer objects hand complete peer tables to the single-call entry points
+    parallel._stream = lambda: 0
+    op = parallel.AllGatherMatmulNVFP4(256 * world, 256, rank, world, num_comm_sms=5)
+    st = op._state
+    ok = (st.rank, st.world, st.M, st.K) == (rank, world, 256 * world, 256) and op.num_comm_sms == 4      # rounded down to whole CTA pairs
+    for b in range(2):
+        for i in range(world):
+            ok = ok and st.codes[b][i] == op.codes[b].peer_ptr(i) and st.scales[b][i] == op.scales[b].peer_ptr(i)
+            ok = ok and st.arrived[b][i] == op.arrived[b].peer_ptr(i) and st.slots[b][i] == op.slots[b].peer_ptr(i)
+    ok = ok and all(st.done[i] == op.flags.peer_ptr(i) for i in range(world)) and st.exit_counter == op.exit_counter.data_ptr()
+    ok = ok and op.arrived[0].shape_ == (256 * world // 64,)
+    Xl = torch.zeros(256, 256, dtype=torch.bfloat16); Wq = torch.zeros(128, 128, dtype=torch.uint8)
+    Wsc = torch.zeros(1, 4, 512, dtype=torch.uint8); Wsg = torch.zeros(1); Dd = torch.zeros(256 * world, 128, dtype=torch.bfloat16)
+    op(Xl, Wq, Wsc, Wsg, Dd); op(Xl, Wq, Wsc, Wsg, Dd)
+    res["ag_calls"] = [c for c in fake.calls if c[0] == "ag_linear"]
+    try:
+        op(Xl[:100], Wq, Wsc, Wsg, Dd)
+        ok = False
+    except RuntimeError:
+        pass
+    res["ag_state"] = ok
+    layer = parallel.MoELayerNVFP4(128 * world, 256, 128, 16 * world, 2, rank, world, num_comm_sms=6)
+    ms = layer._state
+    ok = (ms.rank, ms.world, ms.T, ms.H, ms.I, ms.E, ms.top_k, ms.cap_rows) == (rank, world, 128 * world, 256, 128, 16 * world, 2, layer.cap_rows)
+    for i in range(world):
+        for b in range(2):
+            ok = ok and ms.xq_rows[b][i] == layer.xq_rows[b].peer_ptr(i) and ms.slots[b][i] == layer.slots[b].peer_ptr(i)
+            ok = ok and ms.experts_all[b][i] == layer.experts_all_sym[b].peer_ptr(i)
+        ok = ok and ms.Y[i] == layer.Y.peer_ptr(i) and ms.flags[i] == layer.flags.peer_ptr(i) and ms.counters[i] == layer.counters.peer_ptr(i)
+    ok = ok and ms.codes == layer.codes.data_ptr() and ms.pull_idx == layer.pull_idx.data_ptr() and ms.sg == layer.sg.data_ptr()
+    layer.forward(torch.zeros(128, 16 * world), torch.zeros(128, 256, dtype=torch.bfloat16), Wq, Wsc, Wsg)
+    res["moe_calls"] = [c for c in fake.calls if c[0] == "moe_layer"]
+    res["moe_state"] = ok and layer.cap_rows % 128 == 0
     q.put((rank, res))
     dist.barrier()
     dist.destroy_process_group()
@@ -131,8 +175,10 @@ def test_world2_host_logic_gloo():
         assert p.exitcode == 0
     for r in range(world):
         res = results[r]
-        for key in ("tp_codes", "tp_scales", "tp_sg", "moe_route_consistent", "moe_cover_once", "moe_map", "moe_padding"):
+        for key in ("tp_codes", "tp_scales", "tp_sg", "moe_route_consistent", "moe_cover_once", "moe_map", "moe_padding", "ag_state", "moe_state"):
             assert res[key], (r, key)
+        assert [c[1] for c in res["ag_calls"]] == [1, 2] and all(c[2:4] == (128, 4) for c in res["ag_calls"])      # epochs grow by one per call
+        assert [c[1] for c in res["moe_calls"]] == [1] and res["moe_calls"][0][2] == 6
         # rank r sees its own pointer for itself and "rank o's pointer" for the peer
         for o in range(world):
             expect = results[o]["own_ptr"] if o == r else ((o << 40) | results[o]["own_ptr"])
