@@ -571,6 +571,57 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt_e2e = float(t.item())
 
+    # The same step as a user would stream it: copies on their own streams and two buffer sets, so the H2D copy of step
+    # i+1 and the D2H copy of step i-1 overlap step i's kernels.  Every step still moves all of its bytes inside the
+    # timed region.  The number is used only if the pipeline ran and its last results equal the device buffers.
+    dt_e2e_serial, e2e_mode = dt_e2e, "serial: H2D, kernels and D2H of a step one after the other on one stream"
+    if world == 1:
+        try:
+            main = torch.cuda.current_stream()
+            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            sets = [(dA, dB, groups[0], hostD), (torch.empty_like(dA), torch.empty_like(dB), groups[1], torch.empty_like(hostD).pin_memory())]
+            ev_in = [torch.cuda.Event() for _ in range(2)]; ev_done = [torch.cuda.Event() for _ in range(2)]; ev_out = [torch.cuda.Event() for _ in range(2)]
+
+            def piped_step(i):
+                k = i % 2
+                dAk, dBk, (a_, asc_, b_, bsc_, D_), hostDk = sets[k]
+                s_in.wait_event(ev_done[k])              # the kernels of step i-2 have consumed this set's inputs
+                with torch.cuda.stream(s_in):
+                    dAk.copy_(hostA, non_blocking=True); dBk.copy_(hostB, non_blocking=True)
+                    ev_in[k].record(s_in)
+                main.wait_event(ev_in[k])
+                main.wait_event(ev_out[k])               # this set's D has been copied out by step i-2
+                ops.mxfp8_quantize(dAk, a_, asc_); ops.mxfp8_quantize(dBk, b_, bsc_)
+                ops.mxfp8_gemm(a_, asc_, b_, bsc_, D_)
+                ev_done[k].record(main)
+                s_out.wait_event(ev_done[k])
+                with torch.cuda.stream(s_out):
+                    hostDk.copy_(D_, non_blocking=True)
+                    ev_out[k].record(s_out)
+
+            def piped_loop(steps):
+                s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                time.sleep(0.5)
+                s.record(main)
+                for i in range(steps):
+                    piped_step(i)
+                main.wait_stream(s_in); main.wait_stream(s_out)      # the last D2H copies are inside the timed region
+                e.record(main)
+                torch.cuda.synchronize()
+                return s.elapsed_time(e) * 1e-3 / steps
+
+            piped_loop(2)
+            dt_piped = piped_loop(e2e_steps)
+            same = all(torch.equal(sets[k][3], sets[k][2][4].cpu()) for k in range(2))
+            if same and 0.0 < dt_piped < dt_e2e_serial:
+                dt_e2e = dt_piped
+                e2e_mode = "pipelined: copies on their own streams, two buffer sets (H2D of step i+1 and D2H of step i-1 overlap step i's kernels)"
+            del sets
+        except Exception as ex:      # keep the serial number
+            e2e_mode += f" (pipelined variant failed: {repr(ex)[:120]})"
+        torch.cuda.synchronize()
+
     extras = {}
     if rank == 0 and not args.no_extra:
         extras = side_measurements(torch, ops, dev)
@@ -597,7 +648,7 @@ def run_ours(args) -> None:
                          "peak_source": f"2 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense FP8 ceiling)",
                          "frac_of_nominal_4500": tflops / NOMINAL["fp8"]},
             "e2e": {"value": FLOPS / dt_e2e * 1e-12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
-                    "d2h_bytes_per_step": M * N * 2, "ms_per_step": dt_e2e * 1e3,
+                    "d2h_bytes_per_step": M * N * 2, "ms_per_step": dt_e2e * 1e3, "serial_ms_per_step": dt_e2e_serial * 1e3, "mode": e2e_mode,
                     "path": "pinned host bf16 -> H2D -> tkb_mxfp8_quantize x2 -> tkb_mxfp8_gemm -> D2H"},
             "gpu_launches": args.steps, "clocks": clocks, "extra": extras,
         }
