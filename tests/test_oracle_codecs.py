@@ -1,7 +1,6 @@
 """The oracle's hand-written narrow-float codecs against the CUDA toolkit's host conversions
 (cuda_fp4.h / cuda_fp8.h / cuda_bf16.h) — the functions the reference kernels call."""
 import numpy as np
-import pytest
 
 import oracle as O
 
