@@ -338,11 +338,14 @@ template <int NB>
 static cudaError_t launch_decode_t(const DecodeArgs& a) {
     using C = DecodeCfg<NB>;
     auto kern = decode_kernel<NB>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // the attribute belongs to the (kernel, device) pair: remember it per device, not per process
+    static bool attr_set[64] = {};
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const long long items = (long long)((a.N + 127) / 128) * ((a.K + 255) / 256);
     int grid = a.sm_count;

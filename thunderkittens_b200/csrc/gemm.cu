@@ -612,11 +612,14 @@ template <int KIND, int CTAS, int BN, int MODE = MODE_PLAIN>
 static cudaError_t launch_t(const GemmArgs& a) {
     using C = GemmCfg<KIND, CTAS, BN>;
     auto kern = gemm_kernel<KIND, CTAS, BN, MODE>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // the attribute belongs to the (kernel, device) pair: remember it per device, not per process
+    static bool attr_set[64] = {};
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int tiles = ((a.M + C::BM - 1) / C::BM) * ((a.N + BN - 1) / BN);
     const int comm_units = MODE == MODE_AG ? a.comm.ag.comm_ctas / CTAS : (MODE == MODE_MOE ? a.comm.moe.comm_ctas / CTAS : 0);
