@@ -308,6 +308,8 @@ def run_tp(args) -> None:
                     "d2h_bytes_per_step": Mt * n_local * 2 * world, "ms_per_step": dt_e2e * 1e3,
                     "path": "pinned host bf16 shard -> H2D -> AllGatherMatmulNVFP4 -> D2H of the rank's output columns"},
             "gpu_launches": args.steps * 2 * world, "clocks": clocks, "single_gpu_same_problem": single,
+            "scaling_note": "strong scaling of ONE problem: the 1-GPU time of this problem is single_gpu_same_problem.ms_per_step; the N=1 line of "
+                            "this benchmark is a different workload (MXFP8 GEMM 8192^3, BASELINE configs[1]) and not the T(1) of this curve",
         }
         print(json.dumps(line), flush=True)
     op.close()
