@@ -669,7 +669,7 @@ MXFP8_GEMM_DRAM_BYTES = 464.8e6
 
 # The reference's own GPU kernels (built from its tree into oracle/_ref/tk_<which> by oracle/build.py:build_ref_gpu) timed with
 # the same protocol as this library's (CUDA events, 3 rotating operand sets, 500 ms idle first).  Runs in a child process: the
-# reference's modules are both called `_C`.  Single-GPU only (the reference kernels issue cluster-multicast TMA loads).
+# reference's modules are both called `_C`.  Single-GPU only: the reference's kernel objects do not travel to multi-GPU runs.
 REF_GPU_CHILD = r"""
 import sys, os, json, glob, time, importlib.util
 ROOT, which = sys.argv[1], sys.argv[2]
