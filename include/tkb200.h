@@ -141,6 +141,14 @@ int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const 
 int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, const float* X_sg, const void* W, const void* W_sc,
                                  const float* W_sg, void* D, int64_t ldd, int M, int N, int K, void* stream);
 
+/* NVFP4 GEMM whose result leaves the kernel quantized to NVFP4 (no counterpart in the reference; the specification is
+ * tkb_nvfp4_quantize_with_amax applied to the bf16 result of tkb_nvfp4_gemm, and the outputs are bit-identical to that
+ * sequence): D_codes [M, N/2], D_sc [ceil(M/128), N/64, 512], D_sg[1], quantized with the caller's per-tensor amax
+ * `out_amax` (device float, e.g. a calibrated activation range).  arithmetic: TKB_NVFP4_SPEC or TKB_NVFP4_KERNEL_IEEE.
+ * N % 64 == 0, K % 64 == 0.  State: written and compiled, NOT yet run on a GPU, no test yet. */
+int tkb_nvfp4_gemm_quant(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
+                         const float* out_amax, void* D_codes, void* D_sc, float* D_sg, int M, int N, int K, int arithmetic, void* stream);
+
 /* Replaces mxfp8_gemm(A, A_sc, B, B_sc, D) (mxfp8_b200_gemm.cu:585-603).  K % 128 == 0, N % 8 == 0. */
 int tkb_mxfp8_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
                    void* stream);

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "tkb_moe_combine": ([C.POINTER(_vp), _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_fp8_gemm": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _vp], _i),
     "tkb_fp8_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
+    "tkb_nvfp4_gemm_quant": ([_vp] * 10 + [_i, _i, _i, _i, _vp], _i),
     "tkb_bf16_gemm_ex": ([_vp, _i64, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp], _i),
 }
 

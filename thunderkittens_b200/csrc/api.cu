@@ -380,6 +380,28 @@ int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const voi
                    int64_t ldd, int M, int N, int K, void* stream) {
     return tkb_nvfp4_gemm_ex(A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, TKB_GEMM_DEFAULT, stream);
 }
+int tkb_nvfp4_gemm_quant(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
+                         const float* out_amax, void* D_codes, void* D_sc, float* D_sg, int M, int N, int K, int arithmetic, void* stream) {
+    if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !out_amax || !D_codes || !D_sc || !D_sg) return fail(TKB_ERR_INVALID_ARG, "gemm_quant: null pointer");
+    if (M < 1 || N < 64 || N % 64 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "gemm_quant: need M >= 1, N %% 64 == 0, K %% 64 == 0 (got %d, %d, %d)", M, N, K);
+    if (arithmetic != TKB_NVFP4_SPEC && arithmetic != TKB_NVFP4_KERNEL_IEEE)
+        return fail(TKB_ERR_INVALID_ARG, "gemm_quant: the fused epilogue offers the two IEEE arithmetics only");
+    if (!aligned16(A) || !aligned16(B) || !aligned16(A_sc) || !aligned16(B_sc) || !aligned16(D_codes) || !aligned16(D_sc))
+        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm_quant: buffers must be 16-byte aligned");
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.kind = KIND_NVFP4; g.config = 0;
+    // the bf16 output map is built over the code buffer only to have a valid descriptor: this mode never stores through it
+    if (int e = api_make_gemm_maps(&g, KIND_NVFP4, A, K / 2, A_sc, B, K / 2, B_sc, D_codes, N, M, N, K)) return e;
+    g.sgA = A_sg; g.sgB = B_sg; g.M = M; g.N = N; g.K = K;
+    g.status = c->status; g.prof = g_prof; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
+    g.mode = MODE_QUANT;
+    g.q_codes = D_codes; g.q_sc = D_sc; g.q_sg = D_sg; g.q_amax = out_amax; g.q_arith = arithmetic == TKB_NVFP4_SPEC ? 0 : 1;
+    TKB_CUDA(launch_gemm(g));
+    return TKB_OK;
+}
 int tkb_mxfp8_gemm_ex(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int64_t ldd, int M, int N, int K,
                       int config, void* stream) {
     return gemm_common(KIND_MXFP8, A, K, A_sc, nullptr, B, K, B_sc, nullptr, D, ldd, M, N, K, config, stream);

@@ -27,6 +27,8 @@
 //   * Every mbarrier wait is bounded (ptx.cuh); on a timeout the kernel records the status, leaves
 //     its loops, joins the final cluster barrier, frees TMEM and returns.
 #include <cstdlib>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include "ptx.cuh"
 #include "internal.h"
 #include "ag_schedule.h"
@@ -71,7 +73,37 @@ struct GemmParams {
     int group;                  // row blocks that share a sweep over the columns
     int* status;
     unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
+    // quantizing epilogue (MODE_QUANT): the bf16 result is quantized to NVFP4 before it leaves the SM
+    uint8_t* q_codes; uint8_t* q_sc; float* q_sg; const float* q_amax; int q_arith;
 };
+
+// NVFP4 quantization of one 16-value block held as 8 packed bf16 pairs, with the IEEE arithmetic of the standalone
+// quantizer (quantize.cu: ArithSpec / ArithKernelIeee): returns the e4m3 scale byte, `codes` receives 8 bytes.
+__device__ __forceinline__ uint8_t quant_block16(const uint32_t (&w)[8], float sg_dec, float sg_enc, uint2& codes) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        __nv_bfloat162 a = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        __nv_bfloat162 b = __hmax2(a, *reinterpret_cast<__nv_bfloat162*>(&m));
+        m = *reinterpret_cast<uint32_t*>(&b);
+    }
+    const __nv_bfloat162 mm = *reinterpret_cast<__nv_bfloat162*>(&m);
+    const float amax16 = __bfloat162float(__hmax(mm.x, mm.y));
+    const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(__fmul_rn(__fdiv_rn(amax16, 6.0f), sg_enc), __NV_SATFINITE, __NV_E4M3);
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(s8, __NV_E4M3);
+    const float s_local = __half2float(*reinterpret_cast<const __half*>(&hr));
+    const float s_enc = __frcp_rn(fmaxf(__fmul_rn(s_local, sg_dec), 0.000000000001f));
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float2 f = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+        f.x = __fmul_rn(f.x, s_enc);
+        f.y = __fmul_rn(f.y, s_enc);
+        out[i >> 2] |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * (i & 3));
+    }
+    codes = make_uint2(out[0], out[1]);
+    return s8;
+}
 
 // All-gather mode (tensor-parallel GEMM): the A operand is row-sharded over `world` GPUs.  Every rank
 // keeps a full-size buffer for the gathered codes and scales and quantizes its own shard into its own
@@ -538,6 +570,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         asm volatile("griddepcontrol.wait;" ::: "memory");          // D may still be read, and the scales written, by the previous kernel
         float alpha = 1.0f;
         if constexpr (KIND == KIND_NVFP4) alpha = __fmul_rn(*p.sgA, *p.sgB);
+        float q_sg_dec = 0.f, q_sg_enc = 0.f;
+        if constexpr (MODE == MODE_QUANT) {
+            const float amax = *p.q_amax;
+            if (p.q_arith == 0) {          // the torch specification's association
+                q_sg_enc = __fdiv_rn(6.0f * 448.0f, fmaxf(amax, 0.000000000001f));
+                q_sg_dec = __frcp_rn(q_sg_enc);
+            } else {                       // the reference kernel's association
+                q_sg_dec = __fdiv_rn(amax, 6.0f * 448.0f);
+                q_sg_enc = __frcp_rn(fmaxf(q_sg_dec, 0.000000000001f));
+            }
+            if (blockIdx.x == 0 && warp == 2 && lane == 0) *p.q_sg = q_sg_dec;
+        }
+        (void)q_sg_dec; (void)q_sg_enc;
         const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
         const uint32_t stage_box = sEpi + ew * C::EPI_WARP_BYTES;
         const uint64_t d_policy = l2_policy_evict_first();     // D is written once and never read here: keep the operands in L2 instead
@@ -573,6 +618,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             drain += clock64() - t1;
             const int row0 = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32;
             const int col0 = n_blk * BN + col_base;
+            if constexpr (MODE == MODE_QUANT) {
+                // This thread holds row `row0 + lane`, columns col0 .. col0 + 127 of D as bf16: eight 16-value blocks.
+                // Codes: 64 contiguous bytes of the row; scales: two 4-byte words in the 512-byte chunks of its row block.
+                const int row = row0 + lane;
+                const int k_chunks_out = p.N / 64;
+                uint32_t sc_word[2] = {0u, 0u};
+                if (row < p.M) {
+                    uint4* crow = reinterpret_cast<uint4*>(p.q_codes + size_t(row) * (p.N / 2) + col0 / 2);
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        uint2 c0, c1;
+                        const uint32_t (&w0)[8] = *reinterpret_cast<const uint32_t (*)[8]>(&packed[8 * j]);
+                        const uint32_t (&w1)[8] = *reinterpret_cast<const uint32_t (*)[8]>(&packed[8 * j + 8]);
+                        const uint8_t s0 = quant_block16(w0, q_sg_dec, q_sg_enc, c0);
+                        const uint8_t s1 = quant_block16(w1, q_sg_dec, q_sg_enc, c1);
+                        sc_word[j >> 2] |= (uint32_t(s0) << (8 * (j & 3))) | (uint32_t(s1) << (8 * ((j + 1) & 3)));
+                        if (col0 + 16 * j < p.N) crow[j >> 1] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+                    }
+                }
+                // rows past M inside the last 128-row block get zero scales, like the standalone quantizer writes them
+                if (col0 < p.N && m_blk * CTAS + int(cta_rank) < (p.M + 127) / 128) {
+                    uint8_t* chunk = p.q_sc + (size_t(m_blk * CTAS + int(cta_rank)) * k_chunks_out + col0 / 64) * 512 + lane * 16 + quarter * 4;
+                    *reinterpret_cast<uint32_t*>(chunk) = sc_word[0];
+                    if (col0 + 64 < p.N) *reinterpret_cast<uint32_t*>(chunk + 512) = sc_word[1];
+                }
+                continue;
+            }
 #pragma unroll
             for (int h = 0; h < C::COLS_PER_EPI_WARP / 64; h++) {
                 // the previous store of this warp must have finished reading the staging box
@@ -641,7 +713,8 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
     static const int group_env = getenv("TKB_GEMM_GROUP") ? atoi(getenv("TKB_GEMM_GROUP")) : 0;
-    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof};
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof,
+                 static_cast<uint8_t*>(a.q_codes), static_cast<uint8_t*>(a.q_sc), a.q_sg, a.q_amax, a.q_arith};
     return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
 
@@ -660,6 +733,7 @@ int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
 
 cudaError_t launch_gemm(const GemmArgs& a) {
     if (a.mode == MODE_AG) return launch_t<KIND_NVFP4, 2, 256, MODE_AG>(a);
+    if (a.mode == MODE_QUANT) return launch_t<KIND_NVFP4, 2, 256, MODE_QUANT>(a);
     if (a.mode == MODE_MOE) return launch_t<KIND_NVFP4, 1, 256, MODE_MOE>(a);
     switch (a.kind) {
         case KIND_BF16: return launch_k<KIND_BF16>(a);

@@ -46,7 +46,7 @@ struct MoeParams {
     unsigned int epoch;
     int rank, world, comm_ctas, expert_rows; // expert_rows = rows of one expert's weight matrix (the GEMM's N)
 };
-enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2 };
+enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2, MODE_QUANT = 4 };   // QUANT: the epilogue writes D as NVFP4
 struct CommParams { AgParams ag; MoeParams moe; };
 
 struct GemmArgs {
@@ -61,6 +61,8 @@ struct GemmArgs {
     cudaStream_t stream;
     int mode;                 // GemmMode
     CommParams comm;
+    // MODE_QUANT: D leaves the kernel as NVFP4 codes + chunked scales quantized with a caller-supplied amax
+    void* q_codes; void* q_sc; float* q_sg; const float* q_amax; int q_arith;   // q_arith: 0 = spec association, 1 = kernel association (IEEE)
 };
 cudaError_t launch_gemm(const GemmArgs& a);
 int gemm_tile_n(int config);

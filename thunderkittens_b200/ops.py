@@ -149,3 +149,15 @@ def fp8_gemm(A, B, D, config: str | None = None) -> None:
     if B.shape[1] != K or tuple(D.shape) != (M, N):
         raise RuntimeError("shape mismatch: A (M,K), B (N,K), D (M,N)")
     L.check(L.lib().tkb_fp8_gemm_ex(A.data_ptr(), 0, B.data_ptr(), 0, D.data_ptr(), 0, M, N, K, _CONFIG[config], _stream()))
+
+
+def nvfp4_gemm_quant(A, A_sc, A_sg, B, B_sc, B_sg, out_amax, D_codes, D_sc, D_sg, arithmetic: str = "spec") -> None:
+    """NVFP4 GEMM whose bf16 result is quantized to NVFP4 (with the caller's per-tensor amax) inside the epilogue."""
+    M, K = A.shape[0], A.shape[1] * 2
+    N = B.shape[0]
+    if tuple(D_codes.shape) != (M, N // 2):
+        raise RuntimeError("D_codes must have shape (M, N/2)")
+    if arithmetic not in ("spec", "kernel_ieee"):
+        raise RuntimeError("the fused epilogue offers the 'spec' and 'kernel_ieee' arithmetics")
+    L.check(L.lib().tkb_nvfp4_gemm_quant(A.data_ptr(), A_sc.data_ptr(), A_sg.data_ptr(), B.data_ptr(), B_sc.data_ptr(), B_sg.data_ptr(),
+                                         out_amax.data_ptr(), D_codes.data_ptr(), D_sc.data_ptr(), D_sg.data_ptr(), M, N, K, _ARITH[arithmetic], _stream()))
