@@ -202,6 +202,18 @@ int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned in
 int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer, int gather, int rank, int world, void* const* peer_counters,
                    int counter_base, unsigned int epoch, void* stream);
 
+/* The general form of tk_all_to_all(output, input, barrier, scatter_axis, gather_axis) (all_to_all.cu:119-179, kernel 37-94):
+ * `in` is this rank's 4-D tensor of dims[4] elements of elem_bytes each; element (i0,i1,i2,i3) goes to rank
+ * i[scatter] / (dims[scatter] / world), at i[scatter] % (dims[scatter] / world) along the scatter axis and
+ * i[gather] + dims[gather] * rank along the gather axis of that rank's output (dims with the scatter axis divided and the
+ * gather axis multiplied by world).  The innermost axis (and its per-rank part when it is the scattered one) must be whole
+ * 16-byte vectors.  peer_counters[i] + counter_base: 2 * world zero-initialised 32-bit counters on rank i; epoch grows by
+ * one per call on the same counters and the tensor shape must not change between calls on them.  The call enqueues a
+ * bounded all-ranks-entered hand-shake, the pushes and a bounded wait for all incoming data.
+ * State: written and compiled, NOT yet run on a GPU. */
+int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* dims, int elem_bytes, int scatter_axis, int gather_axis, int rank,
+                      int world, void* const* peer_counters, int counter_base, unsigned int epoch, void* stream);
+
 /* Tensor-parallel all-gather GEMM, NVFP4.  Replaces all_gather_matmul(A, B, C, barrier, num_comm_sms)
  * (kernels/parallel/ag_gemm/ag_gemm_b200.cu:280-305; the reference ships bf16 and fp8 variants only).
  *   D[M, N_local] = gather_rows(Xq)[M, K] . W_local[N_local, K]^T.

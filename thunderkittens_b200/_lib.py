@@ -49,6 +49,7 @@ _SIGNATURES = {
     "tkb_wait_flags": ([_vp, _i, _i, C.c_uint, _vp], _i),
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
+    "tkb_all_to_all_4d": ([C.POINTER(_vp), _vp, C.POINTER(C.c_longlong), _i, _i, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_ag_linear_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp,
                            C.c_uint, _i, _vp], _i),

@@ -25,6 +25,7 @@ int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, 
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
 
 struct PeerPtrs { unsigned int* p[kMaxWorld]; };
+constexpr int kAllToAll4dMaxGrid = 592;   // CTAs of tkb_all_to_all_4d at most (part of its counter protocol)
 constexpr int kAllToAllParts = 4;      // CTAs per destination in tkb_all_to_all (part of its counter protocol)
 
 __global__ void signal_peers_kernel(PeerPtrs peers, int world, int rank, int index, unsigned int value, int include_self) {
@@ -96,6 +97,53 @@ __global__ void all_to_all_push_kernel(PeerBytes out, const unsigned char* in, s
     if (threadIdx.x == 0) {
         __threadfence_system();
         asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(counters.p[dst] + counter_base + rank), "r"(1u) : "memory");
+    }
+}
+
+// General 4-D all-to-all (all_to_all::kernel<S,G>, kernels/parallel/all_to_all/all_to_all.cu:37-94): element
+// (i0, i1, i2, i3) of this rank's input goes to rank i[S] / out[S], at index i[S] % out[S] along the scatter axis and
+// i[G] + in[G] * rank along the gather axis (out[S] = in[S] / world, out[G] = in[G] * world).  Threads move 16-byte
+// vectors along the innermost axis with plain loads (local) and stores (NVLink, posted); when a CTA is through, it
+// bumps a counter on every rank (system-scope release add).
+struct A2A4Params {
+    unsigned char* out[kMaxWorld];
+    unsigned int* counters[kMaxWorld];
+    long long in_dims[4];        // innermost in 16-byte vectors
+    long long out_dims[4];
+    int scatter, gather, rank, world, counter_base;
+};
+__global__ void __launch_bounds__(256) all_to_all_4d_kernel(const unsigned char* __restrict__ in, const A2A4Params p) {
+    const long long total = p.in_dims[0] * p.in_dims[1] * p.in_dims[2] * p.in_dims[3];
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+        long long idx[4], rest = v;
+#pragma unroll
+        for (int a = 3; a >= 0; a--) { idx[a] = rest % p.in_dims[a]; rest /= p.in_dims[a]; }
+        const int dst = int(idx[p.scatter] / p.out_dims[p.scatter]);
+        idx[p.scatter] %= p.out_dims[p.scatter];
+        idx[p.gather] += p.in_dims[p.gather] * p.rank;
+        const long long o = ((idx[0] * p.out_dims[1] + idx[1]) * p.out_dims[2] + idx[2]) * p.out_dims[3] + idx[3];
+        reinterpret_cast<uint4*>(p.out[dst])[o] = __ldg(reinterpret_cast<const uint4*>(in) + v);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int d = 0; d < p.world; d++)
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.counters[d] + p.counter_base + p.rank), "r"(1u) : "memory");
+    }
+}
+// All ranks have entered: one add per peer, then a bounded wait for everybody's.
+__global__ void a2a_enter_kernel(PeerPtrs counters, int base, int rank, int world, unsigned int epoch, int* status) {
+    const int t = threadIdx.x;
+    if (t < world) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(counters.p[t] + base + rank), "r"(1u) : "memory");
+    if (t < world) {
+        const long long t0 = clock64();
+        while (true) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counters.p[rank] + base + t) : "memory");
+            if (int(v - epoch) >= 0) break;
+            if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
+            __nanosleep(100);
+        }
     }
 }
 
@@ -194,6 +242,50 @@ int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer,
     TKB_CUDA_C(cudaGetLastError());
     // every sender adds `parts` to its counter per call: wait until all of them have reached epoch * parts
     wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base, world, -1, epoch * unsigned(parts), status);
+    TKB_CUDA_C(cudaGetLastError());
+    return TKB_OK;
+}
+
+int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* dims, int elem_bytes, int scatter_axis, int gather_axis, int rank,
+                      int world, void* const* peer_counters, int counter_base, unsigned int epoch, void* stream) {
+    if (!peer_out || !in || !dims || !peer_counters) return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: null pointer");
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || counter_base < 0 || epoch == 0)
+        return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: bad rank / world / counters / epoch");
+    if (scatter_axis < 0 || scatter_axis > 3 || gather_axis < 0 || gather_axis > 3 || scatter_axis == gather_axis)
+        return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: scatter and gather axes must be two different axes in 0..3");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8) return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: element size must be 1, 2, 4 or 8 bytes");
+    for (int a = 0; a < 4; a++)
+        if (dims[a] < 1) return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: dims must be positive");
+    if (dims[scatter_axis] % world) return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: the scattered axis must divide by the world size");
+    const long long inner_bytes = dims[3] * elem_bytes;
+    if (inner_bytes % 16 || (scatter_axis == 3 && (inner_bytes / world) % 16) || (reinterpret_cast<uintptr_t>(in) & 15u))
+        return api_fail(TKB_ERR_BAD_ALIGNMENT, "all_to_all_4d: the innermost axis (and its per-rank part, if scattered) must be whole 16-byte vectors");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    A2A4Params p;
+    memset(&p, 0, sizeof(p));
+    PeerPtrs pc;
+    for (int i = 0; i < kMaxWorld; i++) {
+        p.out[i] = i < world ? static_cast<unsigned char*>(peer_out[i]) : nullptr;
+        p.counters[i] = i < world ? static_cast<unsigned int*>(peer_counters[i]) : nullptr;
+        pc.p[i] = p.counters[i];
+        if (i < world && (!p.out[i] || !p.counters[i] || (reinterpret_cast<uintptr_t>(p.out[i]) & 15u)))
+            return api_fail(TKB_ERR_INVALID_ARG, "all_to_all_4d: null or misaligned buffer of rank %d", i);
+    }
+    for (int a = 0; a < 4; a++) p.in_dims[a] = p.out_dims[a] = a == 3 ? inner_bytes / 16 : dims[a];
+    p.out_dims[scatter_axis] = p.in_dims[scatter_axis] / world;
+    p.out_dims[gather_axis] = p.in_dims[gather_axis] * world;
+    p.scatter = scatter_axis; p.gather = gather_axis; p.rank = rank; p.world = world; p.counter_base = counter_base + world;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // counters [base, base + world): "rank r has entered call `epoch`" (nobody writes into a peer that may still be reading
+    // its output of the previous call); [base + world, base + 2 * world): CTAs of rank r that are through
+    a2a_enter_kernel<<<1, 32, 0, s>>>(pc, counter_base, rank, world, epoch, status);
+    TKB_CUDA_C(cudaGetLastError());
+    const long long total = p.in_dims[0] * p.in_dims[1] * p.in_dims[2] * p.in_dims[3];
+    const int grid = int(total / 2048 < 1 ? 1 : (total / 2048 > kAllToAll4dMaxGrid ? kAllToAll4dMaxGrid : total / 2048));   // the same on every rank
+    all_to_all_4d_kernel<<<grid, 256, 0, s>>>(static_cast<const unsigned char*>(in), p);
+    TKB_CUDA_C(cudaGetLastError());
+    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base + world, world, -1, epoch * unsigned(grid), status);
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }

@@ -318,3 +318,27 @@ class MoELayerNVFP4:
     def close(self) -> None:
         for t in self.xq_rows + self.slots + self.experts_all_sym + [self.Y, self.flags, self.counters]:
             t.close()
+
+
+def tk_all_to_all(output: TKParallelTensor, input: TKParallelTensor, barrier: TKParallelTensor, scatter_axis: int, gather_axis: int) -> None:
+    """The reference's tk_all_to_all(output, input, barrier, scatter_axis, gather_axis) (all_to_all.cu:119-179): `input` is
+    this rank's 4-D tensor, `output` has the scatter axis divided and the gather axis multiplied by the world size.
+    `barrier` must be an int32 TKParallelTensor of at least 2 * world zero-initialised elements that is used for nothing
+    else; the call counter lives on it."""
+    w, r = input.local_world_size_, input.local_rank_
+    if len(input.shape_) != 4 or len(output.shape_) != 4:
+        raise RuntimeError("input and output must be 4-D")
+    expect = list(input.shape_)
+    if expect[scatter_axis] % w:
+        raise RuntimeError("the scattered axis must divide by the world size")
+    expect[scatter_axis] //= w
+    expect[gather_axis] *= w
+    if tuple(expect) != tuple(output.shape_) or input.dtype_ != output.dtype_:
+        raise RuntimeError(f"output must have shape {tuple(expect)} and the input's dtype")
+    if barrier.dtype_ != torch.int32 or barrier.data_.numel() < 2 * w:
+        raise RuntimeError("barrier must be an int32 parallel tensor of at least 2 * world elements")
+    epoch = getattr(barrier, "_tkb_epoch", 0) + 1
+    barrier._tkb_epoch = epoch
+    dims = (C.c_longlong * 4)(*input.shape_)
+    L.check(L.lib().tkb_all_to_all_4d(output.peer_ptr_array(), input.data_.data_ptr(), dims, input.data_.element_size(), scatter_axis, gather_axis,
+                                      r, w, barrier.peer_ptr_array(), 0, epoch, _stream()))
