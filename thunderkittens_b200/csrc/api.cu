@@ -39,6 +39,8 @@ static int fail(int code, const char* fmt, ...) {
 constexpr int kMaxDevices = 64;
 constexpr int kQuantSlots = 256;
 constexpr int kDecodeRing = 4;
+constexpr int kSmallScratchRing = 4;
+constexpr size_t kSmallScratchBytes = 2u << 20;
 constexpr int kDecodeMaxGrid = 160;                      // CTAs the scratch is sized for
 constexpr size_t kDecodePartialFloats = size_t(kDecodeMaxGrid) * 128 * 128;
 
@@ -50,6 +52,8 @@ struct DeviceCtx {
     QuantWork* quant_ws = nullptr;  // kQuantSlots zeroed slots, each returned to zero by the kernel that used it
     std::atomic<unsigned> next_slot{0};
     // skinny-M GEMM scratch: kDecodeRing independent sets of (per-CTA fp32 partial tiles, per-CTA flags)
+    unsigned char* small_scratch = nullptr;     // kSmallScratchRing buffers of kSmallScratchBytes for short-lived kernel temporaries
+    std::atomic<unsigned> small_scratch_calls{0};
     float* decode_partials = nullptr;
     unsigned int* decode_flags = nullptr;
     std::atomic<unsigned> decode_calls{0};
@@ -200,6 +204,26 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
 }
 
 unsigned long long* api_profile_buffer() { return g_prof; }
+
+// A buffer of library-owned device scratch for temporaries that live for a few consecutive launches of one call (up to
+// kSmallScratchRing calls may be in flight per device).  *ptr is null when the request is larger than a buffer: the
+// caller then takes a path that needs none.
+int api_small_scratch(size_t bytes, void** ptr) {
+    *ptr = nullptr;
+    DeviceCtx* c;
+    if (int e = get_ctx(&c)) return e;
+    if (bytes > kSmallScratchBytes) return TKB_OK;
+    if (!c->small_scratch) {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        if (!c->small_scratch) {
+            unsigned char* p = nullptr;
+            TKB_CUDA(cudaMalloc(&p, kSmallScratchRing * kSmallScratchBytes));
+            c->small_scratch = p;
+        }
+    }
+    *ptr = c->small_scratch + (c->small_scratch_calls.fetch_add(1) % kSmallScratchRing) * kSmallScratchBytes;
+    return TKB_OK;
+}
 
 int api_device(int* sm_count, int** status) {
     DeviceCtx* c;

@@ -23,6 +23,7 @@ namespace tkb {
 int api_fail(int code, const char* fmt, ...);
 int api_device(int* sm_count, int** status);
 unsigned long long* api_profile_buffer();             // api.cu: tkb_gemm_set_profile_buffer
+int api_small_scratch(size_t bytes, void** ptr);      // api.cu: library-owned temporaries, null when too large
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);
 
@@ -154,6 +155,125 @@ moe_assign_kernel(const int* __restrict__ experts_all, int total, int top_k, int
     }
 }
 
+// ------------------------------------------------------------------------------ schedule as a counting sort ----
+// The same schedule as moe_count_kernel + moe_assign_kernel: the (token, slot) -> expert list is cut into chunks of
+// 1024 entries (one CTA each, one entry per thread); (1) every chunk counts its entries per expert, (2) one CTA per
+// expert turns its row of counts into per-chunk starting positions (block scan) and the padded segment size, (3) every
+// chunk ranks its entries among the earlier entries of the same expert (warps in order, lanes in order) and writes the
+// pull list and the combine map; the first CTAs also write this rank's block table, its padding rows and the block
+// count.  Positions are in ascending list order, exactly as the expert-per-CTA kernels produce them, but the list is
+// read twice instead of 2 * E times.
+constexpr int kSchedChunk = 1024;
+
+__global__ void __launch_bounds__(kSchedChunk)
+moe_sched_hist_kernel(const int* __restrict__ experts_all, int total, int E, int nchunks, int* __restrict__ hist /* [E][nchunks] */) {
+    __shared__ int s_cnt[256];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * kSchedChunk + threadIdx.x;
+    if (i < total) atomicAdd(&s_cnt[experts_all[i]], 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) hist[size_t(e) * nchunks + blockIdx.x] = s_cnt[e];
+}
+
+// CTA e: exclusive prefix of expert e's per-chunk counts (nchunks <= 1024 * 32 handled in rounds of blockDim.x)
+__global__ void __launch_bounds__(1024)
+moe_sched_scan_kernel(int* __restrict__ hist, int nchunks, int* __restrict__ counts, int* __restrict__ padded) {
+    __shared__ int s_warp[32];
+    __shared__ int s_carry;
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int* row = hist + size_t(e) * nchunks;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (int c0 = 0; c0 < nchunks; c0 += blockDim.x) {
+        const int c = c0 + threadIdx.x;
+        const int v = c < nchunks ? row[c] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = s_warp[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, o);
+                if (lane >= o) w += t;
+            }
+            s_warp[lane] = w;
+        }
+        __syncthreads();
+        const int carry = s_carry;
+        if (c < nchunks) row[c] = carry + incl - v + (warp > 0 ? s_warp[warp - 1] : 0);
+        __syncthreads();
+        if (threadIdx.x == 0) s_carry = carry + s_warp[31];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const int total = s_carry;
+        counts[e] = total;
+        padded[e] = (total + 127) / 128 * 128;
+    }
+}
+
+__global__ void __launch_bounds__(kSchedChunk)
+moe_sched_assign_kernel(const int* __restrict__ experts_all, int total, int top_k, int E, int world, int rank, int tokens_per_rank,
+                        const int* __restrict__ hist /* per-chunk starts, [E][nchunks] */, int nchunks, const int* __restrict__ counts,
+                        const int* __restrict__ padded, int* __restrict__ pull_idx, int* __restrict__ block_expert, int* __restrict__ num_blocks,
+                        int* __restrict__ comb_idx, int cap_rows, int* status) {
+    __shared__ int s_warp_cnt[32][256];
+    __shared__ int s_seg[256];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e_per = E / world;
+    // start of every expert's segment inside its owner's buffer
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {
+        int seg = 0;
+        for (int y = (x / e_per) * e_per; y < x; y++) seg += padded[y];
+        s_seg[x] = seg;
+    }
+    for (int x = lane; x < E; x += 32) s_warp_cnt[warp][x] = 0;
+    __syncthreads();
+    // this rank's experts, dealt to the first CTAs: block table and padding rows; CTA 0: block count / capacity error
+    for (int x = rank * e_per + blockIdx.x; x < (rank + 1) * e_per; x += gridDim.x) {
+        const int seg = s_seg[x], pad = padded[x];
+        if (seg + pad <= cap_rows) {
+            for (int r = counts[x] + threadIdx.x; r < pad; r += blockDim.x) { pull_idx[2 * (seg + r)] = -1; pull_idx[2 * (seg + r) + 1] = -1; }
+            for (int b = threadIdx.x; b < pad / 128; b += blockDim.x) block_expert[seg / 128 + b] = x - rank * e_per;
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int t = 0;
+        for (int x = rank * e_per; x < (rank + 1) * e_per; x++) t += padded[x];
+        *num_blocks = t <= cap_rows ? t / 128 : 0;
+        if (t > cap_rows && status) atomicExch(status, 6 /* capacity */);
+    }
+    const int i = blockIdx.x * kSchedChunk + threadIdx.x;
+    const bool live = i < total;
+    const int e = live ? experts_all[i] : -1 - lane;                      // dead lanes match nobody
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+    if (live && rank_in_warp == 0) s_warp_cnt[warp][e] = __popc(same);    // first lane of each group
+    __syncthreads();
+    if (!live) return;
+    int before = 0;
+    for (int w = 0; w < warp; w++) before += s_warp_cnt[w][e];
+    const int pos = hist[size_t(e) * nchunks + blockIdx.x] + before + rank_in_warp;
+    const int owner = e / e_per, seg = s_seg[e];
+    const int tok = i / top_k;
+    if (owner == rank && seg + padded[e] <= cap_rows) {
+        pull_idx[2 * (seg + pos)] = tok / tokens_per_rank;
+        pull_idx[2 * (seg + pos) + 1] = tok % tokens_per_rank;
+    }
+    if (tok / tokens_per_rank == rank) {
+        const int li = (tok % tokens_per_rank) * top_k + i % top_k;
+        comb_idx[2 * li] = owner;
+        comb_idx[2 * li + 1] = seg + pos;
+    }
+}
+
 // ------------------------------------------------------------------------------ combine ------
 struct PeerRows { const __nv_bfloat16* p[kMaxWorld]; };
 
@@ -233,6 +353,20 @@ int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world,
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // counting-sort schedule when its temporaries (per-chunk counts) fit the library's scratch
+    const int total = T * top_k, nchunks = (total + kSchedChunk - 1) / kSchedChunk;
+    void* scratch = nullptr;
+    if (E <= 256)
+        if (int e = api_small_scratch(size_t(nchunks) * E * sizeof(int), &scratch)) return e;
+    if (scratch) {
+        int* hist = static_cast<int*>(scratch);
+        moe_sched_hist_kernel<<<nchunks, kSchedChunk, 0, s>>>(experts_all, total, E, nchunks, hist);
+        moe_sched_scan_kernel<<<E, 1024, 0, s>>>(hist, nchunks, counts, padded_per_expert);
+        moe_sched_assign_kernel<<<nchunks, kSchedChunk, 0, s>>>(experts_all, total, top_k, E, world, rank, T / world, hist, nchunks, counts,
+                                                                padded_per_expert, pull_idx, block_expert, num_blocks, comb_idx, cap_rows, status);
+        TKB_CUDA_M(cudaGetLastError());
+        return TKB_OK;
+    }
     moe_count_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, counts, padded_per_expert);
     moe_assign_kernel<<<E, 1024, 0, s>>>(experts_all, T * top_k, top_k, E, world, rank, T / world, counts, padded_per_expert, pull_idx,
                                          block_expert, num_blocks, comb_idx, cap_rows, status);
