@@ -35,7 +35,7 @@ def main():
         D = torch.full((M, n_local), float("nan"), dtype=torch.bfloat16, device=dev)
         # both host paths on alternating calls: the single library call (epoch hand-shake inside the kernels) and
         # the spelled-out sequence (separate wait / signal launches)
-        (op if it % 2 == 0 else op.step_by_step)(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
+        (op if (it % 2 == 0 or ce) else op.step_by_step)(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
         torch.cuda.synchronize()
         st = _lib.device_status()
         xq = O.nvfp4_quantize(bf16_bits(X), False, "spec")        # quantize(full X): what the shards must add up to
