@@ -205,7 +205,7 @@ def run_tp(args) -> None:
     GROUPS = 3
     # comm CTAs: 20 at 4 and 8 GPUs leaves 64 CTA pairs, which divide the 896 / 448 output tiles of a rank into whole waves
     comm = args.comm_sms if args.comm_sms > 0 else (8 if world <= 2 else 20)
-    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=comm)
+    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=comm, copy_engines=args.comm_sms < 0)   # --comm-sms -1: copy-engine gather
     sets = []
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     for gi in range(GROUPS):
@@ -299,7 +299,8 @@ def run_tp(args) -> None:
             "config": {"workload": "TP NVFP4 GEMM M=8192 N=28672 K=8192: weights N-sharded, bf16 activation rows sharded, per step two launches: "
                                    "quantize with the amax max-reduced over NVLink inside the kernel, then the NVFP4 all-gather over NVLink "
                                    "fused with the tcgen05 GEMM", "parallelism": f"tp{world}",
-                       "l2": f"{GROUPS} rotating weight/activation/output sets", "comm_ctas": op.num_comm_sms},
+                       "l2": f"{GROUPS} rotating weight/activation/output sets", "comm_ctas": 0 if op.copy_engines else op.num_comm_sms,
+                       "gather": "copy engines (peer cudaMemcpyAsync on a second stream)" if op.copy_engines else "comm CTAs of the GEMM kernel"},
             "roofline": {"bound": "tensor", "achieved": tf / world, "peak": 4.0 * pk["bf16_tflops"], "unit": "TFLOP/s per GPU",
                          "frac": tf / peak, "traffic": None, "kernel": "tkb::gemm_kernel<NVFP4, cta pair, N256, all-gather>",
                          "peak_source": f"4 x {pk['source']} cuBLAS bf16 burst (derived dense FP4 ceiling)",

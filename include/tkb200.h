@@ -253,6 +253,11 @@ typedef struct tkb_ag_state {
     float* amax;            /* device scratch, 1 float */
     float* sg;              /* device, 1 float: the per-tensor scale of the gathered activations */
     void* exit_counter;     /* device, one zeroed 32-bit word */
+    /* optional, for the copy-engine gather (comm_ctas < 0 in tkb_ag_linear_nvfp4): a second stream of the same device and
+     * three events created by the caller (cudaStream_t / cudaEvent_t, timing disabled) */
+    void* copy_stream;
+    void* ev_quantized;
+    void* ev_copied[2];
 } tkb_ag_state;
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local_bf16, const void* W, const void* W_sc,
                         const float* W_sg, void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream);

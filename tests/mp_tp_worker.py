@@ -27,14 +27,15 @@ def main():
     W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
     wq = O.nvfp4_quantize(bf16_bits(W[rank * n_local:(rank + 1) * n_local]))
     Wd, Wsc, Wsg = to_dev_u8(wq[0], dev), to_dev_u8(wq[1], dev), torch.from_numpy(wq[2]).to(dev)
-    op = parallel.AllGatherMatmulNVFP4(M, K, local, world, num_comm_sms=4, arithmetic="spec")
+    ce = os.environ.get("TKB_TEST_TP_CE", "0") == "1"       # gather by copy engines instead of comm CTAs
+    op = parallel.AllGatherMatmulNVFP4(M, K, local, world, num_comm_sms=4, arithmetic="spec", copy_engines=ce)
     ok = True
     for it in range(6):      # several calls: both buffer sets, acknowledgements, growing epochs
         X = (torch.randn(M, K, generator=g) * (1.0 + it)).to(torch.bfloat16)
         D = torch.full((M, n_local), float("nan"), dtype=torch.bfloat16, device=dev)
         # both host paths on alternating calls: the single library call (epoch hand-shake inside the kernels) and
         # the spelled-out sequence (separate wait / signal launches)
-        (op if it % 2 == 0 else op.step_by_step)(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
+        (op if (it % 2 == 0 or ce) else op.step_by_step)(X[rank * rows:(rank + 1) * rows].to(dev), Wd, Wsc, Wsg, D)
         torch.cuda.synchronize()
         st = _lib.device_status()
         xq = O.nvfp4_quantize(bf16_bits(X), False, "spec")        # quantize(full X): what the shards must add up to

@@ -32,11 +32,12 @@ def test_ag_gemm_world1(cuda, lib):
     op.close()
 
 
+@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_ag_gemm_multi_gpu(cuda, lib, world):
+def test_ag_gemm_multi_gpu(cuda, lib, world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TKB_TEST_TP_CE="1" if gather == "copy_engines" else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "mp_tp_worker.py")],
                        capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)

@@ -72,7 +72,8 @@ class AgState(C.Structure):
     """Mirror of tkb_ag_state (include/tkb200.h)."""
     _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("K", _i),
                 ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
-                ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp)]
+                ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp),
+                ("copy_stream", _vp), ("ev_quantized", _vp), ("ev_copied", _vp * 2)]
 
 
 class MoeState(C.Structure):

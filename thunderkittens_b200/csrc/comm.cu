@@ -54,6 +54,14 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip
     }
 }
 
+// Stores `value` into count consecutive 32-bit flags (copy-engine gather: the arrival epochs of one rank's rows on one peer,
+// launched in the copy stream right after the copies they announce).
+__global__ void set_flags_kernel(unsigned int* flags, int count, unsigned int value) {
+    __threadfence_system();
+    for (int t = threadIdx.x; t < count; t += blockDim.x)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags + t), "r"(value) : "memory");
+}
+
 // Max all-reduce of one float across the ranks without a library collective: every rank stores (epoch, value
 // bits) into slot[rank] of every peer's slot array and then waits (bounded) until all of its own slots carry the
 // epoch.  About one NVLink round trip instead of a collective launch.
@@ -301,7 +309,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
     if (comm_ctas < 0 || comm_ctas % 2 || comm_ctas > sm - 2) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: comm_ctas must be even and leave compute CTAs");
-    if (world > 1 && comm_ctas == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world > 1 needs comm_ctas >= 2");
+    // comm_ctas == 0 with world > 1: the caller moves the rows itself (copy engines, see tkb_ag_linear_nvfp4) and raises the arrival flags
     if (peer_done && !exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: peer_done needs an exit counter");
     GemmArgs g;
     memset(&g, 0, sizeof(g));
@@ -342,6 +350,7 @@ int tkb_debug_struct_layout(int which, int field) {
             TKB_OFF(tkb_ag_state, rank) TKB_OFF(tkb_ag_state, world) TKB_OFF(tkb_ag_state, M) TKB_OFF(tkb_ag_state, K)
             TKB_OFF(tkb_ag_state, codes) TKB_OFF(tkb_ag_state, scales) TKB_OFF(tkb_ag_state, arrived) TKB_OFF(tkb_ag_state, slots)
             TKB_OFF(tkb_ag_state, done) TKB_OFF(tkb_ag_state, amax) TKB_OFF(tkb_ag_state, sg) TKB_OFF(tkb_ag_state, exit_counter)
+            TKB_OFF(tkb_ag_state, copy_stream) TKB_OFF(tkb_ag_state, ev_quantized) TKB_OFF(tkb_ag_state, ev_copied)
             default: return -1;
         }
     }
@@ -393,11 +402,38 @@ int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* 
     uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
     uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
     // This rank's slice of its own buffers is only read by its own kernels (earlier in this stream); what the peers
-    // read are the copies the comm CTAs push, and those wait for the peers' epoch - 2 kernels themselves.
+    // read are the copies pushed to them, and those wait for the peers' epoch - 2 kernels.
+    cudaStream_t main = static_cast<cudaStream_t>(stream);
+    const bool ce = w > 1 && comm_ctas < 0;          // gather by copy engines on st->copy_stream instead of comm CTAs
+    if (ce) {
+        if (!st->copy_stream || !st->ev_quantized || !st->ev_copied[0] || !st->ev_copied[1])
+            return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs copy_stream, ev_quantized and ev_copied[2] in the state");
+        // the copies of epoch - 2 read the slice that is about to be overwritten
+        if (epoch > 2) TKB_CUDA_C(cudaStreamWaitEvent(main, static_cast<cudaEvent_t>(st->ev_copied[b]), 0));
+    }
     if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, stream))
         return e;
+    if (ce) {
+        cudaStream_t cs = static_cast<cudaStream_t>(st->copy_stream);
+        TKB_CUDA_C(cudaEventRecord(static_cast<cudaEvent_t>(st->ev_quantized), main));
+        TKB_CUDA_C(cudaStreamWaitEvent(cs, static_cast<cudaEvent_t>(st->ev_quantized), 0));
+        // every peer's kernel of epoch - 2 (the last reader of this buffer set) must be finished before it is written
+        if (epoch > 2)
+            if (int e = tkb_wait_flags(st->done[r], w, r, epoch - 2, st->copy_stream)) return e;
+        const size_t code_bytes = size_t(rows) * (st->K / 2), code_off = size_t(r) * code_bytes;
+        const size_t sc_bytes = size_t(rows / 128) * (st->K / 64) * 512, sc_off = size_t(r) * sc_bytes;
+        const int flags_per_rank = rows / 64;
+        for (int i = 1; i < w; i++) {
+            const int d = (r + w - i) % w;           // in the order in which the peers consume this rank's rows
+            TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->codes[b][d]) + code_off, my_codes, code_bytes, cudaMemcpyDeviceToDevice, cs));
+            TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->scales[b][d]) + sc_off, my_scales, sc_bytes, cudaMemcpyDeviceToDevice, cs));
+            set_flags_kernel<<<1, 64, 0, cs>>>(static_cast<unsigned int*>(st->arrived[b][d]) + size_t(r) * flags_per_rank, flags_per_rank, epoch);
+            TKB_CUDA_C(cudaGetLastError());
+        }
+        TKB_CUDA_C(cudaEventRecord(static_cast<cudaEvent_t>(st->ev_copied[b]), cs));
+    }
     return tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
-                             st->done, st->exit_counter, epoch, w > 1 ? comm_ctas : 0, stream);
+                             st->done, st->exit_counter, epoch, (w > 1 && !ce) ? comm_ctas : 0, stream);
 }
 
 } // extern "C"

@@ -108,7 +108,8 @@ class AllGatherMatmulNVFP4:
     that its kernel finished with the previous contents.
     """
 
-    def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None):
+    def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None,
+                 copy_engines: bool = False):
         self.arithmetic = arithmetic      # NVFP4 quantizer arithmetic (None = ops.default_nvfp4_arithmetic)
         if M % (256 * local_world_size):
             raise RuntimeError("M must be a multiple of 256 * world size")
@@ -140,6 +141,15 @@ class AllGatherMatmulNVFP4:
         for i in range(local_world_size):
             st.done[i] = self.flags.peer_ptr(i)
         st.amax, st.sg, st.exit_counter = self.amax.data_ptr(), self.sg.data_ptr(), self.exit_counter.data_ptr()
+        self.copy_engines = bool(copy_engines) and local_world_size > 1
+        if self.copy_engines:
+            # the gather travels by peer copies on a second stream; the library needs the raw stream and three events
+            self._copy_stream = torch.cuda.Stream()
+            self._events = [torch.cuda.Event() for _ in range(3)]
+            for ev in self._events:
+                ev.record()                         # creates the underlying CUDA event
+            st.copy_stream = self._copy_stream.cuda_stream
+            st.ev_quantized, st.ev_copied[0], st.ev_copied[1] = (ev.cuda_event for ev in self._events)
         self._state = st
         if local_world_size > 1:
             dist.barrier(group=group)
@@ -156,7 +166,7 @@ class AllGatherMatmulNVFP4:
         self.epoch += 1
         arith = ops._ARITH[self.arithmetic or ops.default_nvfp4_arithmetic]
         L.check(L.lib().tkb_ag_linear_nvfp4(C.byref(self._state), self.epoch, X_local.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
-                                            D.data_ptr(), 0, n_local, self.num_comm_sms, arith, _stream()))
+                                            D.data_ptr(), 0, n_local, -1 if self.copy_engines else self.num_comm_sms, arith, _stream()))
 
     def step_by_step(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
         lib = L.lib()
