@@ -2,21 +2,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic input:
+One JSON line on stdout (rank 0).  The workload is the same at every N, so the per-N lines form one strong-scaling curve:
 
-  N = 1   workload = MXFP8 GEMM M=N=K=8192 (bf16 ~N(0,1) with 1 % of entries x32, quantized to e4m3 with per-32
-          UE8M0 scales, fp32 accumulate, bf16 out).  `value` = TFLOP/s of the GEMM with operands resident in HBM;
-          `e2e` = the same FLOPs through the C-ABI calls a user makes, starting from bf16 matrices in pinned HOST
-          memory: H2D copies, both quantize launches, the GEMM and the D2H copy of D are all inside the timed region.
-  N > 1   workload = tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192 (weights N-sharded, activation rows sharded and
-          all-gathered over NVLink inside the GEMM kernel), strong scaling; the line also carries the time of the same
-          whole problem on one GPU.  `--workload moe` runs the expert-parallel MoE layer instead.
+  NVFP4 tensor-parallel GEMM M=8192 N=28672 K=8192: weights (NVFP4, N(0, 0.02)) sharded by output column over the N GPUs,
+  bf16 activation rows (N(0, 1)) sharded by row.  A step = every rank quantizes its rows to NVFP4 (the per-tensor amax is
+  max-reduced over NVLink inside the quantize kernel), the codes and scales are all-gathered over NVLink while the
+  tcgen05 GEMM already multiplies (own rows first), D[:, rank's columns] is written as bf16.  At N = 1 the same two
+  launches run on one GPU without an exchange.  `value` = 2*M*N*K / step time, whole job, operands resident in HBM;
+  `e2e` = the same step from bf16 rows in pinned HOST memory to the rank's output columns back in pinned host memory.
+  `extra` carries the other rows of the path measured the same way: the MXFP8 / NVFP4 / BF16 / FP8 GEMMs at 8192^3, the
+  quantizers, the skinny-M decode GEMM (HBM GB/s), and the expert-parallel MoE layer on the same N GPUs (`extra.moe`).
+
   `--case <kernel>` runs one kernel only (the commands of the ncu summaries under profiles/), `--workload tp_timeline`
-  prints per-launch times and the kernels' wait counters of the tensor-parallel step.
+  prints per-launch times and the kernels' wait counters of the tensor-parallel step, `--workload moe` the MoE layer alone.
 
-`--impl reference` times the reference's CPU implementation of the same GEMM arithmetic — its own naive kernels from
-kernels/gemm/common.cuh compiled for the host (oracle/_ref) when that build exists, otherwise the oracle's C++
-restatement — on all host cores, on a bounded row slab of the same workload.
+`--impl reference` times the reference's CPU implementation of the same GEMM arithmetic (its own naive NVFP4 kernel from
+kernels/gemm/common.cuh compiled for the host, oracle/_ref, when that build exists, otherwise the oracle's C++
+restatement) on all host cores, each step a bounded row slab of the same workload.
 """
 from __future__ import annotations
 
@@ -31,9 +33,20 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-M = N = K = 8192
+M = N = K = 8192                      # the 8192^3 side measurements
 FLOPS = 2.0 * M * N * K
+TP_M, TP_N, TP_K = 8192, 28672, 8192  # the headline workload
+TP_FLOPS = 2.0 * TP_M * TP_N * TP_K
 NOMINAL = {"bf16": 2250.0, "fp8": 4500.0, "fp4": 9000.0, "hbm_gbs": 8000.0}
+METRIC = "NVFP4 GEMM throughput (M=8192 N=28672 K=8192, tensor-parallel over the GPUs of the run)"
+WORKLOAD = ("NVFP4 tensor-parallel GEMM M=8192 N=28672 K=8192: weights ~N(0,0.02) N-sharded, bf16 activations ~N(0,1) row-sharded, "
+            "quantized on the fly, gathered over NVLink, bf16 out")
+DTYPE = "nvfp4 (e2m1 x ue4m3 block scales x fp32 tensor scale, fp32 accumulate)"
+CPU_SLAB_ROWS = 4
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel at N = 1 (the NVFP4 GEMM, M=8192 N=28672
+# K=8192), from an ncu capture of `python bench.py --case nvfp4_gemm --m 8192 --size 28672 --k 8192`; None = not captured.
+TP_GEMM_DRAM_BYTES = None
 
 
 def measured_peaks() -> dict:
@@ -110,51 +123,56 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU arm -----
-def cpu_reference_gemm(steps: int, warmup: int, rows: int = 16):
-    """Times the reference's CPU arithmetic for the N=1 workload on a `rows`-row slab (full N, full K)."""
+def cpu_reference_slab(steps: int, warmup: int, rows: int = CPU_SLAB_ROWS):
+    """Times the reference's CPU arithmetic for the headline workload on a `rows`-row slab (all 28672 columns, full K)
+    with every host core.  Returns (cpu_baseline dict, seconds per step)."""
+    # torchrun exports OMP_NUM_THREADS=1; this leg is the only CPU work of its process and takes every core
     import numpy as np
     import oracle as O
+    O.set_num_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(3)
-    A = rng.standard_normal((rows, K)).astype(np.float32)
-    A[rng.random((rows, K)) < 0.01] *= 32.0
-    # B: 8192 x 8192 generated in blocks to keep peak memory modest
-    B = rng.standard_normal((N, K)).astype(np.float32)
-    B[rng.random((N, K)) < 0.01] *= 32.0
-    ac, asc = O.mxfp8_quantize(O.f32_to_bf16(A))
-    bc, bsc = O.mxfp8_quantize(O.f32_to_bf16(B))
+    A = rng.standard_normal((128, TP_K), dtype=np.float32)           # a whole 128-row scale block; `rows` of it are multiplied
+    aq = O.nvfp4_quantize(O.f32_to_bf16(A))
+    B = (rng.standard_normal((TP_N, TP_K), dtype=np.float32) * np.float32(0.02))
+    bq = O.nvfp4_quantize(O.f32_to_bf16(B))
     del A, B
     ref = O.ref_host()
     cores = O.num_threads()
     if ref is not None:
         kind = "reference"
-        # the reference kernel indexes the scale tensor by row; give it a full 128-row block
-        D = np.empty((rows, N), np.uint16)
+        D = np.empty((rows, TP_N), np.uint16)
+        a_codes, a_sc, a_sg = np.ascontiguousarray(aq[0][:rows]), np.ascontiguousarray(aq[1]).reshape(-1), np.ascontiguousarray(aq[2], np.float32)
+        b_codes, b_sc, b_sg = np.ascontiguousarray(bq[0]), np.ascontiguousarray(bq[1]).reshape(-1), np.ascontiguousarray(bq[2], np.float32)
+
         def run():
-            ref.tkref_mxfp8_gemm(ac, asc.reshape(-1), bc, bsc.reshape(-1), D, rows, N, K)
+            ref.tkref_nvfp4_gemm(a_codes, a_sc, a_sg, b_codes, b_sc, b_sg, D, rows, TP_N, TP_K)
     else:
         kind = "port"
+
         def run():
-            O.mxfp8_gemm(ac, asc, bc, bsc, 0, rows)
+            O.nvfp4_gemm(*aq, *bq, 0, rows)
     for _ in range(warmup):
         run()
     t0 = time.perf_counter()
     for _ in range(steps):
         run()
     dt = (time.perf_counter() - t0) / steps
-    tflops = 2.0 * rows * N * K / dt * 1e-12
+    tflops = 2.0 * rows * TP_N * TP_K / dt * 1e-12
     return {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": kind,
-            "sample": f"{rows} of {M} output rows x full N={N} x full K={K} per step, {steps} steps ({dt:.2f} s/step)"}, dt
+            "sample": f"{rows} of {TP_M} output rows x all N={TP_N} columns x full K={TP_K} per step, {steps} steps ({dt:.2f} s/step), "
+                      f"{'the reference kernel reference_nvfp4_gemm_kernel compiled for the host' if kind == 'reference' else 'C++ restatement'}"}, dt
 
 
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    cb, dt = cpu_reference_gemm(max(1, args.steps), max(0, min(args.warmup, 1)), rows=16)
-    line = {"impl": "reference", "metric": "block-scaled GEMM throughput (MXFP8 8192^3)", "value": cb["value"], "unit": "TFLOP/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (M / 16),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8 (e4m3 x ue8m0, fp32 acc)",
-            "data": "synthetic", "config": {"workload": "MXFP8 GEMM M=N=K=8192, 1% x32 outliers", "timed": "CPU row slab"},
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    cb, dt = cpu_reference_slab(steps, warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": max(args.gpus, world), "steps": steps,
+            "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
+            "data": "synthetic", "config": {"workload": WORKLOAD},
+            "timed": "CPU: each step multiplies a bounded row slab of the workload (cpu_baseline.sample); value = the slab's FLOPs / its time",
             "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -170,80 +188,129 @@ def synth(torch, dev, rows, cols, seed, std=1.0, outliers=0.0):
     return x.to(torch.bfloat16)
 
 
-def event_time(torch, fn, steps, cooldown=0.5, sampler=None):
+def event_time(torch, fn, steps, cooldown=0.5, sampler=None, host=None):
     """CUDA-event time per step on the current stream.  A 500 ms idle period precedes the timed loop, as in the
     reference's own protocol (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:673-700), so the loop starts from the
-    same thermal/power state every time."""
+    same thermal/power state every time.  `host`, if given, receives the host time spent enqueueing one step."""
     s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     time.sleep(cooldown)
     s.record()
+    t0 = time.perf_counter()
     for i in range(steps):
         fn(i)
+    t1 = time.perf_counter()
     e.record()
+    if host is not None:
+        host.append((t1 - t0) / steps)
     if sampler is not None:
         sampler.poll_until(e.query)       # clocks while the GPU works through the queue; the host launches are over
     torch.cuda.synchronize()
     return s.elapsed_time(e) * 1e-3 / steps
 
 
-def run_tp(args) -> None:
-    """N > 1: tensor-parallel NVFP4 GEMM M=8192 N=28672 K=8192, weights column(N)-sharded, bf16 activation rows sharded
-    and all-gathered (as NVFP4 codes + scales) over NVLink inside the GEMM kernel.  Strong scaling."""
-    import torch
-    import torch.distributed as dist
+class Dist:
+    """Rank bookkeeping; torch.distributed (NCCL) only when the run has more than one rank."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", "0")); self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def gather_settings(args, world):
+    """--comm-sms: 0 = default (copy engines for N > 1), -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel."""
+    if world == 1:
+        return False, 0
+    if args.comm_sms > 0:
+        return False, args.comm_sms
+    return True, 0
+
+
+def measure_tp(args, D_) -> dict:
+    """The headline workload on the run's GPUs (see the module docstring)."""
+    torch = D_.torch
     import thunderkittens_b200.ops as ops
     from thunderkittens_b200 import _lib, parallel
-
-    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
-    Mt, Nt, Kt = 8192, 28672, 8192
-    n_local, rows = Nt // world, Mt // world
+    rank, world, dev = D_.rank, D_.world, D_.dev
+    n_local, rows = TP_N // world, TP_M // world
     u8 = torch.uint8
     GROUPS = 3
-    # comm CTAs: 20 at 4 and 8 GPUs leaves 64 CTA pairs, which divide the 896 / 448 output tiles of a rank into whole waves
-    comm = args.comm_sms if args.comm_sms > 0 else (8 if world <= 2 else 20)
-    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local_rank, world, num_comm_sms=comm, copy_engines=args.comm_sms < 0)   # --comm-sms -1: copy-engine gather
+    ce, comm = gather_settings(args, world)
+    op = parallel.AllGatherMatmulNVFP4(TP_M, TP_K, D_.local_rank, world, num_comm_sms=max(comm, 2), copy_engines=ce, copy_streams=args.copy_streams)
     sets = []
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     for gi in range(GROUPS):
         # weight shard: rows [rank*n_local, ...) of a seeded N(0, 0.02) matrix, quantized with the all-reduced amax
-        W = synth(torch, dev, n_local, Kt, 800 + 10 * gi + rank, std=0.02)
+        W = synth(torch, dev, n_local, TP_K, 800 + 10 * gi + rank, std=0.02)
         ops.absmax_bf16(W, amax_w)
-        dist.all_reduce(amax_w, op=dist.ReduceOp.MAX)
-        wc = torch.empty(n_local, Kt // 2, dtype=u8, device=dev); ws = torch.empty((n_local + 127) // 128, Kt // 64, 512, dtype=u8, device=dev)
+        if world > 1:
+            D_.dist.all_reduce(amax_w, op=D_.dist.ReduceOp.MAX)
+        wc = torch.empty(n_local, TP_K // 2, dtype=u8, device=dev); ws = torch.empty((n_local + 127) // 128, TP_K // 64, 512, dtype=u8, device=dev)
         wg = torch.empty(1, dtype=torch.float32, device=dev)
         ops.nvfp4_quantize(W, wc, ws, wg, False, amax=amax_w)
-        X = synth(torch, dev, rows, Kt, 700 + 10 * gi + rank)
-        sets.append((X, wc, ws, wg, torch.empty(Mt, n_local, dtype=torch.bfloat16, device=dev)))
+        X = synth(torch, dev, rows, TP_K, 700 + 10 * gi + rank)
+        sets.append((X, wc, ws, wg, torch.empty(TP_M, n_local, dtype=torch.bfloat16, device=dev)))
         del W
     hostX = sets[0][0].cpu().pin_memory()
-    hostD = torch.empty(Mt, n_local, dtype=torch.bfloat16).pin_memory()
+    hostD = torch.empty(TP_M, n_local, dtype=torch.bfloat16).pin_memory()
     torch.cuda.synchronize()
 
     def step(i):
         X, wc, ws, wg, D = sets[i % GROUPS]
         op(X, wc, ws, wg, D)
 
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for i in range(warm):
         step(i)
-    barrier()
-    cs = ClockSampler(local_rank)
-    dt = event_time(torch, step, args.steps, sampler=cs)
+    D_.barrier()
+    cs = ClockSampler(D_.local_rank)
+    host = []
+    dt = event_time(torch, step, args.steps, sampler=cs, host=host)
     clocks = cs.summary()
-    assert _lib.device_status() == 0, "a device-side wait timed out"
-    t = torch.tensor([dt], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dt = float(t.item())
-    barrier()
+    status = _lib.device_status()
+    dt = D_.max(dt)
+    D_.barrier()
 
-    dX = torch.empty(rows, Kt, dtype=torch.bfloat16, device=dev)
+    # per-launch breakdown of the same step (events between the launches of a step; a separate short loop so that the
+    # events do not sit inside the timed region above)
+    quant_us = gemm_us = None
+    if world == 1:
+        X, wc, ws, wg, D = sets[0]
+        xc = torch.empty(TP_M, TP_K // 2, dtype=u8, device=dev); xs = torch.empty(TP_M // 128, TP_K // 64, 512, dtype=u8, device=dev)
+        xg = torch.empty(1, dtype=torch.float32, device=dev)
+        for i in range(3):
+            ops.nvfp4_quantize(X, xc, xs, xg, False)
+        quant_us = event_time(torch, lambda i: ops.nvfp4_quantize(sets[i % GROUPS][0], xc, xs, xg, False), 10, cooldown=0.1) * 1e6
+        gemm_us = event_time(torch, lambda i: ops.nvfp4_gemm(xc, xs, xg, *sets[i % GROUPS][1:4], sets[i % GROUPS][4]), 10, cooldown=0.1) * 1e6
+        del xc, xs, xg
+    else:
+        gemm_us = max(dt * 1e6 - 0.0, 0.0)      # at N > 1 the GEMM kernel spans the gather; the step time is its upper bound
+
+    # end to end: pinned host rows -> H2D -> step -> D2H of this rank's output columns
+    dX = torch.empty(rows, TP_K, dtype=torch.bfloat16, device=dev)
     _, wc, ws, wg, D = sets[0]
 
     def e2e_step(i):
@@ -253,104 +320,44 @@ def run_tp(args) -> None:
 
     for i in range(2):
         e2e_step(i)
-    barrier()
-    dt_e2e = event_time(torch, e2e_step, max(3, min(args.steps, 10)))
-    t = torch.tensor([dt_e2e], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dt_e2e = float(t.item())
-    barrier()
-    # The same whole problem on ONE GPU (quantize of all 8192 activation rows + the full-N GEMM, no exchange), measured on
-    # rank 0 while the other ranks idle: the T(1) of the strong-scaling curve.
-    single = None
-    if rank == 0 and not args.no_extra:
-        del sets
-        torch.cuda.empty_cache()
-        Xf = synth(torch, dev, Mt, Kt, 700)
-        Wf = synth(torch, dev, Nt, Kt, 800, std=0.02)
-        wcf = torch.empty(Nt, Kt // 2, dtype=u8, device=dev); wsf = torch.empty(Nt // 128, Kt // 64, 512, dtype=u8, device=dev)
-        wgf = torch.empty(1, dtype=torch.float32, device=dev)
-        ops.nvfp4_quantize(Wf, wcf, wsf, wgf, False)
-        del Wf
-        xcf = torch.empty(Mt, Kt // 2, dtype=u8, device=dev); xsf = torch.empty(Mt // 128, Kt // 64, 512, dtype=u8, device=dev)
-        xgf = torch.empty(1, dtype=torch.float32, device=dev)
-        Df = [torch.empty(Mt, Nt, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-
-        def one_gpu(i):
-            ops.nvfp4_quantize(Xf, xcf, xsf, xgf, False)
-            ops.nvfp4_gemm(xcf, xsf, xgf, wcf, wsf, wgf, Df[i % 2])
-
-        for i in range(3):
-            one_gpu(i)
-        t1 = event_time(torch, one_gpu, max(3, min(args.steps, 10)))
-        single = {"ms_per_step": t1 * 1e3, "tflops": 2.0 * Mt * Nt * Kt / t1 * 1e-12,
-                  "what": "tkb_nvfp4_quantize of the 8192 x 8192 activations + tkb_nvfp4_gemm with all 28672 weight rows on rank 0's GPU"}
-        del Xf, wcf, wsf, xcf, xsf, Df
-    barrier()
-    if rank == 0:
-        pk = measured_peaks()
-        flops = 2.0 * Mt * Nt * Kt
-        tf = flops / dt * 1e-12
-        peak = 4.0 * pk["bf16_tflops"] * world
-        nvl_bytes = (world - 1) / world * Mt * (Kt // 2 + Kt // 16)
-        line = {
-            "metric": "tensor-parallel NVFP4 GEMM throughput (M=8192 N=28672 K=8192)", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 x fp32, fp32 acc)", "data": "synthetic",
-            "config": {"workload": "TP NVFP4 GEMM M=8192 N=28672 K=8192: weights N-sharded, bf16 activation rows sharded, per step two launches: "
-                                   "quantize with the amax max-reduced over NVLink inside the kernel, then the NVFP4 all-gather over NVLink "
-                                   "fused with the tcgen05 GEMM", "parallelism": f"tp{world}",
-                       "l2": f"{GROUPS} rotating weight/activation/output sets", "comm_ctas": 0 if op.copy_engines else op.num_comm_sms,
-                       "gather": "copy engines (peer cudaMemcpyAsync on a second stream)" if op.copy_engines else "comm CTAs of the GEMM kernel"},
-            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": 4.0 * pk["bf16_tflops"], "unit": "TFLOP/s per GPU",
-                         "frac": tf / peak, "traffic": None, "kernel": "tkb::gemm_kernel<NVFP4, cta pair, N256, all-gather>",
-                         "peak_source": f"4 x {pk['source']} cuBLAS bf16 burst (derived dense FP4 ceiling)",
-                         "nvlink_bytes_in_per_gpu": nvl_bytes, "nvlink_time_at_770GBs_ms": nvl_bytes / 770e9 * 1e3},
-            "e2e": {"value": flops / dt_e2e * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": rows * Kt * 2 * world,
-                    "d2h_bytes_per_step": Mt * n_local * 2 * world, "ms_per_step": dt_e2e * 1e3,
-                    "path": "pinned host bf16 shard -> H2D -> AllGatherMatmulNVFP4 -> D2H of the rank's output columns"},
-            "gpu_launches": args.steps * 2 * world, "clocks": clocks, "single_gpu_same_problem": single,
-            "scaling_note": "strong scaling of ONE problem: the 1-GPU time of this problem is single_gpu_same_problem.ms_per_step; the N=1 line of "
-                            "this benchmark is a different workload (MXFP8 GEMM 8192^3, BASELINE configs[1]) and not the T(1) of this curve",
-        }
-        print(json.dumps(line), flush=True)
+    D_.barrier()
+    dt_e2e = D_.max(event_time(torch, e2e_step, max(3, min(args.steps, 10))))
+    status |= _lib.device_status()
+    D_.barrier()
     op.close()
-    dist.destroy_process_group()
+    del sets, dX
+    torch.cuda.empty_cache()
+    return {"dt": dt, "dt_e2e": dt_e2e, "clocks": clocks, "status": status, "host_enqueue_us": statistics.median(host) * 1e6 if host else None,
+            "quant_us": quant_us, "gemm_us": gemm_us, "copy_engines": ce, "comm_ctas": comm, "warmup": warm, "groups": GROUPS,
+            "h2d": rows * TP_K * 2 * world, "d2h": TP_M * n_local * 2 * world}
 
 
-def run_moe(args) -> None:
-    """MoE layer (BASELINE configs[4]): 16384 tokens, hidden 7168, 128 experts, intermediate 2048, top-8 routing from a
-    softmax over seeded N(0,1) logits, NVFP4 expert weights ~N(0,0.02), experts and tokens sharded over the ranks.
+def measure_moe(args, D_, steps: int) -> dict:
+    """MoE layer: 16384 tokens, hidden 7168, 128 experts, intermediate 2048, top-8 routing from a softmax over seeded
+    N(0,1) logits, NVFP4 expert weights ~N(0,0.02), experts and tokens sharded over the ranks.
     A step = route -> schedule -> quantize -> dispatch fused with the grouped GEMM -> combine."""
-    import torch
-    import torch.distributed as dist
+    torch = D_.torch
     import thunderkittens_b200.ops as ops
     from thunderkittens_b200 import _lib, parallel
-
-    rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    rank, world, dev = D_.rank, D_.world, D_.dev
     T, H, I, E, k = 16384, 7168, 2048, 128, 8
     Tl, El = T // world, E // world
     u8 = torch.uint8
-    layer = parallel.MoELayerNVFP4(T, H, I, E, k, local_rank, world, num_comm_sms=args.comm_sms if args.comm_sms > 0 else 32)
+    comm = args.moe_comm_sms if args.moe_comm_sms > 0 else 32
+    layer = parallel.MoELayerNVFP4(T, H, I, E, k, D_.local_rank, world, num_comm_sms=comm)
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     wc = torch.empty(El * I, H // 2, dtype=u8, device=dev); ws = torch.empty(El * I // 128, H // 64, 512, dtype=u8, device=dev)
     wg = torch.empty(1, dtype=torch.float32, device=dev)
-    for e in range(El):       # expert by expert to keep the bf16 staging small
+    common = torch.zeros(1, dtype=torch.float32, device=dev)
+    for e in range(El):       # expert by expert to keep the bf16 staging small; one common per-tensor scale
         W = synth(torch, dev, I, H, 1100 + rank * El + e, std=0.02)
-        ops.absmax_bf16(W, amax_w)     # per-expert amax is fine for a benchmark; one common scale is used below
-        if e == 0:
-            common = amax_w.clone()
-        else:
-            common = torch.maximum(common, amax_w)
+        ops.absmax_bf16(W, amax_w)
+        common = torch.maximum(common, amax_w)
         del W
     if world > 1:
-        dist.all_reduce(common, op=dist.ReduceOp.MAX)
+        D_.dist.all_reduce(common, op=D_.dist.ReduceOp.MAX)
     for e in range(El):
         W = synth(torch, dev, I, H, 1100 + rank * El + e, std=0.02)
-        sg_tmp = torch.empty(1, dtype=torch.float32, device=dev)
         ops.nvfp4_quantize(W, wc[e * I:(e + 1) * I], ws[e * I // 128:(e + 1) * I // 128], wg, False, amax=common)
         del W
     sets = [(synth(torch, dev, Tl, E, 900 + 10 * gi + rank).float(), synth(torch, dev, Tl, H, 1000 + 10 * gi + rank)) for gi in range(3)]
@@ -360,140 +367,31 @@ def run_moe(args) -> None:
         lg, X = sets[i % 3]
         layer.forward(lg, X, wc, ws, wg)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(max(args.warmup, 3)):
+    for i in range(3):
         step(i)
-    barrier()
-    dt = event_time(torch, step, args.steps)
+    D_.barrier()
+    dt = D_.max(event_time(torch, step, steps, cooldown=0.2))
     st = _lib.device_status()
-    if world > 1:
-        t = torch.tensor([dt], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
     rows = int(layer.num_blocks.item()) * 128
-    if rank == 0:
-        flops = 2.0 * T * k * H * I
-        print(json.dumps({"metric": "MoE layer throughput (16384 tokens, H 7168, 128 experts, I 2048, top-8, NVFP4)", "value": flops / dt * 1e-12,
-                          "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "ms_per_step": dt * 1e3, "scaling": "strong",
-                          "device_status": st, "rank0_padded_rows": rows, "comm_ctas": layer.num_comm_sms,
-                          "dispatch_bytes_in_per_gpu": (world - 1) / world * T * k / world * (H // 2 + H // 16),
-                          "combine_bytes_in_per_gpu": (world - 1) / world * Tl * k * I * 2,
-                          "config": {"workload": "MoE layer", "parallelism": f"ep{world}"}}), flush=True)
-    barrier()
+    D_.barrier()
     layer.close()
-    if world > 1:
-        dist.destroy_process_group()
+    del wc, ws, sets
+    torch.cuda.empty_cache()
+    flops = 2.0 * T * k * H * I
+    return {"metric": "MoE layer (16384 tokens, hidden 7168, 128 experts, intermediate 2048, top-8, NVFP4 up-projection + combine)",
+            "ms_per_step": dt * 1e3, "tflops": flops / dt * 1e-12, "n_gpus": world, "steps": steps, "device_status": st, "comm_ctas": comm,
+            "rank0_padded_rows": rows, "dispatch_bytes_in_per_gpu": (world - 1) / world * T * k / world * (H // 2 + H // 16),
+            "combine_bytes_in_per_gpu": (world - 1) / world * Tl * k * I * 2,
+            "parity": "routing and combine have no counterpart in the reference (unpinned); dispatch + grouped GEMM are checked against the oracle"}
 
 
-def run_tp_timeline(args) -> None:
-    """Diagnostic for the tensor-parallel step (N > 1, torchrun): CUDA events around each of the two launches of a step
-    inside a free-running loop, plus the kernels' own wait counters (tkb_gemm_set_profile_buffer) for the last step of
-    the loop.  Prints one JSON line from rank 0 and one from rank world/2.  Not a benchmark line."""
-    import ctypes
-    import numpy as np
+def run_moe(args) -> None:
     import torch
-    import torch.distributed as dist
-    import thunderkittens_b200.ops as ops
-    from thunderkittens_b200 import _lib as L, parallel
-
-    rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    Mt, Nt, Kt = 8192, 28672, 8192
-    nl, rows = Nt // world, Mt // world
-    lib, s = L.lib(), torch.cuda.current_stream().cuda_stream
-    comm = args.comm_sms if args.comm_sms > 0 else (8 if world <= 2 else 20)
-    op = parallel.AllGatherMatmulNVFP4(Mt, Kt, local, world, num_comm_sms=comm)
-    X = synth(torch, dev, rows, Kt, 700 + rank)
-    W = synth(torch, dev, nl, Kt, 800 + rank, std=0.02)
-    u8 = torch.uint8
-    wc = torch.empty(nl, Kt // 2, dtype=u8, device=dev); ws = torch.empty((nl + 127) // 128, Kt // 64, 512, dtype=u8, device=dev)
-    wg = torch.empty(1, dtype=torch.float32, device=dev)
-    ops.nvfp4_quantize(W, wc, ws, wg, False)
-    D = torch.empty(Mt, nl, dtype=torch.bfloat16, device=dev)
-    arith = ops._ARITH[ops.default_nvfp4_arithmetic]
-
-    def two(ev=None):       # the two launches of tkb_ag_linear_nvfp4, issued one by one so that an event fits in between
-        op.epoch += 1
-        e, b = op.epoch, op.epoch % 2
-        codes, scales = op.codes[b], op.scales[b]
-        mc = codes.data_[rank * rows:(rank + 1) * rows]; ms = scales.data_[rank * rows // 128:(rank + 1) * rows // 128]
-        if ev:
-            ev[0].record()
-        L.check(lib.tkb_nvfp4_quantize_sharded(X.data_ptr(), 0, mc.data_ptr(), ms.data_ptr(), op.sg.data_ptr(), rows, Kt, 0, arith,
-                                               op.slots[b].peer_ptr_array(), world, rank, e, s))
-        if ev:
-            ev[1].record()
-        L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), op.sg.data_ptr(), wc.data_ptr(), ws.data_ptr(), wg.data_ptr(),
-                                      D.data_ptr(), 0, Mt, nl, Kt, rank, world, op.arrived[b].peer_ptr_array(), op.flags.peer_ptr_array(),
-                                      op.exit_counter.data_ptr(), e, op.num_comm_sms, s))
-        if ev:
-            ev[2].record()
-
-    for _ in range(max(args.warmup, 3)):
-        two()
-    torch.cuda.synchronize(); dist.barrier()
-    prof = torch.zeros(148 * 8, dtype=torch.int64, device=dev)
-    setp = L.bind("tkb_gemm_set_profile_buffer", [ctypes.c_void_p])
-    setp(prof.data_ptr())
-    steps = max(args.steps, 4)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
-    for i in range(steps):
-        two(evs[i])
-    torch.cuda.synchronize()
-    setp(None)
-    q = np.array([evs[i][0].elapsed_time(evs[i][1]) for i in range(steps)]) * 1e3
-    g = np.array([evs[i][1].elapsed_time(evs[i][2]) for i in range(steps)]) * 1e3
-    pr = prof.cpu().numpy().reshape(148, 8)
-    lead = pr[op.num_comm_sms::2]
-    lead = lead[lead[:, 4] > 0]
-    if len(lead) == 0:
-        lead = np.zeros((1, 8), np.int64)
-    med = lambda a: float(np.median(a))
-    out = {"rank": rank, "n_gpus": world, "comm_ctas": op.num_comm_sms, "step_us": evs[0][0].elapsed_time(evs[-1][2]) * 1e3 / steps,
-           "quantize_us_median_max": [med(q), float(q.max())], "ag_gemm_us_median_max": [med(g), float(g.max())],
-           "cycles_of_last_step": {"mma_total": med(lead[:, 4]), "mma_waiting_for_operands": med(lead[:, 3]), "mma_waiting_for_drain": med(lead[:, 2]),
-                                   "producer_waiting_for_remote_rows": med(lead[:, 7]), "comm_cta_total": med(pr[:op.num_comm_sms, 0]),
-                                   "comm_cta_waiting_done_flags": med(pr[:op.num_comm_sms, 1]), "comm_cta_fence_and_flag": med(pr[:op.num_comm_sms, 2])},
-           "device_status": L.device_status()}
-    # The exchange alone: the same two launches with only 256 weight rows, so that the multiplying CTAs have next to
-    # nothing to do and the fused kernel lasts as long as the pushes (bytes in per GPU: (world-1)/world * M * K * 0.5625).
-    n_small = 256
-    Ds = torch.empty(Mt, n_small, dtype=torch.bfloat16, device=dev)
-
-    def push_only(ev):
-        op.epoch += 1
-        e, b = op.epoch, op.epoch % 2
-        codes, scales = op.codes[b], op.scales[b]
-        mc = codes.data_[rank * rows:(rank + 1) * rows]; ms = scales.data_[rank * rows // 128:(rank + 1) * rows // 128]
-        L.check(lib.tkb_nvfp4_quantize_sharded(X.data_ptr(), 0, mc.data_ptr(), ms.data_ptr(), op.sg.data_ptr(), rows, Kt, 0, arith,
-                                               op.slots[b].peer_ptr_array(), world, rank, e, s))
-        ev[0].record()
-        L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), op.sg.data_ptr(), wc.data_ptr(), ws.data_ptr(), wg.data_ptr(),
-                                      Ds.data_ptr(), 0, Mt, n_small, Kt, rank, world, op.arrived[b].peer_ptr_array(), op.flags.peer_ptr_array(),
-                                      op.exit_counter.data_ptr(), e, op.num_comm_sms, s))
-        ev[1].record()
-
-    dist.barrier()
-    pe = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(6)]
-    for i in range(6):
-        push_only(pe[i])
-    torch.cuda.synchronize()
-    pt = np.array([pe[i][0].elapsed_time(pe[i][1]) for i in range(2, 6)]) * 1e3
-    bytes_in = (world - 1) / world * Mt * (Kt // 2 + Kt // 16)
-    out["exchange_alone_us_median"] = med(pt)
-    out["exchange_alone_gbs_in_per_gpu"] = bytes_in / (med(pt) * 1e-6) * 1e-9
-    out["device_status"] = L.device_status()
-    if rank in (0, world // 2):
+    D_ = Dist(torch)
+    out = measure_moe(args, D_, args.steps)
+    if D_.rank == 0:
         print(json.dumps(out), flush=True)
-    dist.barrier()
-    op.close()
-    dist.destroy_process_group()
+    D_.close()
 
 
 def run_ours(args) -> None:
@@ -501,171 +399,66 @@ def run_ours(args) -> None:
         return run_moe(args)
     if args.workload == "tp_timeline":
         return run_tp_timeline(args)
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        return run_tp(args)
     import torch
-    import torch.distributed as dist
-    import thunderkittens_b200.ops as ops
     from thunderkittens_b200 import _lib
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     _lib.lib()   # fail loudly if the CUDA library is missing
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    u8 = torch.uint8
-    GROUPS = 3   # rotating operand sets: 3 x (64 + 64 + 128 MiB) so every launch starts with a cold L2
-    groups = []
-    for gi in range(GROUPS):
-        A = synth(torch, dev, M, K, 3 + 10 * gi + 100 * rank, outliers=0.01)
-        B = synth(torch, dev, N, K, 4 + 10 * gi + 100 * rank, outliers=0.01)
-        a = torch.empty(M, K, dtype=u8, device=dev); asc = torch.empty(M // 128, K // 128, 512, dtype=u8, device=dev)
-        b = torch.empty(N, K, dtype=u8, device=dev); bsc = torch.empty(N // 128, K // 128, 512, dtype=u8, device=dev)
-        ops.mxfp8_quantize(A, a, asc); ops.mxfp8_quantize(B, b, bsc)
-        groups.append((a, asc, b, bsc, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
-        if gi == 0:
-            hostA = A.cpu().pin_memory(); hostB = B.cpu().pin_memory()
-        del A, B
-    torch.cuda.synchronize()
-
-    def step(i):
-        ops.mxfp8_gemm(*groups[i % GROUPS])
-
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    barrier()
-    cs = ClockSampler(local_rank)
-    dt = event_time(torch, step, args.steps, sampler=cs)
-    clocks = cs.summary()
-    assert _lib.device_status() == 0, "a device-side wait timed out"
-    if world > 1:
-        t = torch.tensor([dt], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
-    barrier()
-
-    # end to end: bf16 in pinned host memory -> H2D -> quantize x2 -> GEMM -> D2H
-    dA = torch.empty(M, K, dtype=torch.bfloat16, device=dev); dB = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
-    hostD = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-    a, asc, b, bsc, D = groups[0]
-
-    def e2e_step(i):
-        dA.copy_(hostA, non_blocking=True); dB.copy_(hostB, non_blocking=True)
-        ops.mxfp8_quantize(dA, a, asc); ops.mxfp8_quantize(dB, b, bsc)
-        ops.mxfp8_gemm(a, asc, b, bsc, D)
-        hostD.copy_(D, non_blocking=True)
-
-    e2e_steps = max(3, min(args.steps, 10))
-    for i in range(2):
-        e2e_step(i)
-    barrier()
-    dt_e2e = event_time(torch, e2e_step, e2e_steps)
-    if world > 1:
-        t = torch.tensor([dt_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt_e2e = float(t.item())
-
-    # The same step as a user would stream it: copies on their own streams and two buffer sets, so the H2D copy of step
-    # i+1 and the D2H copy of step i-1 overlap step i's kernels.  Every step still moves all of its bytes inside the
-    # timed region.  The number is used only if the pipeline ran and its last results equal the device buffers.
-    dt_e2e_serial, e2e_mode = dt_e2e, "serial: H2D, kernels and D2H of a step one after the other on one stream"
-    if world == 1:
-        try:
-            main = torch.cuda.current_stream()
-            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-            sets = [(dA, dB, groups[0], hostD), (torch.empty_like(dA), torch.empty_like(dB), groups[1], torch.empty_like(hostD).pin_memory())]
-            ev_in = [torch.cuda.Event() for _ in range(2)]; ev_done = [torch.cuda.Event() for _ in range(2)]; ev_out = [torch.cuda.Event() for _ in range(2)]
-
-            def piped_step(i):
-                k = i % 2
-                dAk, dBk, (a_, asc_, b_, bsc_, D_), hostDk = sets[k]
-                s_in.wait_event(ev_done[k])              # the kernels of step i-2 have consumed this set's inputs
-                with torch.cuda.stream(s_in):
-                    dAk.copy_(hostA, non_blocking=True); dBk.copy_(hostB, non_blocking=True)
-                    ev_in[k].record(s_in)
-                main.wait_event(ev_in[k])
-                main.wait_event(ev_out[k])               # this set's D has been copied out by step i-2
-                ops.mxfp8_quantize(dAk, a_, asc_); ops.mxfp8_quantize(dBk, b_, bsc_)
-                ops.mxfp8_gemm(a_, asc_, b_, bsc_, D_)
-                ev_done[k].record(main)
-                s_out.wait_event(ev_done[k])
-                with torch.cuda.stream(s_out):
-                    hostDk.copy_(D_, non_blocking=True)
-                    ev_out[k].record(s_out)
-
-            def piped_loop(steps):
-                s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                time.sleep(0.5)
-                s.record(main)
-                for i in range(steps):
-                    piped_step(i)
-                main.wait_stream(s_in); main.wait_stream(s_out)      # the last D2H copies are inside the timed region
-                e.record(main)
-                torch.cuda.synchronize()
-                return s.elapsed_time(e) * 1e-3 / steps
-
-            piped_loop(2)
-            dt_piped = piped_loop(e2e_steps)
-            same = all(torch.equal(sets[k][3], sets[k][2][4].cpu()) for k in range(2))
-            if same and 0.0 < dt_piped < dt_e2e_serial:
-                dt_e2e = dt_piped
-                e2e_mode = "pipelined: copies on their own streams, two buffer sets (H2D of step i+1 and D2H of step i-1 overlap step i's kernels)"
-            del sets
-        except Exception as ex:      # keep the serial number
-            e2e_mode += f" (pipelined variant failed: {repr(ex)[:120]})"
-        torch.cuda.synchronize()
-
+    D_ = Dist(torch)
+    rank, world = D_.rank, D_.world
+    tp = measure_tp(args, D_)
+    assert tp["status"] == 0, f"a device-side wait timed out or a capacity check failed (status {tp['status']})"
     extras = {}
-    if rank == 0 and not args.no_extra:
-        extras = side_measurements(torch, ops, dev)
+    if not args.no_extra:
+        try:
+            extras["moe"] = measure_moe(args, D_, max(5, min(args.steps, 10)))
+        except Exception as e:      # side measurements never invalidate the headline line
+            extras["moe"] = {"error": repr(e)[:300]}
         if world == 1:
+            import thunderkittens_b200.ops as ops
+            extras.update(side_measurements(torch, ops, D_.dev))
             torch.cuda.synchronize()
             extras["reference_gpu_kernels_8192"] = reference_gpu_kernels()
-
     if rank == 0:
         pk = measured_peaks()
-        tflops = FLOPS / dt * 1e-12
-        peak = 2.0 * pk["bf16_tflops"]
+        dt, dt_e2e = tp["dt"], tp["dt_e2e"]
+        tf = TP_FLOPS / dt * 1e-12
+        peak = 4.0 * pk["bf16_tflops"]
+        gemm_tf = TP_FLOPS / world / (tp["gemm_us"] * 1e-6) * 1e-12
+        nvl_bytes = (world - 1) / world * TP_M * (TP_K // 2 + TP_K // 16)
         line = {
-            "metric": "block-scaled GEMM throughput (MXFP8 8192^3)", "value": tflops * world, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "mxfp8 (e4m3 x ue8m0, fp32 acc)", "data": "synthetic",
-            "config": {"workload": "MXFP8 GEMM M=N=K=8192, bf16~N(0,1) with 1% x32 outliers, per-32 UE8M0 scales, bf16 out",
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
-                       "l2": f"{GROUPS} rotating operand sets of 256 MiB (> 126 MB L2)"},
-            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                         "traffic": MXFP8_GEMM_DRAM_BYTES, "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/mxfp8_gemm_ncu.md)",
-                         "algorithmic_bytes": 2 * M * K + 2 * (M // 128) * (K // 128) * 512 + M * N * 2,
-                         "kernel": "tkb::gemm_kernel<MXFP8, cta pair, N256>",
-                         "peak_source": f"2 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense FP8 ceiling)",
-                         "frac_of_nominal_4500": tflops / NOMINAL["fp8"]},
-            "e2e": {"value": FLOPS / dt_e2e * 1e-12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
-                    "d2h_bytes_per_step": M * N * 2, "ms_per_step": dt_e2e * 1e3, "serial_ms_per_step": dt_e2e_serial * 1e3, "mode": e2e_mode,
-                    "path": "pinned host bf16 -> H2D -> tkb_mxfp8_quantize x2 -> tkb_mxfp8_gemm -> D2H"},
-            "gpu_launches": args.steps, "clocks": clocks, "extra": extras,
+            "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": tp["warmup"],
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                       "l2": f"{tp['groups']} rotating weight / activation / output sets (> 126 MB L2)",
+                       "gather": "none (one GPU)" if world == 1 else ("copy engines: one peer cudaMemcpyAsync per destination for codes, scales and "
+                                 "arrival flags" if tp["copy_engines"] else f"{tp['comm_ctas']} comm CTAs of the GEMM kernel"),
+                       "launches_per_step": "tkb_nvfp4_quantize_sharded + tkb_ag_gemm_nvfp4 (one call: tkb_ag_linear_nvfp4)"},
+            "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": peak, "unit": "TFLOP/s per GPU", "frac": gemm_tf / peak,
+                         "peak_derived": True, "peak_source": f"4 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense-FP4 ceiling; "
+                                                              "no FP4 figure is in the measured peaks)",
+                         "frac_of_nominal_9000": gemm_tf / NOMINAL["fp4"],
+                         "kernel": "tkb::gemm_kernel<NVFP4, cta pair, N256, all-gather>",
+                         "kernel_us": tp["gemm_us"], "kernel_us_how": "CUDA events around 10 launches of the GEMM alone on the rotating sets" if world == 1
+                         else "the step time (the GEMM kernel spans the gather): a lower bound on achieved",
+                         "algorithmic_flops_per_launch": TP_FLOPS / world, "traffic": TP_GEMM_DRAM_BYTES if world == 1 else None,
+                         "traffic_unit": "bytes per launch, dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of this kernel and shape",
+                         "algorithmic_bytes": TP_M * TP_K // 2 + TP_N * TP_K // 2 + (TP_M + TP_N) * TP_K // 16 + TP_M * TP_N * 2,
+                         "nvlink_bytes_in_per_gpu": nvl_bytes, "nvlink_time_at_770GBs_ms": nvl_bytes / 770e9 * 1e3},
+            "e2e": {"value": TP_FLOPS / dt_e2e * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": tp["h2d"], "d2h_bytes_per_step": tp["d2h"],
+                    "ms_per_step": dt_e2e * 1e3,
+                    "path": "pinned host bf16 rows -> H2D -> AllGatherMatmulNVFP4 (tkb_ag_linear_nvfp4) -> D2H of the rank's output columns"},
+            "gpu_launches": args.steps * 2 * world, "host_enqueue_us_per_step": tp["host_enqueue_us"],
+            "step_breakdown_us": {"quantize": tp["quant_us"], "gemm": tp["gemm_us"]} if world == 1 else None,
+            "clocks": tp["clocks"], "extra": extras,
         }
         if world == 1 and not args.no_extra:
-            cb, _ = cpu_reference_gemm(3, 1, rows=16)
+            cb, _ = cpu_reference_slab(3, 1)
+            line["cpu_baseline"] = cb
+        elif not args.no_extra:
+            cb, _ = cpu_reference_slab(2, 1)
             line["cpu_baseline"] = cb
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 8192^3 MXFP8 GEMM (ncu capture summarised in
-# profiles/mxfp8_gemm_ncu.md): 348.0 MB read + 116.8 MB written.
-MXFP8_GEMM_DRAM_BYTES = 464.8e6
+    D_.barrier()
+    D_.close()
 
 
 # The reference's own GPU kernels (built from its tree into oracle/_ref/tk_<which> by oracle/build.py:build_ref_gpu) timed with
@@ -730,6 +523,20 @@ def reference_gpu_kernels() -> dict:
             out[which] = json.loads(lines[-1][7:]) if r.returncode == 0 and lines else {"unavailable": (r.stderr or "no output")[-300:]}
         except Exception as e:      # a comparison aid: never fails the benchmark line
             out[which] = {"unavailable": repr(e)[:300]}
+    # the reference's standalone bf16 / fp8 GEMM benchmarks: their own main() times 1024^3 ... 16384^3 (5 warm-up + 10 timed launches,
+    # rotating operand groups, 500 ms idle first: the protocol this file mirrors); the 8192^3 figures are read from their output
+    import re
+    for which in ("bf16", "fp8"):
+        exe = os.path.join(ROOT, "oracle", "_ref", f"tk_{which}", f"{which}_b200_gemm.out")
+        if not os.path.exists(exe):
+            out[which] = {"unavailable": "reference standalone benchmark not built (oracle/build.py:build_ref_standalone needs the reference tree)"}
+            continue
+        try:
+            r = subprocess.run([exe], capture_output=True, text=True, timeout=240)
+            m = re.search(r"M=8192 N=8192 K=8192.*?Average kernel execution time: ([0-9.eE+-]+) us.*?Achieved performance: ([0-9.eE+-]+) TFLOPs", r.stdout, re.S)
+            out[which] = {"gemm_us": float(m.group(1)), "gemm_tflops": float(m.group(2))} if m else {"unavailable": (r.stdout + r.stderr)[-300:]}
+        except Exception as e:
+            out[which] = {"unavailable": repr(e)[:300]}
     return out
 
 
@@ -759,6 +566,31 @@ def side_measurements(torch, ops, dev) -> dict:
         tf = FLOPS / t * 1e-12
         out["nvfp4_gemm_8192"] = {"tflops": tf, "us": t * 1e6, "frac_of_4x_measured_bf16": tf / (4 * pk["bf16_tflops"]),
                                   "frac_of_nominal_9000": tf / NOMINAL["fp4"]}
+        del gs
+        torch.cuda.empty_cache()
+        # MXFP8 8192^3: bf16 ~N(0,1) with 1 % of entries x32, per-32 UE8M0 scales
+        gs = []
+        for gi in range(3):
+            A = synth(torch, dev, M, K, 3 + 10 * gi, outliers=0.01); B = synth(torch, dev, N, K, 4 + 10 * gi, outliers=0.01)
+            a = torch.empty(M, K, dtype=u8, device=dev); asc = torch.empty(M // 128, K // 128, 512, dtype=u8, device=dev)
+            b = torch.empty(N, K, dtype=u8, device=dev); bsc = torch.empty(N // 128, K // 128, 512, dtype=u8, device=dev)
+            ops.mxfp8_quantize(A, a, asc); ops.mxfp8_quantize(B, b, bsc)
+            gs.append((a, asc, b, bsc, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+            del A, B
+        f = lambda i: ops.mxfp8_gemm(*gs[i % 3])
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        tf = FLOPS / t * 1e-12
+        out["mxfp8_gemm_8192"] = {"tflops": tf, "us": t * 1e6, "frac_of_2x_measured_bf16": tf / (2 * pk["bf16_tflops"]),
+                                  "frac_of_nominal_4500": tf / NOMINAL["fp8"]}
+        # dense FP8 (e4m3) on the same codes
+        f = lambda i: ops.fp8_gemm(gs[i % 3][0], gs[i % 3][2], gs[i % 3][4])
+        for i in range(3):
+            f(i)
+        t = event_time(torch, f, 10)
+        tf = FLOPS / t * 1e-12
+        out["fp8_gemm_8192"] = {"tflops": tf, "us": t * 1e6, "frac_of_2x_measured_bf16": tf / (2 * pk["bf16_tflops"])}
         del gs
         torch.cuda.empty_cache()
         gs = [(synth(torch, dev, M, K, 41 + gi), synth(torch, dev, N, K, 51 + gi), torch.empty(M, N, dtype=torch.bfloat16, device=dev)) for gi in range(3)]
@@ -800,7 +632,7 @@ def side_measurements(torch, ops, dev) -> dict:
             Dd = torch.empty(Md, Nw, dtype=torch.bfloat16, device=dev)
             def f(i):
                 ops.nvfp4_quantize(X, xc, xs, xg, False)
-                ops.nvfp4_gemm(xc, xs, xg, *ws[i % 3], Dd)
+                ops.nvfp4_gemm(xc, xs, xg, *ws[i % 3], Dd, "skinny_prefetch")   # static weights: may be loaded under the quantizer
             for i in range(3):
                 f(i)
             t = event_time(torch, f, 20)
@@ -824,6 +656,63 @@ def side_measurements(torch, ops, dev) -> dict:
     return out
 
 
+def run_tp_timeline(args) -> None:
+    """Diagnostic for the tensor-parallel step (N > 1, torchrun): per-step CUDA-event times of a free-running loop plus the
+    GEMM kernel's own wait counters (tkb_gemm_set_profile_buffer) for the last step.  One JSON line from rank 0 and one
+    from rank world/2.  Not a benchmark line."""
+    import ctypes
+    import numpy as np
+    import torch
+    import thunderkittens_b200.ops as ops
+    from thunderkittens_b200 import _lib as L, parallel
+    D_ = Dist(torch)
+    rank, world, dev = D_.rank, D_.world, D_.dev
+    nl, rows = TP_N // world, TP_M // world
+    ce, comm = gather_settings(args, world)
+    op = parallel.AllGatherMatmulNVFP4(TP_M, TP_K, D_.local_rank, world, num_comm_sms=max(comm, 2), copy_engines=ce,
+                                       copy_streams=args.copy_streams)
+    X = synth(torch, dev, rows, TP_K, 700 + rank)
+    W = synth(torch, dev, nl, TP_K, 800 + rank, std=0.02)
+    u8 = torch.uint8
+    wc = torch.empty(nl, TP_K // 2, dtype=u8, device=dev); ws = torch.empty((nl + 127) // 128, TP_K // 64, 512, dtype=u8, device=dev)
+    wg = torch.empty(1, dtype=torch.float32, device=dev)
+    ops.nvfp4_quantize(W, wc, ws, wg, False)
+    del W
+    D = torch.empty(TP_M, nl, dtype=torch.bfloat16, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        op(X, wc, ws, wg, D)
+    D_.barrier()
+    prof = torch.zeros(160 * 8, dtype=torch.int64, device=dev)
+    setp = L.bind("tkb_gemm_set_profile_buffer", [ctypes.c_void_p])
+    steps = max(args.steps, 4)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        if i == steps - 1:
+            setp(prof.data_ptr())
+        op(X, wc, ws, wg, D)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    setp(None)
+    per = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]) * 1e3
+    pr = prof.cpu().numpy().reshape(160, 8)
+    ncomm = 0 if ce else op.num_comm_sms
+    lead = pr[ncomm::2]
+    lead = lead[lead[:, 4] > 0]
+    if len(lead) == 0:
+        lead = np.zeros((1, 8), np.int64)
+    med = lambda a: float(np.median(a))
+    out = {"rank": rank, "n_gpus": world, "gather": "copy engines" if ce else f"{ncomm} comm CTAs", "step_us_median_max": [med(per), float(per.max())],
+           "cycles_of_last_step": {"mma_total": med(lead[:, 4]), "mma_waiting_for_operands": med(lead[:, 3]), "mma_waiting_for_drain": med(lead[:, 2]),
+                                   "producer_waiting_for_remote_rows_median_max": [med(lead[:, 7]), float(lead[:, 7].max())]},
+           "device_status": L.device_status()}
+    if rank in (0, world // 2):
+        print(json.dumps(out), flush=True)
+    D_.barrier()
+    op.close()
+    D_.close()
+
+
 def run_case(args) -> None:
     """One kernel of the path, a few launches, nothing else: the command line used for ncu captures
     (python bench.py --case nvfp4_gemm --size 8192 --steps 3)."""
@@ -833,7 +722,7 @@ def run_case(args) -> None:
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     u8 = torch.uint8
-    m, n, k = args.size if args.m is None else args.m, args.size, args.size if args.k is None else args.k
+    m, n, k = args.size if args.m is None else args.m, args.size, args.size if args.k is None else args.k      # --size is N (and the default of M, K)
     A = synth(torch, dev, m, k, 1, outliers=0.01 if "mxfp8" in args.case else 0.0)
     B = synth(torch, dev, n, k, 2, std=1.0 if "mxfp8" in args.case or "bf16" in args.case else 0.02)
     D = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
@@ -878,8 +767,10 @@ def main() -> None:
     ap.add_argument("--config", default=None)
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "moe", "tp_timeline"],
-                    help="auto: N=1 MXFP8 GEMM, N>1 tensor-parallel NVFP4 GEMM; moe: the MoE layer; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
-    ap.add_argument("--comm-sms", type=int, default=0, help="CTAs of the multi-GPU kernels that move data over NVLink (0 = per-workload default)")
+                    help="auto: the tensor-parallel NVFP4 GEMM (plus the side measurements); moe: the MoE layer alone; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
+    ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 or -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
+    ap.add_argument("--copy-streams", type=int, default=3, help="streams the copy-engine gather spreads its peer copies over (1..4)")
+    ap.add_argument("--moe-comm-sms", type=int, default=0, help="CTAs of the MoE kernel that pull token rows over NVLink (0 = 32)")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -52,7 +52,11 @@ enum {
     TKB_GEMM_SINGLE_N256 = 2,  /* one-CTA 128 x 256 tiles */
     TKB_GEMM_PAIR_N128 = 3,    /* two-CTA 256 x 128 tiles */
     TKB_GEMM_SINGLE_N128 = 4,  /* one-CTA 128 x 128 tiles */
-    TKB_GEMM_SKINNY = 5        /* NVFP4, M <= 128: weight-streaming stream-K kernel (the default for such M) */
+    TKB_GEMM_SKINNY = 5,       /* NVFP4, M <= 128: weight-streaming stream-K kernel (the default for such M) */
+    TKB_GEMM_SKINNY_PREFETCH = 6 /* the same kernel for STATIC weights: the caller states that B, B_sc were complete before the
+                                  kernel that precedes this call in the stream started (weights quantized ahead of time), so
+                                  the kernel may load them while that kernel (typically the activation quantizer) still runs.
+                                  With any other config nothing is read before the preceding kernel has finished. */
 };
 
 int tkb_version(void);
@@ -61,6 +65,13 @@ const char* tkb_last_error(void);
 /* Status word written by kernels of the current device (0 = no kernel reported a problem).
  * Synchronises `stream`, returns the word through *status and clears it. */
 int tkb_device_status(void* stream, int* status);
+
+/* Upper bound, in SM clock cycles, on every device-side wait of kernels launched after the call (mbarrier waits, flag
+ * spins, grid barriers, cross-rank exchanges); 0 restores the default of 2e9 cycles, about one second.  When a wait runs
+ * out the kernel records TKB_ERR_TIMEOUT in the device status word, abandons its work and returns: outputs of that launch
+ * are undefined, the context stays usable.  The reference's waits are unbounded (include/ops/thread/util/sync.cuh:311-318).
+ * Process-wide. */
+int tkb_set_wait_limit_cycles(long long cycles);
 
 /* Diagnostics (no counterpart in the reference): when set to a device buffer of 8 x uint64 per launched CTA,
  * GEMM kernels record per-CTA wait cycles: [0] producer waiting for a free stage, [1] producer total,
@@ -122,8 +133,9 @@ int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream);
  *   ceil(rows/128) row blocks; A_sg/B_sg fp32[1]; D [M, N] bf16 with leading dimension ldd (0 = N).
  *   K % 64 == 0, N % 8 == 0; any M, N (the reference needs M,N,K % 256 == 0).
  *   M <= 128 ("decode" shapes, which the reference kernel cannot run) goes to a weight-streaming kernel that
- *   uses library-owned scratch (per-CTA fp32 partial tiles); up to 4 such calls may be in flight on
- *   different streams of one device. */
+ *   uses library-owned scratch (per-CTA fp32 partial tiles), one set per stream: up to 4 streams of one device may
+ *   use it (a fifth is refused with TKB_ERR_INVALID_ARG rather than sharing scratch with a call in flight).  A CUDA graph
+ *   captured from such a call must not be replayed on several streams at once. */
 int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
                    void* D, int64_t ldd, int M, int N, int K, void* stream);
 int tkb_nvfp4_gemm_ex(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
@@ -239,9 +251,14 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
  * piece completes its unit.  Returns the number of pieces (even if larger than max_pieces), or -code on bad arguments. */
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces);
 
-/* One call for a whole step of the column-parallel layer: two launches, tkb_nvfp4_quantize_sharded of the local rows
- * into this rank's slice, then tkb_ag_gemm_nvfp4 with the epoch hand-shake inside the kernel.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index [set][rank]);
- * the set used is epoch % 2, and epoch must grow by one per call, starting at 1, on every rank alike.
+/* One call for a whole step of the column-parallel layer: tkb_nvfp4_quantize_sharded of the local rows into this rank's
+ * slice, then the gather and the GEMM.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index
+ * [set][rank]); the set used is epoch % 2, and epoch must grow by one per call, starting at 1, on every rank alike.
+ *   comm_ctas > 0: the gather is done by that many CTAs of the GEMM kernel (tkb_ag_gemm_nvfp4, epoch hand-shake inside).
+ *   comm_ctas < 0: the gather is done by the GPU's copy engines: per peer one cudaMemcpyAsync for the codes, one for the
+ *     scales and one for the arrival flags (stream order makes the flags land last), spread over the streams of st->copy in
+ *     the order in which the peers need this rank's rows, while every SM multiplies (the GEMM kernel waits, bounded, on the
+ *     arrival flags of each 256-row block).  One peer copy per call: no batched-copy API is involved.
  * Host-side convenience over the entry points above; no counterpart in the reference. */
 typedef struct tkb_ag_state {
     int rank, world, M, K;
@@ -253,12 +270,12 @@ typedef struct tkb_ag_state {
     float* amax;            /* device scratch, 1 float */
     float* sg;              /* device, 1 float: the per-tensor scale of the gathered activations */
     void* exit_counter;     /* device, one zeroed 32-bit word */
-    /* optional, for the copy-engine gather (comm_ctas < 0 in tkb_ag_linear_nvfp4): a second stream of the same device and
-     * three events created by the caller (cudaStream_t / cudaEvent_t, timing disabled) */
-    void* copy_stream;
-    void* ev_quantized;
-    void* ev_copied[2];
+    void* copy;             /* optional: handle from tkb_ag_copy_create, needed by the copy-engine gather (comm_ctas < 0) */
 } tkb_ag_state;
+/* Streams, events and the flag pattern of the copy-engine gather, for the current device: n_streams (1..4) copy streams,
+ * stamp_count >= M / world / 64.  Store the handle in tkb_ag_state.copy; destroy it after the last call has finished. */
+int tkb_ag_copy_create(int n_streams, int stamp_count, void** handle);
+int tkb_ag_copy_destroy(void* handle);
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local_bf16, const void* W, const void* W_sc,
                         const float* W_sg, void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream);
 

@@ -106,6 +106,14 @@ def num_threads() -> int:
     return lib().tko_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the oracle and of the reference host build (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().tko_set_num_threads(int(n))
+    r = ref_host()
+    if r is not None and hasattr(r, "tkref_set_num_threads"):
+        r.tkref_set_num_threads(int(n))
+
+
 def f32_to_bf16(x: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x, np.float32)
     out = np.empty(x.shape, np.uint16)

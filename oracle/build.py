@@ -20,7 +20,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD = os.path.join(HERE, "_build")
 REF_OUT = os.path.join(HERE, "_ref")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-REFERENCE = os.environ.get("TK_REFERENCE", "/root/reference")
+# the ThunderKittens tree: $TK_REFERENCE, else a directory named `reference` beside this repository
+REFERENCE = os.environ.get("TK_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 CXXFLAGS = ["-O3", "-march=x86-64-v3", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", "-std=c++17"]
 
@@ -116,6 +117,28 @@ def build_ref_gpu(which: str = "nvfp4") -> str | None:
     cmd += ["-ltorch_python", "-ltorch_cuda", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-lc10", "-lcuda", "-lcudart_static", "-lrt",
             "-lpthread", "-ldl", src, "-o", out]
     _run(cmd)
+    return out
+
+
+def build_ref_standalone(which: str = "bf16") -> str | None:
+    """Compile one of the reference's standalone GEMM benchmarks (kernels/gemm/bf16_b200 or fp8_b200: a kernel plus a main()
+    that times it at 1024^3 ... 16384^3 and checks it against the reference's naive kernel) the way the reference's Makefile does
+    (kernels/common.mk `CONFIG := standalone`, GPU := B200), straight from the reference tree with one nvcc command.  Output:
+    oracle/_ref/tk_<which>/<which>_b200_gemm.out (git-ignored).  Used on a single-GPU box to time the reference beside this
+    library; single-GPU use only (the reference kernels issue TMA loads with cluster multicast)."""
+    srcdir = os.path.join(REFERENCE, "kernels", "gemm", f"{which}_b200")
+    src = os.path.join(srcdir, f"{which}_b200_gemm.cu")
+    outdir = os.path.join(REF_OUT, f"tk_{which}")
+    out = os.path.join(outdir, f"{which}_b200_gemm.out")
+    if not os.path.exists(src):
+        return out if os.path.exists(out) else None
+    if _newer(out, [src, __file__]):
+        return out
+    os.makedirs(outdir, exist_ok=True)
+    _run(["nvcc", src, "-std=c++20", "-O3", "--use_fast_math", "-lrt", "-lpthread", "-ldl", "-lcuda", "-lcudadevrt", "-lcudart_static",
+          "--expt-extended-lambda", "--expt-relaxed-constexpr", "-forward-unknown-to-host-compiler", "-Xcompiler=-Wno-psabi",
+          "-Xcompiler=-fno-strict-aliasing", "-I", os.path.join(REFERENCE, "include"), "-I", os.path.join(REFERENCE, "prototype"),
+          "-DNDEBUG", "-lineinfo", "-DKITTENS_BLACKWELL", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out])
     return out
 
 

@@ -8,6 +8,7 @@
 // from the (unused here) launcher wrappers so a host compiler can parse the file.  The stripped
 // intermediate lives in a temporary directory; the shared object goes to oracle/_ref/ and is never
 // committed.
+#include <omp.h>
 #define KITTENS_BLACKWELL 1
 #include "kittens.cuh"
 #include REF_COMMON_CUH   // set by the build recipe to the stripped temporary copy
@@ -78,6 +79,9 @@ void tkref_fill_uniform_f32(float* out, size_t n, uint64_t seed, float lo, float
         }
     }
 }
+
+// OpenMP threads of this library's parallel loops (launchers such as torchrun export OMP_NUM_THREADS=1)
+void tkref_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 int tkref_scale_swizzle_idx(int row, int k_block, int k_blocks) { return scale_swizzle_idx(row, k_block, k_blocks); }
 

@@ -180,6 +180,15 @@ int tko_num_threads() {
 #endif
 }
 
+// Thread count of the OpenMP runtime this library (and anything else bound to the same runtime) uses from now on.
+void tko_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // ------------------------------------------------------------------ codecs (arrays) -----
 void tko_f32_to_bf16(const float* in, uint16_t* out, size_t n) { for (size_t i = 0; i < n; i++) out[i] = f32_to_bf16(in[i]); }
 void tko_bf16_to_f32(const uint16_t* in, float* out, size_t n) { for (size_t i = 0; i < n; i++) out[i] = bf16_to_f32(in[i]); }

@@ -30,7 +30,8 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REFERENCE = os.environ.get("TK_REFERENCE", "/root/reference")
+# the ThunderKittens tree: $TK_REFERENCE, else a directory named `reference` beside this repository
+REFERENCE = os.environ.get("TK_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 
 import oracle  # noqa: E402  (only for the toolkit host codecs)
 

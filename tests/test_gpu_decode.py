@@ -86,3 +86,28 @@ def test_decode_full_size(cuda, lib, M):
     rows = min(M, 4)
     ref = O.nvfp4_gemm(*xq, *wq, row0=M - rows, nrows=rows)
     _check(D[M - rows:], ref, f"decode full M={M}")
+
+
+@pytest.mark.parametrize("config", ["skinny", "skinny_prefetch"])
+def test_decode_weights_quantized_right_before(cuda, lib, config):
+    """Weights quantized ON THE DEVICE by the launch that directly precedes the skinny GEMM in the same stream.  With the
+    default config the GEMM reads nothing before that launch has finished, so the result must be right; the prefetching
+    config is only legal when the weights were complete earlier, which the extra synchronisation below provides."""
+    ops = _ops()
+    M, N, K = 16, 4096, 8192
+    X, W = randn_bf16((M, K), seed=11), randn_bf16((N, K), seed=12, std=0.02)
+    xq, wq = O.nvfp4_quantize(bf16_bits(X), False, "spec"), O.nvfp4_quantize(bf16_bits(W), False, "spec")
+    xc, xs, xg = to_dev_u8(xq[0], cuda), to_dev_u8(xq[1], cuda), torch.from_numpy(xq[2]).to(cuda)
+    Wd = W.to(cuda)
+    wc = torch.zeros(N, K // 2, dtype=torch.uint8, device=cuda); ws = torch.zeros(N // 128, K // 64, 512, dtype=torch.uint8, device=cuda)
+    wg = torch.zeros(1, dtype=torch.float32, device=cuda)
+    D = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        wc.zero_(); ws.zero_()
+        ops.nvfp4_quantize(Wd, wc, ws, wg, False, "spec")
+        if config == "skinny_prefetch":
+            torch.cuda.synchronize()             # the contract of the prefetching config: weights complete beforehand
+        ops.nvfp4_gemm(xc, xs, xg, wc, ws, wg, D, config)
+        torch.cuda.synchronize()
+        _check(bf16_bits(D), O.nvfp4_gemm(*xq, *wq), f"decode after device-side weight quantize ({config})")

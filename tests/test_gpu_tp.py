@@ -32,15 +32,28 @@ def test_ag_gemm_world1(cuda, lib):
     op.close()
 
 
+def _run_workers(world, gather, size):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TKB_TEST_TP_CE="1" if gather == "copy_engines" else "0", TKB_TEST_TP_SIZE=size)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "mp_tp_worker.py")],
+                       capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    sys.stdout.write(r.stdout[-6000:])
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("PASS") == world
+
+
 @pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ag_gemm_multi_gpu(cuda, lib, world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TKB_TEST_TP_CE="1" if gather == "copy_engines" else "0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-                        "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "mp_tp_worker.py")],
-                       capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
-    sys.stdout.write(r.stdout[-4000:])
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    assert r.stdout.count("PASS") == world
+    _run_workers(world, gather, "small")
+
+
+@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ag_gemm_multi_gpu_benchmark_size(cuda, lib, world, gather):
+    """M = 8192, N = 28672, K = 8192 with the benchmark's gather settings: gathered operand bit-exact, D on slabs of every shard."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run_workers(world, gather, "c4")

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libtkb200.so")
 
 OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_CAPACITY = range(7)
 NVFP4_SPEC, NVFP4_KERNEL_IEEE, NVFP4_KERNEL_FAST = 0, 1, 2
-GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY = range(6)
+GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY, GEMM_SKINNY_PREFETCH = range(7)
 
 
 class TkbError(RuntimeError):
@@ -26,6 +26,7 @@ _vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 _SIGNATURES = {
     "tkb_version": ([], _i),
     "tkb_last_error": ([], C.c_char_p),
+    "tkb_set_wait_limit_cycles": ([C.c_longlong], _i),
     "tkb_device_status": ([_vp, C.POINTER(_i)], _i),
     "tkb_nvfp4_quantize": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "tkb_nvfp4_quantize_with_amax": ([_vp, _i64, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
@@ -50,6 +51,8 @@ _SIGNATURES = {
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_all_to_all_4d": ([C.POINTER(_vp), _vp, C.POINTER(C.c_longlong), _i, _i, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
+    "tkb_ag_copy_create": ([_i, _i, C.POINTER(_vp)], _i),
+    "tkb_ag_copy_destroy": ([_vp], _i),
     "tkb_ag_linear_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp,
                            C.c_uint, _i, _vp], _i),
@@ -73,7 +76,7 @@ class AgState(C.Structure):
     _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("K", _i),
                 ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
                 ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp),
-                ("copy_stream", _vp), ("ev_quantized", _vp), ("ev_copied", _vp * 2)]
+                ("copy", _vp)]
 
 
 class MoeState(C.Structure):

@@ -22,23 +22,16 @@ int api_fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
-static int fail(int code, const char* fmt, ...) {
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(g_err, sizeof(g_err), fmt, ap);
-    va_end(ap);
-    return code;
-}
 #define TKB_CUDA(expr)                                                                                   \
     do {                                                                                                 \
         cudaError_t _e = (expr);                                                                         \
-        if (_e != cudaSuccess) return fail(TKB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+        if (_e != cudaSuccess) return api_fail(TKB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
     } while (0)
 
 // ------------------------------------------------------------------ per-device context -----
 constexpr int kMaxDevices = 64;
 constexpr int kQuantSlots = 256;
-constexpr int kDecodeRing = 4;
+constexpr int kDecodeRing = 4;                           // streams of one device that may use the skinny-M GEMM
 constexpr int kSmallScratchRing = 4;
 constexpr size_t kSmallScratchBytes = 2u << 20;
 constexpr int kDecodeMaxGrid = 160;                      // CTAs the scratch is sized for
@@ -56,7 +49,11 @@ struct DeviceCtx {
     std::atomic<unsigned> small_scratch_calls{0};
     float* decode_partials = nullptr;
     unsigned int* decode_flags = nullptr;
-    std::atomic<unsigned> decode_calls{0};
+    // one scratch set per stream that has used the kernel: calls on one stream are ordered by the stream, calls on different
+    // streams never share a set
+    cudaStream_t decode_stream[kDecodeRing] = {};
+    bool decode_stream_used[kDecodeRing] = {};
+    unsigned decode_calls[kDecodeRing] = {};
 };
 static DeviceCtx g_ctx[kMaxDevices];
 static std::mutex g_ctx_mu;
@@ -66,18 +63,21 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
 static unsigned long long* g_prof = nullptr;   // tkb_gemm_set_profile_buffer
+constexpr long long kDefaultWaitLimit = 2000000000ll;      // about one second at B200 clocks
+static std::atomic<long long> g_wait_limit{kDefaultWaitLimit};
+long long api_wait_limit() { return g_wait_limit.load(std::memory_order_relaxed); }
 
 static int get_ctx(DeviceCtx** out) {
     int dev = 0;
     TKB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return fail(TKB_ERR_INVALID_ARG, "device ordinal %d out of range", dev);
+    if (dev < 0 || dev >= kMaxDevices) return api_fail(TKB_ERR_INVALID_ARG, "device ordinal %d out of range", dev);
     DeviceCtx& c = g_ctx[dev];
     if (!c.ready) {
         std::lock_guard<std::mutex> lk(g_ctx_mu);
         if (!c.ready) {
             cudaDeviceProp prop;
             TKB_CUDA(cudaGetDeviceProperties(&prop, dev));
-            if (prop.major != 10) return fail(TKB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+            if (prop.major != 10) return api_fail(TKB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
             c.sm_count = prop.multiProcessorCount;
             c.cc_major = prop.major;
             TKB_CUDA(cudaMalloc(&c.status, sizeof(int)));
@@ -88,7 +88,7 @@ static int get_ctx(DeviceCtx** out) {
                 void* fn = nullptr;
                 cudaDriverEntryPointQueryResult q;
                 TKB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-                if (!fn || q != cudaDriverEntryPointSuccess) return fail(TKB_ERR_UNSUPPORTED, "driver does not export cuTensorMapEncodeTiled");
+                if (!fn || q != cudaDriverEntryPointSuccess) return api_fail(TKB_ERR_UNSUPPORTED, "driver does not export cuTensorMapEncodeTiled");
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
             TKB_CUDA(cudaDeviceSynchronize());
@@ -111,7 +111,7 @@ static int make_operand_map(CUtensorMap* m, const void* base, CUtensorMapDataTyp
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed with CUresult %d", int(r));
+    if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed with CUresult %d", int(r));
     return TKB_OK;
 }
 // 3-D scale map over [row_blocks][k_chunks][128 x int32] (512-byte chunks), box = chunks_per_stage chunks.
@@ -123,7 +123,7 @@ static int make_scale_map(CUtensorMap* m, const void* base, uint64_t row_blocks,
     CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(scales) failed with CUresult %d", int(r));
+    if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(scales) failed with CUresult %d", int(r));
     return TKB_OK;
 }
 
@@ -143,7 +143,7 @@ static int ensure_decode_scratch(DeviceCtx* c) {
 
 // Skinny-M NVFP4 GEMM (M <= 128): X is the activation (A operand of the public call), W the weight.
 static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const float* X_sg, const void* W, const void* W_sc,
-                         const float* W_sg, void* D, int64_t ldd, int M, int N, int K, void* stream) {
+                         const float* W_sg, void* D, int64_t ldd, int M, int N, int K, int prefetch_weights, void* stream) {
     if (int e = ensure_decode_scratch(c)) return e;
     DecodeArgs d;
     memset(&d, 0, sizeof(d));
@@ -152,14 +152,27 @@ static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const fl
     if (int e = make_operand_map(&d.tmX, X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(K / 2), M, K / 2, nb)) return e;
     if (int e = make_scale_map(&d.tmSW, W_sc, (N + 127) / 128, K / 64, 4)) return e;
     if (int e = make_scale_map(&d.tmSX, X_sc, 1, K / 64, 4)) return e;
-    const unsigned call = c->decode_calls.fetch_add(1);
-    const unsigned ring = call % kDecodeRing;
+    unsigned call = 0;
+    int ring = -1;
+    {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        const cudaStream_t key = static_cast<cudaStream_t>(stream);
+        for (int i = 0; i < kDecodeRing && ring < 0; i++)
+            if (c->decode_stream_used[i] && c->decode_stream[i] == key) ring = i;
+        for (int i = 0; i < kDecodeRing && ring < 0; i++)
+            if (!c->decode_stream_used[i]) { c->decode_stream_used[i] = true; c->decode_stream[i] = key; ring = i; }
+        if (ring >= 0) call = c->decode_calls[ring]++;
+    }
+    if (ring < 0)
+        return api_fail(TKB_ERR_INVALID_ARG, "gemm (M <= 128): this device already runs the skinny-M kernel on %d other streams, which is as many scratch "
+                                         "sets as the library keeps; use one of those streams", kDecodeRing);
     d.sgX = X_sg; d.sgW = W_sg; d.D = D; d.ldd = ldd; d.M = M; d.N = N; d.K = K;
     d.partials = c->decode_partials + ring * kDecodePartialFloats;
     d.flags = c->decode_flags + ring * kDecodeMaxGrid;
-    d.epoch = call / kDecodeRing + 1;           // strictly increasing per scratch set, never 0
+    d.epoch = call + 1;                         // strictly increasing per scratch set, never 0
     d.max_grid = kDecodeMaxGrid;
-    d.status = c->status; d.sm_count = c->sm_count; d.stream = static_cast<cudaStream_t>(stream);
+    d.status = c->status; d.sm_count = c->sm_count; d.stream = static_cast<cudaStream_t>(stream); d.prof = g_prof;
+    d.prefetch_weights = prefetch_weights;
     TKB_CUDA(launch_decode(d));
     return TKB_OK;
 }
@@ -198,7 +211,7 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
         cuuint32_t estr[2] = {1, 1};
         CUresult r = g_encode(&g.tmD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
+        if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
     }
     return TKB_OK;
 }
@@ -237,28 +250,28 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
                        int64_t ldb_bytes, const void* B_sc, const float* B_sg, void* D, int64_t ldd, int M, int N, int K, int config,
                        void* stream) {
     // pure argument errors first: they are reported the same way with or without a device
-    if (!A || !B || !D) return fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
-    if (M < 1 || N < 1 || K < 1) return fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
-    if (config < 0 || config > TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
-    if (config == TKB_GEMM_SKINNY && (kind != KIND_NVFP4 || M > 128))
-        return fail(TKB_ERR_INVALID_ARG, "gemm: the skinny-M kernel needs NVFP4 operands and M <= 128");
+    if (!A || !B || !D) return api_fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
+    if (M < 1 || N < 1 || K < 1) return api_fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+    if (config < 0 || config > TKB_GEMM_SKINNY_PREFETCH) return api_fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
+    if ((config == TKB_GEMM_SKINNY || config == TKB_GEMM_SKINNY_PREFETCH) && (kind != KIND_NVFP4 || M > 128))
+        return api_fail(TKB_ERR_INVALID_ARG, "gemm: the skinny-M kernel needs NVFP4 operands and M <= 128");
     const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : (kind == KIND_FP8 ? 16 : 8));
-    if (K % kmult) return fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
-    if (N % 8) return fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
+    if (K % kmult) return api_fail(TKB_ERR_INVALID_ARG, "gemm: K=%d must be a multiple of %d for this format", K, kmult);
+    if (N % 8) return api_fail(TKB_ERR_INVALID_ARG, "gemm: N=%d must be a multiple of 8", N);
     if (ldd == 0) ldd = N;
-    if (ldd < N || ldd % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
+    if (ldd < N || ldd % 8) return api_fail(TKB_ERR_BAD_ALIGNMENT, "gemm: ldd=%lld must be >= N and a multiple of 8 elements", (long long)ldd);
     if (!aligned16(A) || !aligned16(B) || !aligned16(D) || lda_bytes % 16 || ldb_bytes % 16)
-        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
+        return api_fail(TKB_ERR_BAD_ALIGNMENT, "gemm: operand base pointers and row pitches must be 16-byte aligned");
     if (kind == KIND_NVFP4 || kind == KIND_MXFP8) {
-        if (!A_sc || !B_sc) return fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
-        if (!aligned16(A_sc) || !aligned16(B_sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
+        if (!A_sc || !B_sc) return api_fail(TKB_ERR_INVALID_ARG, "gemm: null scale pointer");
+        if (!aligned16(A_sc) || !aligned16(B_sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "gemm: scale tensors must be 16-byte aligned");
     }
-    if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
+    if (kind == KIND_NVFP4 && (!A_sg || !B_sg)) return api_fail(TKB_ERR_INVALID_ARG, "gemm: null per-tensor scale pointer");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
 
-    if (kind == KIND_NVFP4 && M <= 128 && (config == TKB_GEMM_DEFAULT || config == TKB_GEMM_SKINNY))
-        return decode_common(c, A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, stream);
+    if (kind == KIND_NVFP4 && M <= 128 && (config == TKB_GEMM_DEFAULT || config == TKB_GEMM_SKINNY || config == TKB_GEMM_SKINNY_PREFETCH))
+        return decode_common(c, A, A_sc, A_sg, B, B_sc, B_sg, D, ldd, M, N, K, config == TKB_GEMM_SKINNY_PREFETCH ? 1 : 0, stream);
 
     GemmArgs g;
     memset(&g, 0, sizeof(g));
@@ -275,13 +288,13 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
                                  int scale_2d, int arithmetic, void* stream, int sc_rowmajor = 0, const QuantExchange* xch = nullptr) {
     // sc_rowmajor: codes and scales share one row of K/2 + K/16 bytes (codes first); `sc` is ignored
     if (sc_rowmajor) sc = static_cast<uint8_t*>(codes) + K / 2;
-    if (!A || !codes || !sc || !sg) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
-    if (M < 1 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: need M >= 1 and K a positive multiple of 64 (got M=%d K=%d)", M, K);
-    if (arithmetic < 0 || arithmetic > 2) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: unknown arithmetic %d", arithmetic);
+    if (!A || !codes || !sc || !sg) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: null pointer");
+    if (M < 1 || K < 64 || K % 64) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: need M >= 1 and K a positive multiple of 64 (got M=%d K=%d)", M, K);
+    if (arithmetic < 0 || arithmetic > 2) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: unknown arithmetic %d", arithmetic);
     if (lda == 0) lda = K;
-    if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: lda must be >= K and a multiple of 8 elements");
-    if (!aligned16(A) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: buffers must be 16-byte aligned");
-    if (xch && amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: the cross-rank amax exchange belongs to the fused-amax kernel (no amax input)");
+    if (lda < K || lda % 8) return api_fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: lda must be >= K and a multiple of 8 elements");
+    if (!aligned16(A) || !aligned16(codes) || !aligned16(sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "nvfp4_quantize: buffers must be 16-byte aligned");
+    if (xch && amax && xch->world > 1) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize: the cross-rank amax exchange belongs to the fused-amax kernel (no amax input)");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
     NvQuantArgs a;
@@ -289,10 +302,27 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     a.ws = c->quant_ws + (c->next_slot.fetch_add(1) % kQuantSlots);
     a.M = M; a.K = K; a.scale_2d = scale_2d ? 1 : 0; a.status = c->status;
     a.stream = static_cast<cudaStream_t>(stream); a.sm_count = c->sm_count; a.sc_rowmajor = sc_rowmajor;
+    a.spin_limit = api_wait_limit();
     memset(&a.xch, 0, sizeof(a.xch));
     if (xch) a.xch = *xch;
     TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
     return TKB_OK;
+}
+
+// tkb_nvfp4_quantize_sharded plus an optional stamp: `stamp_count` device words that the kernel fills with `epoch`.
+int api_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
+                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count, void* stream) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: world must be 1..8 and 0 <= rank < world");
+    if (layout != 0 && layout != 1) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: layout must be 0 (operand) or 1 (self-contained rows)");
+    if (world > 1 && (!peer_slots || epoch == 0)) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot table or epoch 0");
+    QuantExchange x;
+    memset(&x, 0, sizeof(x));
+    x.world = world; x.rank = rank; x.epoch = epoch; x.stamp = stamp; x.stamp_count = stamp ? stamp_count : 0;
+    for (int i = 0; i < world && world > 1; i++) {
+        if (!peer_slots[i]) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot array for rank %d", i);
+        x.slots[i] = static_cast<unsigned long long*>(peer_slots[i]);
+    }
+    return nvfp4_quantize_common(A_bf16, lda, codes, layout ? nullptr : sc, sg, nullptr, M, K, 0, arithmetic, stream, layout, (world > 1 || stamp) ? &x : nullptr);
 }
 
 } // namespace tkb
@@ -309,10 +339,16 @@ int tkb_gemm_set_profile_buffer(void* device_u64) {
     return TKB_OK;
 }
 
+int tkb_set_wait_limit_cycles(long long cycles) {
+    if (cycles < 0) return api_fail(TKB_ERR_INVALID_ARG, "set_wait_limit_cycles: negative limit");
+    g_wait_limit.store(cycles == 0 ? kDefaultWaitLimit : cycles, std::memory_order_relaxed);
+    return TKB_OK;
+}
+
 int tkb_device_status(void* stream, int* status) {
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
-    if (!status) return fail(TKB_ERR_INVALID_ARG, "device_status: null output");
+    if (!status) return api_fail(TKB_ERR_INVALID_ARG, "device_status: null output");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     TKB_CUDA(cudaStreamSynchronize(s));
     TKB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
@@ -327,36 +363,26 @@ int tkb_nvfp4_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, f
 
 int tkb_nvfp4_quantize_with_amax(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, const float* amax, int M, int K,
                                  int scale_2d, int arithmetic, void* stream) {
-    if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_with_amax: null amax");
+    if (!amax) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_with_amax: null amax");
     return nvfp4_quantize_common(A_bf16, lda, codes, sc, sg, amax, M, K, scale_2d, arithmetic, stream);
 }
 
 int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* sg, const float* amax, int M, int K, int arithmetic,
                             void* stream) {
-    if (!amax) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_rows: null amax");
+    if (!amax) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_rows: null amax");
     return nvfp4_quantize_common(A_bf16, lda, rows, nullptr, sg, amax, M, K, 0, arithmetic, stream, 1);
 }
 
 int tkb_nvfp4_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
                                void* const* peer_slots, int world, int rank, unsigned int epoch, void* stream) {
-    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: world must be 1..8 and 0 <= rank < world");
-    if (layout != 0 && layout != 1) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: layout must be 0 (operand) or 1 (self-contained rows)");
-    if (world > 1 && (!peer_slots || epoch == 0)) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot table or epoch 0");
-    QuantExchange x;
-    memset(&x, 0, sizeof(x));
-    x.world = world; x.rank = rank; x.epoch = epoch;
-    for (int i = 0; i < world && world > 1; i++) {
-        if (!peer_slots[i]) return fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot array for rank %d", i);
-        x.slots[i] = static_cast<unsigned long long*>(peer_slots[i]);
-    }
-    return nvfp4_quantize_common(A_bf16, lda, codes, layout ? nullptr : sc, sg, nullptr, M, K, 0, arithmetic, stream, layout, world > 1 ? &x : nullptr);
+    return api_quantize_sharded(A_bf16, lda, codes, sc, sg, M, K, layout, arithmetic, peer_slots, world, rank, epoch, nullptr, 0, stream);
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {
-    if (!A_bf16 || !amax) return fail(TKB_ERR_INVALID_ARG, "absmax: null pointer");
-    if (M < 1 || K < 8 || K % 8) return fail(TKB_ERR_INVALID_ARG, "absmax: need M >= 1 and K a positive multiple of 8");
+    if (!A_bf16 || !amax) return api_fail(TKB_ERR_INVALID_ARG, "absmax: null pointer");
+    if (M < 1 || K < 8 || K % 8) return api_fail(TKB_ERR_INVALID_ARG, "absmax: need M >= 1 and K a positive multiple of 8");
     if (lda == 0) lda = K;
-    if (lda < K || lda % 8 || !aligned16(A_bf16)) return fail(TKB_ERR_BAD_ALIGNMENT, "absmax: A must be 16-byte aligned with lda %% 8 == 0");
+    if (lda < K || lda % 8 || !aligned16(A_bf16)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "absmax: A must be 16-byte aligned with lda %% 8 == 0");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -366,11 +392,11 @@ int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, 
 }
 
 int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, int M, int K, void* stream) {
-    if (!A_bf16 || !codes || !sc) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: null pointer");
-    if (M < 1 || K < 128 || K % 128) return fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: need M >= 1 and K a positive multiple of 128 (got M=%d K=%d)", M, K);
+    if (!A_bf16 || !codes || !sc) return api_fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: null pointer");
+    if (M < 1 || K < 128 || K % 128) return api_fail(TKB_ERR_INVALID_ARG, "mxfp8_quantize: need M >= 1 and K a positive multiple of 128 (got M=%d K=%d)", M, K);
     if (lda == 0) lda = K;
-    if (lda < K || lda % 8) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: lda must be >= K and a multiple of 8 elements");
-    if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
+    if (lda < K || lda % 8) return api_fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: lda must be >= K and a multiple of 8 elements");
+    if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
     TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
@@ -378,8 +404,8 @@ int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, i
 }
 
 int tkb_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, void* stream) {
-    if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp32_to_fp4x2: null pointer");
-    if (reinterpret_cast<uintptr_t>(in) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp32_to_fp4x2: input must be 8-byte aligned");
+    if (!in || !out) return api_fail(TKB_ERR_INVALID_ARG, "fp32_to_fp4x2: null pointer");
+    if (reinterpret_cast<uintptr_t>(in) & 7u) return api_fail(TKB_ERR_BAD_ALIGNMENT, "fp32_to_fp4x2: input must be 8-byte aligned");
     if (n_pairs == 0) return TKB_OK;
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
@@ -387,8 +413,8 @@ int tkb_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, void* stream) 
     return TKB_OK;
 }
 int tkb_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, void* stream) {
-    if (!in || !out) return fail(TKB_ERR_INVALID_ARG, "fp4x2_to_fp32: null pointer");
-    if (reinterpret_cast<uintptr_t>(out) & 7u) return fail(TKB_ERR_BAD_ALIGNMENT, "fp4x2_to_fp32: output must be 8-byte aligned");
+    if (!in || !out) return api_fail(TKB_ERR_INVALID_ARG, "fp4x2_to_fp32: null pointer");
+    if (reinterpret_cast<uintptr_t>(out) & 7u) return api_fail(TKB_ERR_BAD_ALIGNMENT, "fp4x2_to_fp32: output must be 8-byte aligned");
     if (n_pairs == 0) return TKB_OK;
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
@@ -406,12 +432,12 @@ int tkb_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const voi
 }
 int tkb_nvfp4_gemm_quant(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc, const float* B_sg,
                          const float* out_amax, void* D_codes, void* D_sc, float* D_sg, int M, int N, int K, int arithmetic, void* stream) {
-    if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !out_amax || !D_codes || !D_sc || !D_sg) return fail(TKB_ERR_INVALID_ARG, "gemm_quant: null pointer");
-    if (M < 1 || N < 64 || N % 64 || K < 64 || K % 64) return fail(TKB_ERR_INVALID_ARG, "gemm_quant: need M >= 1, N %% 64 == 0, K %% 64 == 0 (got %d, %d, %d)", M, N, K);
+    if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !out_amax || !D_codes || !D_sc || !D_sg) return api_fail(TKB_ERR_INVALID_ARG, "gemm_quant: null pointer");
+    if (M < 1 || N < 64 || N % 64 || K < 64 || K % 64) return api_fail(TKB_ERR_INVALID_ARG, "gemm_quant: need M >= 1, N %% 64 == 0, K %% 64 == 0 (got %d, %d, %d)", M, N, K);
     if (arithmetic != TKB_NVFP4_SPEC && arithmetic != TKB_NVFP4_KERNEL_IEEE)
-        return fail(TKB_ERR_INVALID_ARG, "gemm_quant: the fused epilogue offers the two IEEE arithmetics only");
+        return api_fail(TKB_ERR_INVALID_ARG, "gemm_quant: the fused epilogue offers the two IEEE arithmetics only");
     if (!aligned16(A) || !aligned16(B) || !aligned16(A_sc) || !aligned16(B_sc) || !aligned16(D_codes) || !aligned16(D_sc))
-        return fail(TKB_ERR_BAD_ALIGNMENT, "gemm_quant: buffers must be 16-byte aligned");
+        return api_fail(TKB_ERR_BAD_ALIGNMENT, "gemm_quant: buffers must be 16-byte aligned");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
     GemmArgs g;
@@ -438,7 +464,7 @@ int tkb_bf16_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, voi
                      void* stream) {
     if (lda == 0) lda = K;
     if (ldb == 0) ldb = K;
-    if (lda < K || ldb < K) return fail(TKB_ERR_INVALID_ARG, "bf16_gemm: lda/ldb must be >= K");
+    if (lda < K || ldb < K) return api_fail(TKB_ERR_INVALID_ARG, "bf16_gemm: lda/ldb must be >= K");
     return gemm_common(KIND_BF16, A, lda * 2, nullptr, nullptr, B, ldb * 2, nullptr, nullptr, D, ldd, M, N, K, config, stream);
 }
 int tkb_bf16_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {
@@ -448,8 +474,8 @@ int tkb_fp8_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void
                     void* stream) {
     if (lda == 0) lda = K;
     if (ldb == 0) ldb = K;
-    if (lda < K || ldb < K) return fail(TKB_ERR_INVALID_ARG, "fp8_gemm: lda/ldb must be >= K");
-    if (config == TKB_GEMM_SKINNY) return fail(TKB_ERR_INVALID_ARG, "fp8_gemm: no skinny-M kernel for this format");
+    if (lda < K || ldb < K) return api_fail(TKB_ERR_INVALID_ARG, "fp8_gemm: lda/ldb must be >= K");
+    if (config >= TKB_GEMM_SKINNY) return api_fail(TKB_ERR_INVALID_ARG, "fp8_gemm: no skinny-M kernel for this format");
     return gemm_common(KIND_FP8, A, lda, nullptr, nullptr, B, ldb, nullptr, nullptr, D, ldd, M, N, K, config, stream);
 }
 int tkb_fp8_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {

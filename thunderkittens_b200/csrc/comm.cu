@@ -11,6 +11,7 @@
 //     and read with bounded acquire spins; nothing uses multicast or multimem.
 #include <cstddef>
 #include <cstring>
+#include <new>
 #include "../../include/tkb200.h"
 #include "internal.h"
 #include "ptx.cuh"
@@ -21,11 +22,14 @@ namespace tkb {
 int api_fail(int code, const char* fmt, ...);          // api.cu
 int api_device(int* sm_count, int** status);
 unsigned long long* api_profile_buffer();             // api.cu: tkb_gemm_set_profile_buffer           // api.cu
+int api_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
+                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count, void* stream);   // api.cu
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
 
 struct PeerPtrs { unsigned int* p[kMaxWorld]; };
 constexpr int kAllToAll4dMaxGrid = 592;   // CTAs of tkb_all_to_all_4d at most (part of its counter protocol)
+constexpr int kAgMaxCopyStreams = 4;
 constexpr int kAllToAllParts = 4;      // CTAs per destination in tkb_all_to_all (part of its counter protocol)
 
 __global__ void signal_peers_kernel(PeerPtrs peers, int world, int rank, int index, unsigned int value, int include_self) {
@@ -37,7 +41,7 @@ __global__ void signal_peers_kernel(PeerPtrs peers, int world, int rank, int ind
 }
 
 // Waits until every flags[i] (i != skip) has reached `value` (epochs only grow).
-__global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip, unsigned int value, int* status) {
+__global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip, unsigned int value, int* status, long long limit) {
     const int t = threadIdx.x;
     if (t < count && t != skip) {
         const long long t0 = clock64();
@@ -45,7 +49,7 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + t) : "memory");
             if (int(v - value) >= 0) break;
-            if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT);
                 break;
             }
@@ -54,19 +58,11 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int count, int skip
     }
 }
 
-// Stores `value` into count consecutive 32-bit flags (copy-engine gather: the arrival epochs of one rank's rows on one peer,
-// launched in the copy stream right after the copies they announce).
-__global__ void set_flags_kernel(unsigned int* flags, int count, unsigned int value) {
-    __threadfence_system();
-    for (int t = threadIdx.x; t < count; t += blockDim.x)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags + t), "r"(value) : "memory");
-}
-
 // Max all-reduce of one float across the ranks without a library collective: every rank stores (epoch, value
 // bits) into slot[rank] of every peer's slot array and then waits (bounded) until all of its own slots carry the
 // epoch.  About one NVLink round trip instead of a collective launch.
 struct PeerSlots { unsigned long long* p[kMaxWorld]; };
-__global__ void amax_allreduce_kernel(PeerSlots slots, int world, int rank, unsigned int epoch, const float* local, float* out, int* status) {
+__global__ void amax_allreduce_kernel(PeerSlots slots, int world, int rank, unsigned int epoch, const float* local, float* out, int* status, long long limit) {
     const int t = threadIdx.x;
     float v = 0.f;
     if (t < world) {
@@ -77,7 +73,7 @@ __global__ void amax_allreduce_kernel(PeerSlots slots, int world, int rank, unsi
         while (true) {
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(slots.p[rank] + t) : "memory");
             if (int(unsigned(got >> 32) - epoch) >= 0) break;
-            if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
+            if (clock64() - t0 > limit) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
         }
         v = __uint_as_float(unsigned(got & 0xffffffffu));
     }
@@ -140,7 +136,7 @@ __global__ void __launch_bounds__(256) all_to_all_4d_kernel(const unsigned char*
     }
 }
 // All ranks have entered: one add per peer, then a bounded wait for everybody's.
-__global__ void a2a_enter_kernel(PeerPtrs counters, int base, int rank, int world, unsigned int epoch, int* status) {
+__global__ void a2a_enter_kernel(PeerPtrs counters, int base, int rank, int world, unsigned int epoch, int* status, long long limit) {
     const int t = threadIdx.x;
     if (t < world) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(counters.p[t] + base + rank), "r"(1u) : "memory");
     if (t < world) {
@@ -149,7 +145,7 @@ __global__ void a2a_enter_kernel(PeerPtrs counters, int base, int rank, int worl
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counters.p[rank] + base + t) : "memory");
             if (int(v - epoch) >= 0) break;
-            if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
+            if (clock64() - t0 > limit) { if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
             __nanosleep(100);
         }
     }
@@ -213,7 +209,7 @@ int tkb_wait_flags(const void* flags, int count, int skip, unsigned int value, v
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
     wait_flags_kernel<<<1, ((count + 31) / 32) * 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned int*>(flags), count, skip,
-                                                                                         value, status);
+                                                                                         value, status, api_wait_limit());
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }
@@ -225,7 +221,7 @@ int tkb_amax_allreduce(void* const* peer_slots, int world, int rank, unsigned in
     if (int e = api_device(&sm, &status)) return e;
     PeerSlots ps;
     for (int i = 0; i < kMaxWorld; i++) ps.p[i] = i < world ? static_cast<unsigned long long*>(peer_slots[i]) : nullptr;
-    amax_allreduce_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps, world, rank, epoch, local, out, status);
+    amax_allreduce_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps, world, rank, epoch, local, out, status, api_wait_limit());
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }
@@ -249,7 +245,7 @@ int tkb_all_to_all(void* const* peer_out, const void* in, size_t bytes_per_peer,
                                                               counter_base);
     TKB_CUDA_C(cudaGetLastError());
     // every sender adds `parts` to its counter per call: wait until all of them have reached epoch * parts
-    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base, world, -1, epoch * unsigned(parts), status);
+    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base, world, -1, epoch * unsigned(parts), status, api_wait_limit());
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }
@@ -287,13 +283,13 @@ int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* di
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // counters [base, base + world): "rank r has entered call `epoch`" (nobody writes into a peer that may still be reading
     // its output of the previous call); [base + world, base + 2 * world): CTAs of rank r that are through
-    a2a_enter_kernel<<<1, 32, 0, s>>>(pc, counter_base, rank, world, epoch, status);
+    a2a_enter_kernel<<<1, 32, 0, s>>>(pc, counter_base, rank, world, epoch, status, api_wait_limit());
     TKB_CUDA_C(cudaGetLastError());
     const long long total = p.in_dims[0] * p.in_dims[1] * p.in_dims[2] * p.in_dims[3];
     const int grid = int(total / 2048 < 1 ? 1 : (total / 2048 > kAllToAll4dMaxGrid ? kAllToAll4dMaxGrid : total / 2048));   // the same on every rank
     all_to_all_4d_kernel<<<grid, 256, 0, s>>>(static_cast<const unsigned char*>(in), p);
     TKB_CUDA_C(cudaGetLastError());
-    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base + world, world, -1, epoch * unsigned(grid), status);
+    wait_flags_kernel<<<1, 32, 0, s>>>(static_cast<const unsigned int*>(peer_counters[rank]) + counter_base + world, world, -1, epoch * unsigned(grid), status, api_wait_limit());
     TKB_CUDA_C(cudaGetLastError());
     return TKB_OK;
 }
@@ -350,7 +346,7 @@ int tkb_debug_struct_layout(int which, int field) {
             TKB_OFF(tkb_ag_state, rank) TKB_OFF(tkb_ag_state, world) TKB_OFF(tkb_ag_state, M) TKB_OFF(tkb_ag_state, K)
             TKB_OFF(tkb_ag_state, codes) TKB_OFF(tkb_ag_state, scales) TKB_OFF(tkb_ag_state, arrived) TKB_OFF(tkb_ag_state, slots)
             TKB_OFF(tkb_ag_state, done) TKB_OFF(tkb_ag_state, amax) TKB_OFF(tkb_ag_state, sg) TKB_OFF(tkb_ag_state, exit_counter)
-            TKB_OFF(tkb_ag_state, copy_stream) TKB_OFF(tkb_ag_state, ev_quantized) TKB_OFF(tkb_ag_state, ev_copied)
+            TKB_OFF(tkb_ag_state, copy)
             default: return -1;
         }
     }
@@ -392,6 +388,53 @@ int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int 
     return n;
 }
 
+// Streams, events and the arrival-flag pattern of the copy-engine gather (tkb_ag_copy_create).
+struct AgCopyCtx {
+    int n_streams, stamp_count, device;
+    cudaStream_t stream[kAgMaxCopyStreams];
+    cudaEvent_t quantized;                        // recorded in the caller's stream after the quantize launch
+    cudaEvent_t copied[2][kAgMaxCopyStreams];     // per buffer set: this rank's slice has been read by all copies of the call
+    unsigned int* stamp[2];                       // per buffer set: stamp_count words holding the epoch of the call
+};
+
+int tkb_ag_copy_create(int n_streams, int stamp_count, void** handle) {
+    if (!handle || n_streams < 1 || n_streams > kAgMaxCopyStreams || stamp_count < 1)
+        return api_fail(TKB_ERR_INVALID_ARG, "ag_copy_create: need 1..%d streams, stamp_count >= 1 and an output pointer", kAgMaxCopyStreams);
+    AgCopyCtx* c = new (std::nothrow) AgCopyCtx();
+    if (!c) return api_fail(TKB_ERR_CUDA, "ag_copy_create: out of host memory");
+    memset(c, 0, sizeof(*c));
+    c->n_streams = n_streams; c->stamp_count = stamp_count;
+    cudaError_t e = cudaGetDevice(&c->device);
+    for (int i = 0; i < n_streams && e == cudaSuccess; i++) e = cudaStreamCreateWithFlags(&c->stream[i], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->quantized, cudaEventDisableTiming);
+    for (int b = 0; b < 2 && e == cudaSuccess; b++) {
+        for (int i = 0; i < n_streams && e == cudaSuccess; i++) e = cudaEventCreateWithFlags(&c->copied[b][i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaMalloc(&c->stamp[b], size_t(stamp_count) * sizeof(unsigned int));
+        if (e == cudaSuccess) e = cudaMemset(c->stamp[b], 0, size_t(stamp_count) * sizeof(unsigned int));
+    }
+    if (e != cudaSuccess) {
+        tkb_ag_copy_destroy(c);
+        return api_fail(TKB_ERR_CUDA, "ag_copy_create: %s", cudaGetErrorString(e));
+    }
+    *handle = c;
+    return TKB_OK;
+}
+
+int tkb_ag_copy_destroy(void* handle) {
+    AgCopyCtx* c = static_cast<AgCopyCtx*>(handle);
+    if (!c) return TKB_OK;
+    for (int i = 0; i < kAgMaxCopyStreams; i++)
+        if (c->stream[i]) { cudaStreamSynchronize(c->stream[i]); cudaStreamDestroy(c->stream[i]); }
+    if (c->quantized) cudaEventDestroy(c->quantized);
+    for (int b = 0; b < 2; b++) {
+        for (int i = 0; i < kAgMaxCopyStreams; i++)
+            if (c->copied[b][i]) cudaEventDestroy(c->copied[b][i]);
+        if (c->stamp[b]) cudaFree(c->stamp[b]);
+    }
+    delete c;
+    return TKB_OK;
+}
+
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local, const void* W, const void* W_sc, const float* W_sg,
                         void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream) {
     if (!st || !X_local || epoch == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: null state/input or epoch 0");
@@ -401,39 +444,50 @@ int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* 
     if (!st->exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: null exit counter");
     uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
     uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
-    // This rank's slice of its own buffers is only read by its own kernels (earlier in this stream); what the peers
-    // read are the copies pushed to them, and those wait for the peers' epoch - 2 kernels.
     cudaStream_t main = static_cast<cudaStream_t>(stream);
-    const bool ce = w > 1 && comm_ctas < 0;          // gather by copy engines on st->copy_stream instead of comm CTAs
-    if (ce) {
-        if (!st->copy_stream || !st->ev_quantized || !st->ev_copied[0] || !st->ev_copied[1])
-            return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs copy_stream, ev_quantized and ev_copied[2] in the state");
-        // the copies of epoch - 2 read the slice that is about to be overwritten
-        if (epoch > 2) TKB_CUDA_C(cudaStreamWaitEvent(main, static_cast<cudaEvent_t>(st->ev_copied[b]), 0));
+    const bool ce = w > 1 && comm_ctas < 0;          // gather by copy engines instead of comm CTAs
+    if (!ce) {
+        // This rank's slice of its own buffers is only read by its own kernels (earlier in this stream); what the peers
+        // read are the copies the comm CTAs push, and those wait for the peers' epoch - 2 kernels themselves.
+        if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, stream))
+            return e;
+        return tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
+                                 st->done, st->exit_counter, epoch, w > 1 ? comm_ctas : 0, stream);
     }
-    if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, stream))
+    // ---- copy-engine gather.  Ordering argument: the amax exchange inside the quantize kernel is a barrier over the ranks
+    // for this epoch, and a rank only reaches it after its GEMM of the previous call (same stream).  So once this rank's
+    // quantize kernel has finished, no peer still reads the buffer set of epoch - 2, which is the one written now; no
+    // separate acknowledgement is needed.  The copy streams carry copies only (no kernels), so they never compete with the
+    // persistent GEMM kernel for an SM.
+    AgCopyCtx* c = static_cast<AgCopyCtx*>(st->copy);
+    const int flags_per_rank = rows / 64;
+    if (!c || c->stamp_count < flags_per_rank)
+        return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs st->copy from tkb_ag_copy_create(n, >= M / world / 64)");
+    // the copies of epoch - 2 read the slice and the flag pattern that are about to be overwritten
+    if (epoch > 2)
+        for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(main, c->copied[b][i], 0));
+    if (int e = api_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, c->stamp[b],
+                                     flags_per_rank, stream))
         return e;
-    if (ce) {
-        cudaStream_t cs = static_cast<cudaStream_t>(st->copy_stream);
-        TKB_CUDA_C(cudaEventRecord(static_cast<cudaEvent_t>(st->ev_quantized), main));
-        TKB_CUDA_C(cudaStreamWaitEvent(cs, static_cast<cudaEvent_t>(st->ev_quantized), 0));
-        // every peer's kernel of epoch - 2 (the last reader of this buffer set) must be finished before it is written
-        if (epoch > 2)
-            if (int e = tkb_wait_flags(st->done[r], w, r, epoch - 2, st->copy_stream)) return e;
-        const size_t code_bytes = size_t(rows) * (st->K / 2), code_off = size_t(r) * code_bytes;
-        const size_t sc_bytes = size_t(rows / 128) * (st->K / 64) * 512, sc_off = size_t(r) * sc_bytes;
-        const int flags_per_rank = rows / 64;
-        for (int i = 1; i < w; i++) {
-            const int d = (r + w - i) % w;           // in the order in which the peers consume this rank's rows
-            TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->codes[b][d]) + code_off, my_codes, code_bytes, cudaMemcpyDeviceToDevice, cs));
-            TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->scales[b][d]) + sc_off, my_scales, sc_bytes, cudaMemcpyDeviceToDevice, cs));
-            set_flags_kernel<<<1, 64, 0, cs>>>(static_cast<unsigned int*>(st->arrived[b][d]) + size_t(r) * flags_per_rank, flags_per_rank, epoch);
-            TKB_CUDA_C(cudaGetLastError());
-        }
-        TKB_CUDA_C(cudaEventRecord(static_cast<cudaEvent_t>(st->ev_copied[b]), cs));
+    TKB_CUDA_C(cudaEventRecord(c->quantized, main));
+    // the GEMM goes into the queue first: it starts with this rank's own rows while the host is still issuing the copies
+    if (int e = tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
+                                  nullptr, nullptr, epoch, 0, stream))
+        return e;
+    const size_t code_bytes = size_t(rows) * (st->K / 2), code_off = size_t(r) * code_bytes;
+    const size_t sc_bytes = size_t(rows / 128) * (st->K / 64) * 512, sc_off = size_t(r) * sc_bytes;
+    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(c->stream[i], c->quantized, 0));
+    for (int i = 1; i < w; i++) {
+        const int d = (r + w - i) % w;           // in the order in which the peers consume this rank's rows
+        cudaStream_t cs = c->stream[(i - 1) % c->n_streams];
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->codes[b][d]) + code_off, my_codes, code_bytes, cudaMemcpyDeviceToDevice, cs));
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->scales[b][d]) + sc_off, my_scales, sc_bytes, cudaMemcpyDeviceToDevice, cs));
+        // stream order: the flags leave after the rows they announce have been written
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<unsigned int*>(st->arrived[b][d]) + size_t(r) * flags_per_rank, c->stamp[b],
+                                   size_t(flags_per_rank) * sizeof(unsigned int), cudaMemcpyDeviceToDevice, cs));
     }
-    return tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
-                             st->done, st->exit_counter, epoch, (w > 1 && !ce) ? comm_ctas : 0, stream);
+    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaEventRecord(c->copied[b][i], c->stream[i]));
+    return TKB_OK;
 }
 
 } // extern "C"

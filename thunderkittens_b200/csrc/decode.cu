@@ -17,6 +17,7 @@
 //     tensor memory so the epilogue of one segment overlaps the main loop of the next.
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include "ptx.cuh"
 #include "internal.h"
@@ -50,7 +51,16 @@ struct DecodeParams {
     unsigned int* flags;        // [grid]
     unsigned int epoch;
     int* status;
+    unsigned long long* prof;   // optional (tkb_gemm_set_profile_buffer): 8 words per CTA, see decode_kernel
+    long long wait_limit;       // clock cycles any wait of the kernel may last
+    int prefetch_weights;       // the weights were complete before the previous kernel in the stream started: load them before the dependency wait
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -112,6 +122,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     __shared__ int s_flag_ok;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // profile words of this CTA (global nanosecond timer): [0] CTA start, [1] producer past the dependency wait, [2] first
+    // stage landed, [3] last MMA issued, [4] epilogue finished, [5] ns the epilogue waited for other CTAs' partial tiles,
+    // [6] ns the MMA thread waited for operands, [7] SM id
+    unsigned long long* prof = p.prof ? p.prof + size_t(blockIdx.x) * 8 : nullptr;
+    if (prof && threadIdx.x == 0) {
+        prof[0] = global_ns();
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        prof[7] = smid;
+    }
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sW = smem_base;
     const uint32_t sX = sW + C::STAGES * C::W_BYTES;
@@ -136,7 +156,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-    WaitCtx wc{&s_abort, p.status};
+    WaitCtx wc{&s_abort, p.status, p.wait_limit};
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
@@ -144,11 +164,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            // The weights do not depend on the kernel that runs before this one in the stream (the activation
-            // quantizer): fill the ring with weight tiles first, only then wait for that kernel and add the
-            // activation tiles of the same stages.
+            // With prefetch_weights the caller states that the weights do not depend on the kernel that runs before
+            // this one in the stream (typically the activation quantizer): fill the ring with weight tiles first, only
+            // then wait for that kernel and add the activation tiles of the same stages.  Without it nothing is read
+            // before the wait.
             int prefetched = 0;
-            {
+            if (p.prefetch_weights) {
                 WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
                 Segment sg;
                 while (prefetched < C::STAGES && wr.next(sg))
@@ -160,6 +181,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     }
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (prof) prof[1] = global_ns();
             WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
             Segment sg;
             int item = 0;
@@ -181,6 +203,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
+            if (!ok) drain_ring(bar_full, C::STAGES, uint32_t(item > prefetched ? item : prefetched), p.wait_limit);   // giving up: let the issued copies land
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -188,7 +211,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (elect_one()) {
             uint32_t stage = 0, phase = 0, slot = 0;
             int seg_idx = 0;
-            bool ok = true;
+            bool ok = true, first = true;
+            unsigned long long waited = 0;
             WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
             Segment sg;
             while (ok && wr.next(sg)) {
@@ -197,7 +221,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 tc_fence_after();
                 const uint32_t acc_t = tmem_base + buf * C::ACC_STRIDE;
                 for (int kb = sg.kb0; kb < sg.kb1; kb++) {
-                    if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                    if (prof) {
+                        const unsigned long long t0 = global_ns();
+                        if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
+                        const unsigned long long t1 = global_ns();
+                        waited += t1 - t0;
+                        if (first) { prof[2] = t1; first = false; }
+                    } else if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sfa_t = tmem_base + C::SF_BASE + slot * 32;
                     const uint32_t sfb_t = sfa_t + 16;
@@ -219,6 +249,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 tc_commit<1>(smem_u32(&bar_acc_full[buf]));
                 seg_idx++;
             }
+            if (prof) { prof[3] = global_ns(); prof[6] = waited; }
         }
         __syncwarp();
     } else {
@@ -249,10 +280,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 // wait for their partial tiles
                 if (threadIdx.x == 64) {
                     int good = 1;
+                    const unsigned long long tw0 = prof ? global_ns() : 0ull;
                     for (int h = contrib_lo; h < contrib_hi && good; h++) {
                         const long long t0 = clock64();
                         while (ld_acquire_gpu(p.flags + h) != p.epoch) {
-                            if (s_abort || clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+                            if (s_abort || clock64() - t0 > p.wait_limit) {
                                 good = 0; s_abort = 1;
                                 if (p.status) atomicExch(p.status, (int)TKB_DEV_TIMEOUT);
                                 break;
@@ -261,6 +293,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         }
                     }
                     s_flag_ok = good;
+                    if (prof) prof[5] += global_ns() - tw0;
                 }
                 epi_barrier();
                 if (!s_flag_ok) ok = false;
@@ -323,6 +356,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
             seg_idx++;
         }
+        if (prof && threadIdx.x == 64) prof[4] = global_ns();
         __syncwarp();
     }
 
@@ -339,20 +373,20 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     using C = DecodeCfg<NB>;
     auto kern = decode_kernel<NB>;
     // the attribute belongs to the (kernel, device) pair: remember it per device, not per process
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     const long long items = (long long)((a.N + 127) / 128) * ((a.K + 255) / 256);
     int grid = a.sm_count;
     if (grid > a.max_grid) grid = a.max_grid;
     if (grid > items) grid = int(items);
     if (grid < 1) grid = 1;
-    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status};
+    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights};
     CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
     void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
     (void)params;
@@ -410,7 +444,7 @@ int api_fail(int code, const char* fmt, ...);     // api.cu: records the calling
 
 namespace {
 constexpr int kStaticMaxDevices = 64;
-struct StaticDev { bool ready; unsigned char* scratch; int sm_count; };
+struct StaticDev { std::atomic<bool> ready; unsigned char* scratch; int sm_count; };
 StaticDev g_static_dev[kStaticMaxDevices];
 std::mutex g_static_mu;
 
@@ -454,11 +488,11 @@ extern "C" int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, con
     if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: cudaGetDevice failed: %s", cudaGetErrorString(ce));
     if (dev < 0 || dev >= kStaticMaxDevices) return api_fail(1, "gemm_skinny_static: device ordinal %d out of range", dev);
     StaticDev& sd = g_static_dev[dev];
-    if (!sd.ready) {
+    if (!sd.ready.load(std::memory_order_acquire)) {
         // First call on this device (it is the current device): resolve the device address of the scratch
         // array.  The array's name is only a host-side handle for the symbol, never a pointer a kernel can use.
         std::lock_guard<std::mutex> lk(g_static_mu);
-        if (!sd.ready) {
+        if (!sd.ready.load(std::memory_order_relaxed)) {
             void* p = nullptr;
             ce = cudaGetSymbolAddress(&p, g_static_scratch);
             if (ce != cudaSuccess || !p) return api_fail(3, "gemm_skinny_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(ce));
@@ -476,7 +510,7 @@ extern "C" int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, con
             }
             sd.scratch = static_cast<unsigned char*>(p);
             sd.sm_count = sms;
-            sd.ready = true;
+            sd.ready.store(true, std::memory_order_release);       // publishes scratch and sm_count
         }
     }
     DecodeArgs a;
@@ -493,6 +527,7 @@ extern "C" int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, con
     a.sgX = X_sg; a.sgW = W_sg; a.D = D; a.ldd = ldd; a.M = M; a.N = N; a.K = K;
     a.partials = reinterpret_cast<float*>(sd.scratch); a.flags = flags; a.epoch = 1; a.max_grid = kStaticMaxGrid;
     a.status = nullptr; a.sm_count = sd.sm_count; a.stream = s;
+    a.prefetch_weights = 0;
     ce = launch_decode(a);
     if (ce != cudaSuccess) return api_fail(3, "gemm_skinny_static: launch failed: %s", cudaGetErrorString(ce));
     return 0;

@@ -26,6 +26,7 @@
 //     past M / N are clipped by the TMA unit.
 //   * Every mbarrier wait is bounded (ptx.cuh); on a timeout the kernel records the status, leaves
 //     its loops, joins the final cluster barrier, frees TMEM and returns.
+#include <atomic>
 #include <cstdlib>
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
@@ -73,6 +74,7 @@ struct GemmParams {
     int group;                  // row blocks that share a sweep over the columns
     int* status;
     unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
+    long long wait_limit;       // clock cycles any wait of the kernel may last
     // quantizing epilogue (MODE_QUANT): the bf16 result is quantized to NVFP4 before it leaves the SM
     uint8_t* q_codes; uint8_t* q_sc; float* q_sg; const float* q_amax; int q_arith;
 };
@@ -137,7 +139,7 @@ __device__ __forceinline__ bool flag_wait(const WaitCtx& w, const unsigned int* 
     const long long t0 = clock64();
     while (int(ld_acquire_sys(flag) - value) < 0) {
         if (*w.abort_flag) return false;
-        if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > w.limit) {
             *w.abort_flag = 1;
             if (w.status) atomicExch(w.status, (int)TKB_DEV_TIMEOUT);
             return false;
@@ -311,7 +313,9 @@ __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc
                 }
                 issued += BATCH; next += BATCH;
             }
-            for (int i = 0; i < BATCH; i++) mbar_wait(wc, smem_u32(&bars[(done + i) % ring]), ((done + i) / ring) & 1);
+            bool landed = true;
+            for (int i = 0; i < BATCH && landed; i++) landed = mbar_wait(wc, smem_u32(&bars[(done + i) % ring]), ((done + i) / ring) & 1);
+            if (!landed) break;          // every thread waits on the same barriers and sees the same abort flag: a uniform exit
             if (tid < BATCH) {
                 // one lane per row forwards the codes; its previous store (one batch ago) has long been read
                 const int r = r0 + tid;
@@ -407,7 +411,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if constexpr (CTAS == 2) cluster_sync(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-    WaitCtx wc{&s_abort, p.status};
+    WaitCtx wc{&s_abort, p.status, p.wait_limit};
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // successors launched with programmatic serialization wait on their own
 
     if constexpr (MOE || AG) {
@@ -438,7 +442,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer ----------
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             long long waited = 0, waited_flags = 0;
             asm volatile("griddepcontrol.wait;" ::: "memory");      // operands may come from the previous kernel in the stream
@@ -495,6 +499,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                             b_sblk + j);
                         }
                     }
+                    issued++;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -503,6 +508,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int s = 0; s < C::STAGES && ok; s++) {
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) {
+                // giving up: the copies already issued must land before this CTA (pair) may exit.  Both CTAs' bytes are
+                // credited to the leader's barriers; the other CTA just leaves the copies time and then meets the leader
+                // at the teardown barrier.
+                if (is_leader) drain_ring(bar_full, C::STAGES, issued, p.wait_limit);
+                else __nanosleep(50000);
             }
         }
         __syncwarp();
@@ -685,13 +697,13 @@ static cudaError_t launch_t(const GemmArgs& a) {
     using C = GemmCfg<KIND, CTAS, BN>;
     auto kern = gemm_kernel<KIND, CTAS, BN, MODE>;
     // the attribute belongs to the (kernel, device) pair: remember it per device, not per process
-    static bool attr_set[64] = {};
+    static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     const int tiles = ((a.M + C::BM - 1) / C::BM) * ((a.N + BN - 1) / BN);
     const int comm_units = MODE == MODE_AG ? a.comm.ag.comm_ctas / CTAS : (MODE == MODE_MOE ? a.comm.moe.comm_ctas / CTAS : 0);
@@ -713,7 +725,7 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
     static const int group_env = getenv("TKB_GEMM_GROUP") ? atoi(getenv("TKB_GEMM_GROUP")) : 0;
-    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof,
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof, api_wait_limit(),
                  static_cast<uint8_t*>(a.q_codes), static_cast<uint8_t*>(a.q_sc), a.q_sg, a.q_amax, a.q_arith};
     return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
@@ -726,6 +738,15 @@ static cudaError_t launch_k(const GemmArgs& a) {
         case 2: return launch_t<KIND, 2, 128>(a);
         default: return launch_t<KIND, 1, 128>(a);
     }
+}
+
+// Row slots of the MoE dispatch ring for hidden size K (the arithmetic of moe_pull on the shared memory of its kernel instance)
+int moe_dispatch_ring(int K) {
+    using C = GemmCfg<KIND_NVFP4, 1, 256>;
+    const long avail = long(C::STAGES) * C::STAGE_BYTES + C::EPI_BYTES;
+    const long ring0 = 128L * (K / 16) + (((K / 2) + 127) & ~127);
+    const long ring = (avail - ring0) / (K / 2 + K / 16);
+    return int(ring < 0 ? 0 : (ring > 32 ? 32 : ring));
 }
 
 int gemm_tile_n(int config) { return (config & 2) ? 128 : 256; }

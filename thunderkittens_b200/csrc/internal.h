@@ -19,6 +19,9 @@ cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64
 cudaError_t launch_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, cudaStream_t s);
 cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cudaStream_t s);
 
+// api.cu: clock cycles a device-side wait may last (tkb_set_wait_limit_cycles)
+long long api_wait_limit();
+
 // gemm.cu
 constexpr int kMaxWorld = 8;
 struct AgParams {
@@ -65,6 +68,7 @@ struct GemmArgs {
     void* q_codes; void* q_sc; float* q_sg; const float* q_amax; int q_arith;   // q_arith: 0 = spec association, 1 = kernel association (IEEE)
 };
 cudaError_t launch_gemm(const GemmArgs& a);
+int moe_dispatch_ring(int K);     // row slots the MoE dispatch ring gets for hidden size K (needs >= 24)
 int gemm_tile_n(int config);
 int gemm_tile_m(int config);
 
@@ -76,6 +80,8 @@ struct DecodeArgs {
     int M, N, K;
     float* partials; unsigned int* flags; unsigned int epoch; int max_grid;
     int* status; int sm_count; cudaStream_t stream;
+    unsigned long long* prof;   // optional per-CTA timeline, 8 x uint64 per CTA
+    int prefetch_weights;       // TKB_GEMM_SKINNY_PREFETCH
 };
 cudaError_t launch_decode(const DecodeArgs& a);
 int decode_padded_rows(int M);

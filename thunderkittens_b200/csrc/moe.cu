@@ -386,9 +386,12 @@ int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: need K %% 256 == 0, I %% 128 == 0, cap_rows %% 128 == 0");
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
-    // dispatch staging per comm CTA: a block's scales (128 x K/16 bytes), a zero row and at least 12 row slots; one thread per 64 K-elements
-    if (128 * (K / 16) + K / 2 + 128 + 12 * (K / 2 + K / 16) > 190 * 1024 || K / 64 + 1 > 320)
-        return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d too large for the dispatch staging", K);
+    // dispatch staging per comm CTA: a block's scales (128 x K/16 bytes), a zero row and a ring of row slots of which 16 trail the
+    // loads (two batches whose stores may still read them), so at least 24 are needed to keep a batch of 8 loads in flight;
+    // one thread per 64 K-elements
+    if (moe_dispatch_ring(K) < 24 || K / 64 + 1 > 320)
+        return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d is too large for the dispatch staging in shared memory (%d row slots, 24 needed)",
+                        K, moe_dispatch_ring(K));
     if (comm_ctas < 1 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [1, %d]", sm / 2);
     if (ldy == 0) ldy = I;
     GemmArgs g;

@@ -2,9 +2,10 @@
 // allocation, MMA, commit, cp, ld) and cluster helpers.  Everything here is a single instruction or
 // a bounded wait; no tile abstractions.
 //
-// Every wait in this library is bounded: tkb::mbar_wait gives up after TKB_WAIT_LIMIT_CYCLES
-// clock cycles, records TKB_DEV_TIMEOUT in the launch's status word, raises the CTA's abort flag
-// and returns false; callers leave their loops when that happens.
+// Every wait in this library is bounded: tkb::mbar_wait gives up after WaitCtx::limit clock cycles
+// (a launch parameter: 2e9 cycles, about a second, unless tkb_set_wait_limit_cycles changed it), records
+// TKB_DEV_TIMEOUT in the launch's status word, raises the CTA's abort flag and returns false; callers
+// leave their loops when that happens.
 #pragma once
 #include <cstdint>
 #include <cuda.h>
@@ -12,10 +13,6 @@
 #include <cuda_bf16.h>
 
 namespace tkb {
-
-#ifndef TKB_WAIT_LIMIT_CYCLES
-#define TKB_WAIT_LIMIT_CYCLES (2000000000ll)   // about one second at B200 clocks
-#endif
 
 enum DevStatus : int { TKB_DEV_OK = 0, TKB_DEV_TIMEOUT = 4 };
 
@@ -104,6 +101,7 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parit
 struct WaitCtx {
     volatile int* abort_flag;   // in shared memory; non-zero once any wait of this CTA gave up
     int* status;                // in global memory; receives TKB_DEV_TIMEOUT
+    long long limit;            // clock cycles a wait may last
 };
 
 // Bounded wait.  Returns false if the limit ran out or the CTA was already aborting.
@@ -113,11 +111,24 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32
     while (true) {
         if (mbar_try_wait_sleep(bar, parity, 100000u)) return true;      // parked for up to 100 us per attempt
         if (*w.abort_flag) return false;
-        if (clock64() - t0 > TKB_WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > w.limit) {
             *w.abort_flag = 1;
             if (w.status) atomicExch(w.status, (int)TKB_DEV_TIMEOUT);
             return false;
         }
+    }
+}
+
+// Abort path only: waits, bounded and without touching the abort state, until the copies of the last phase that was
+// issued into each stage of an operand ring have landed, so that a CTA that gives up does not exit under its own
+// in-flight bulk copies.  `issued` = stages filled so far by the calling producer thread (round-robin from stage 0).
+__device__ __forceinline__ void drain_ring(uint64_t* bar_full, int stages, uint32_t issued, long long limit) {
+    const long long t0 = clock64();
+    for (int s = 0; s < stages; s++) {
+        const uint32_t n = (issued + uint32_t(stages) - 1u - uint32_t(s)) / uint32_t(stages);      // phases issued into stage s
+        if (n == 0) continue;
+        while (!mbar_try_wait_sleep(smem_u32(&bar_full[s]), (n - 1u) & 1u, 20000u))
+            if (clock64() - t0 > limit) return;
     }
 }
 

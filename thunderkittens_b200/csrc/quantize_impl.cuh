@@ -28,9 +28,6 @@ namespace tkb {
 
 
 constexpr int QT_ROWS = 128, QT_COLS = 128, Q_THREADS = 256;
-#ifndef TKB_SPIN_LIMIT_CYCLES
-#define TKB_SPIN_LIMIT_CYCLES (2000000000ll)
-#endif
 
 __device__ __forceinline__ uint32_t habs2_max(uint32_t a, uint32_t b) {
     __nv_bfloat162 x = __habs2(*reinterpret_cast<__nv_bfloat162*>(&a));
@@ -75,7 +72,7 @@ __device__ __forceinline__ void load_tile(const __nv_bfloat16* A, int64_t lda, i
 // ranks over NVLink (one posted 64-bit store per peer, then bounded polls of its own slots) before it
 // releases the grid, so a row-sharded tensor is quantized with the amax of the whole tensor in one launch.
 constexpr unsigned int kAmaxFailed = 0xffffffffu;      // never a maximum of bf16 magnitudes (NaNs are dropped)
-__device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status, const QuantExchange& xch) {
+__device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status, const QuantExchange& xch, long long spin_limit) {
     __shared__ float s_amax;
     __shared__ float s_warp[Q_THREADS / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -106,7 +103,7 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
                 while (true) {
                     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(xch.slots[xch.rank] + pr) : "memory");
                     if (int(unsigned(got >> 32) - xch.epoch) >= 0) break;
-                    if (clock64() - t0 > TKB_SPIN_LIMIT_CYCLES) { got_all = false; break; }
+                    if (clock64() - t0 > spin_limit) { got_all = false; break; }
                 }
                 if (got_all) g = fmaxf(g, __uint_as_float(unsigned(got & 0xffffffffu)));
             }
@@ -116,7 +113,7 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
         }
         bool ok = true;
         while (*reinterpret_cast<volatile unsigned int*>(&ws->arrived) < target) {
-            if (clock64() - t0 > 2 * TKB_SPIN_LIMIT_CYCLES) { ok = false; break; }
+            if (clock64() - t0 > 2 * spin_limit) { ok = false; break; }
         }
         __threadfence();
         const unsigned int bits = *reinterpret_cast<volatile unsigned int*>(&ws->amax_bits);
@@ -153,7 +150,7 @@ template <class Arith, bool SCALE_2D, bool FUSED_AMAX, bool RESIDENT>
 __global__ void __launch_bounds__(Q_THREADS)
 nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, float* __restrict__ sg, const float* __restrict__ amax_in, QuantWork* ws,
-                      int M, int K, int* status, int sc_rowmajor, int64_t ldsc, const QuantExchange xch) {
+                      int M, int K, int* status, int sc_rowmajor, int64_t ldsc, const QuantExchange xch, long long spin_limit) {
     __shared__ __align__(16) uint8_t s_sc[2][2][512];   // [double buffer][chunk][byte]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
@@ -164,6 +161,8 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     // launched with programmatic stream serialization: everything above overlapped the previous kernel's tail
     pdl_wait();
     pdl_launch_dependents();
+    if (xch.stamp != nullptr && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < xch.stamp_count; i += Q_THREADS) xch.stamp[i] = xch.epoch;
     float amax;
     uint4 v[8];
     if constexpr (FUSED_AMAX) {
@@ -187,7 +186,7 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
                 for (int i = 0; i < 8; i++) local = fmaxf(local, fmaxf(amax8(v[i]), amax8(v2[i])));
             }
         }
-        amax = grid_amax_barrier(ws, local, status, xch);
+        amax = grid_amax_barrier(ws, local, status, xch, spin_limit);
         if (amax < 0.f) {
             if (threadIdx.x == 0) grid_amax_depart(ws);      // keep the slot usable for later calls
             return;
@@ -296,6 +295,7 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     int sc_rowmajor = a.sc_rowmajor;
     int64_t ldsc = a.ldsc;
     const QuantExchange xch = a.xch;
+    long long spin_limit = a.spin_limit;
     // Programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream drains;
     // it executes griddepcontrol.wait before touching global memory.
     cudaLaunchConfig_t cfg = {};
@@ -304,7 +304,7 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor, ldsc, xch);
+    return cudaLaunchKernelEx(&cfg, kern, A, lda, codes, ldc, sc, sg, amax_in, ws, M, K, status, sc_rowmajor, ldsc, xch, spin_limit);
 }
 
 // One tile per CTA with the whole grid resident (needed by the grid barrier)?

@@ -18,11 +18,15 @@ struct QuantExchange {
     unsigned long long* slots[8];
     int world, rank;
     unsigned int epoch;
+    // optional: `stamp_count` words that block 0 fills with `epoch` (the arrival-flag pattern that copy engines
+    // forward to the peers after the rows of this call, see tkb_ag_linear_nvfp4)
+    unsigned int* stamp; int stamp_count;
 };
 
 struct NvQuantArgs {
     const void* A; int64_t lda; void* codes; int64_t ldc; void* sc; float* sg; const float* amax_in; QuantWork* ws;
     int M, K, scale_2d; int* status; cudaStream_t stream; int sm_count;
+    long long spin_limit;   // clock cycles the grid barrier / cross-rank exchange may wait
     int sc_rowmajor;   // 0: 512-byte chunk layout (GEMM operand); 1: plain scale rows of K/16 bytes, ldsc bytes apart
     int64_t ldsc;
     QuantExchange xch;

@@ -109,7 +109,7 @@ class AllGatherMatmulNVFP4:
     """
 
     def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None,
-                 copy_engines: bool = False):
+                 copy_engines: bool = False, copy_streams: int = 3):
         self.arithmetic = arithmetic      # NVFP4 quantizer arithmetic (None = ops.default_nvfp4_arithmetic)
         if M % (256 * local_world_size):
             raise RuntimeError("M must be a multiple of 256 * world size")
@@ -142,14 +142,13 @@ class AllGatherMatmulNVFP4:
             st.done[i] = self.flags.peer_ptr(i)
         st.amax, st.sg, st.exit_counter = self.amax.data_ptr(), self.sg.data_ptr(), self.exit_counter.data_ptr()
         self.copy_engines = bool(copy_engines) and local_world_size > 1
+        self._copy = None
         if self.copy_engines:
-            # the gather travels by peer copies on a second stream; the library needs the raw stream and three events
-            self._copy_stream = torch.cuda.Stream()
-            self._events = [torch.cuda.Event() for _ in range(3)]
-            for ev in self._events:
-                ev.record()                         # creates the underlying CUDA event
-            st.copy_stream = self._copy_stream.cuda_stream
-            st.ev_quantized, st.ev_copied[0], st.ev_copied[1] = (ev.cuda_event for ev in self._events)
+            # the gather travels by peer copies on streams that the library owns
+            h = C.c_void_p()
+            L.check(L.lib().tkb_ag_copy_create(min(copy_streams, 4), max(1, self.rows // 64), C.byref(h)))
+            self._copy = h.value
+            st.copy = h.value
         self._state = st
         if local_world_size > 1:
             dist.barrier(group=group)
@@ -194,6 +193,10 @@ class AllGatherMatmulNVFP4:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))      # my kernel of epoch e is done
 
     def close(self) -> None:
+        torch.cuda.synchronize()
+        if self._copy is not None:
+            L.lib().tkb_ag_copy_destroy(self._copy)
+            self._copy = None
         for t in self.codes + self.scales + self.arrived + self.slots + [self.flags]:
             t.close()
 
