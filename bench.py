@@ -46,7 +46,7 @@ CPU_SLAB_ROWS = 4
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel at N = 1 (the NVFP4 GEMM, M=8192 N=28672
 # K=8192), from an ncu capture of `python bench.py --case nvfp4_gemm --m 8192 --size 28672 --k 8192`; None = not captured.
-TP_GEMM_DRAM_BYTES = None
+TP_GEMM_DRAM_BYTES = 735267584     # 302.7 MB read + 432.6 MB written (profiles/nvfp4_tp_gemm_ncu.md)
 
 
 def measured_peaks() -> dict:
