@@ -258,7 +258,9 @@ int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int 
  *   comm_ctas < 0: the gather is done by the GPU's copy engines: per peer one cudaMemcpyAsync for the codes, one for the
  *     scales and one for the arrival flags (stream order makes the flags land last), spread over the streams of st->copy in
  *     the order in which the peers need this rank's rows, while every SM multiplies (the GEMM kernel waits, bounded, on the
- *     arrival flags of each 256-row block).  One peer copy per call: no batched-copy API is involved.
+ *     arrival flags of each 256-row block).  One peer copy per call: no batched-copy API is involved.  In this mode the
+ *     kernels take the epoch from st->epoch_counter on the device (the host's `epoch` only selects the buffer set), which
+ *     is what allows tkb_ag_graph_create to record steps once and replay them.
  * Host-side convenience over the entry points above; no counterpart in the reference. */
 typedef struct tkb_ag_state {
     int rank, world, M, K;
@@ -271,6 +273,7 @@ typedef struct tkb_ag_state {
     float* sg;              /* device, 1 float: the per-tensor scale of the gathered activations */
     void* exit_counter;     /* device, one zeroed 32-bit word */
     void* copy;             /* optional: handle from tkb_ag_copy_create, needed by the copy-engine gather (comm_ctas < 0) */
+    void* epoch_counter;    /* copy-engine gather: device, one zeroed 32-bit word; the kernels keep the count of completed steps in it */
 } tkb_ag_state;
 /* Streams, events and the flag pattern of the copy-engine gather, for the current device: n_streams (1..4) copy streams,
  * stamp_count >= M / world / 64.  Store the handle in tkb_ag_state.copy; destroy it after the last call has finished. */
@@ -278,6 +281,18 @@ int tkb_ag_copy_create(int n_streams, int stamp_count, void** handle);
 int tkb_ag_copy_destroy(void* handle);
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local_bf16, const void* W, const void* W_sc,
                         const float* W_sg, void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream);
+
+/* `steps` consecutive tkb_ag_linear_nvfp4 calls (copy-engine gather) recorded as ONE CUDA graph: step i reads X_local[i],
+ * W[i], W_sc[i], W_sg[i] and writes D[i] (the arrays may repeat pointers), its epoch is first_epoch + i.  steps is even, so
+ * that a replay always starts on the same buffer set; launch the graph only when the next epoch of the state has the parity
+ * of first_epoch, and count `steps` epochs per launch.  Replaying takes one cudaGraphLaunch on the host instead of about
+ * thirty driver calls per step, which matters when a step lasts ~100 us.  Every rank creates and launches its graph alike.
+ * The quantize launches inside a graph keep the scratch slots they were recorded with.  No counterpart in the reference
+ * (its kernels take per-call host arguments). */
+int tkb_ag_graph_create(const tkb_ag_state* st, unsigned int first_epoch, int steps, const void* const* X_local_bf16, const void* const* W,
+                        const void* const* W_sc, const float* const* W_sg, void* const* D, int64_t ldd, int N_local, int arithmetic, void** handle);
+int tkb_ag_graph_launch(void* handle, void* stream);
+int tkb_ag_graph_destroy(void* handle);
 
 /* ---- MoE layer -----------------------------------------------------------------------------------
  * Replaces moe_dispatch_gemm(pre_tokens, post_tokens, weights, outputs, padded_tokens_per_expert,

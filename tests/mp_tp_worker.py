@@ -80,6 +80,32 @@ def main():
         print(f"rank {rank} iter {it} [{size}, {'copy engines' if ce else 'comm CTAs'}]: status={st} rel_fro={err:.2e} max_ulp={ulp} "
               f"gathered_codes_bit_exact={codes_ok} scales={scales_ok} all_written={nan_free}", flush=True)
         ok = ok and good
+    if ce:
+        # the same step recorded as a CUDA graph of two calls and replayed twice (device-side epochs, both buffer sets)
+        Xs = [normal_bf16(rng, (M, K), 0.5 + j) for j in range(2)]
+        Xl = [x[rank * rows:(rank + 1) * rows].to(dev) for x in Xs]
+        Ds = [torch.full((M, n_local), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        graph = op.capture([(Xl[j], Wd, Wsc, Wsg, Ds[j]) for j in range(2)])
+        for rep in range(2):
+            for d_ in Ds:
+                d_.fill_(float("nan"))
+            op.replay(graph)
+            torch.cuda.synchronize()
+            st = _lib.device_status()
+            good = st == 0
+            for j in range(2):
+                xq = O.nvfp4_quantize(bf16_bits(Xs[j]), False, "spec")
+                if edge == 0:
+                    err, ulp = check_rows(bf16_bits(Ds[j]), O.nvfp4_gemm(*xq, *wq))
+                else:
+                    err, ulp = 0.0, 0
+                    for s_ in range(world):
+                        r0 = s_ * rows + (rows - edge if (s_ + j) % 2 else 0)
+                        e1, u1 = check_rows(bf16_bits(Ds[j][r0:r0 + edge]), O.nvfp4_gemm(*xq, *wq, row0=r0, nrows=edge))
+                        err, ulp = max(err, e1), max(ulp, u1)
+                good = good and err <= 1e-3 and ulp <= 2 and not bool(torch.isnan(Ds[j]).any().item())
+            print(f"rank {rank} graph replay {rep} [{size}]: status={st} ok={good}", flush=True)
+            ok = ok and good
     dist.barrier()
     op.close()
     dist.destroy_process_group()

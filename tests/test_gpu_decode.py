@@ -111,3 +111,25 @@ def test_decode_weights_quantized_right_before(cuda, lib, config):
         ops.nvfp4_gemm(xc, xs, xg, wc, ws, wg, D, config)
         torch.cuda.synchronize()
         _check(bf16_bits(D), O.nvfp4_gemm(*xq, *wq), f"decode after device-side weight quantize ({config})")
+
+
+@pytest.mark.parametrize("M", [1, 16, 33, 128])
+def test_decode_dynamic_phase(cuda, lib, M):
+    """N = 8192, K = 8192: large enough for the second, dynamically scheduled phase of the kernel (the last fifth of the
+    weight slabs, handed out in K-parts through a counter and added up by whichever CTA finishes a slab).  Run three
+    times: the counters must come back to zero by themselves, and the result must be the same bit for bit every time
+    (the parts are always added in the same order)."""
+    N, K = 8192, 8192
+    wq = _weights(N, K, seed=77)
+    X = randn_bf16((M, K), seed=78 + M)
+    xq = O.nvfp4_quantize(bf16_bits(X), False, "spec")
+    rows = min(M, 3)
+    ref = O.nvfp4_gemm(*xq, *wq, row0=M - rows, nrows=rows)
+    first = None
+    for _ in range(3):
+        D = _run(cuda, X, wq)
+        _check(D[M - rows:], ref, f"decode dynamic M={M}")
+        assert not np.isnan(O.bf16_to_f32(D)).any()
+        if first is None:
+            first = D
+        assert np.array_equal(first, D)

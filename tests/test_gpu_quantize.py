@@ -179,3 +179,28 @@ def test_argument_errors(cuda, lib):
     with pytest.raises(RuntimeError):
         ops.mxfp8_quantize(torch.zeros(128, 128, dtype=torch.float32, device=cuda), torch.zeros(128, 128, dtype=torch.uint8, device=cuda),
                            torch.zeros(1, 1, 512, dtype=torch.uint8, device=cuda))
+
+
+@pytest.mark.parametrize("M,K", [(1, 8192), (5, 2112), (16, 1024), (16, 8192), (3, 64), (16, 7168)])
+@pytest.mark.parametrize("arith,assoc", [("spec", "spec"), ("kernel_ieee", "kernel")])
+def test_nvfp4_small_activation_kernel_vs_oracle(cuda, lib, M, K, arith, assoc):
+    """M <= 16, K <= 8192 takes the thread-block-cluster kernel (amax through distributed shared memory)."""
+    A = randn_bf16((M, K), seed=M * 11 + K, outlier_frac=0.01)
+    rc, rs, rg = O.nvfp4_quantize(bf16_bits(A), False, assoc)
+    codes, sc, sg = gpu_nvfp4_quantize(A.to(cuda), False, arith)
+    assert sg[0] == rg[0]
+    assert np.array_equal(sc, rs), f"{(sc != rs).sum()} scale bytes differ"
+    assert np.array_equal(codes, rc), f"{(codes != rc).sum()} code bytes differ"
+
+
+@pytest.mark.parametrize("M,K", [(1, 8192), (16, 8192), (7, 4160)])
+def test_nvfp4_small_activation_kernel_fast_arithmetic_equals_general_kernel(cuda, lib, M, K):
+    """The fast-math arithmetic has no CPU restatement: the cluster kernel must equal the general kernel, which is reached
+    by supplying the amax (and which is bit-identical to the reference's own kernel)."""
+    ops = _ops()
+    A = randn_bf16((M, K), seed=M + K, outlier_frac=0.01).to(cuda)
+    amax = torch.zeros(1, dtype=torch.float32, device=cuda)
+    ops.absmax_bf16(A, amax)
+    a = gpu_nvfp4_quantize(A, False, "kernel_fast")
+    b = gpu_nvfp4_quantize(A, False, "kernel_fast", amax)
+    assert a[2][0] == b[2][0] and np.array_equal(a[1], b[1]) and np.array_equal(a[0], b[0])

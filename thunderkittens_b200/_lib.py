@@ -53,6 +53,10 @@ _SIGNATURES = {
     "tkb_all_to_all_4d": ([C.POINTER(_vp), _vp, C.POINTER(C.c_longlong), _i, _i, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_ag_copy_create": ([_i, _i, C.POINTER(_vp)], _i),
     "tkb_ag_copy_destroy": ([_vp], _i),
+    "tkb_ag_graph_create": ([_vp, C.c_uint, _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i64, _i, _i,
+                             C.POINTER(_vp)], _i),
+    "tkb_ag_graph_launch": ([_vp, _vp], _i),
+    "tkb_ag_graph_destroy": ([_vp], _i),
     "tkb_ag_linear_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp], _i),
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp,
                            C.c_uint, _i, _vp], _i),
@@ -76,7 +80,7 @@ class AgState(C.Structure):
     _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("K", _i),
                 ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
                 ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp),
-                ("copy", _vp)]
+                ("copy", _vp), ("epoch_counter", _vp)]
 
 
 class MoeState(C.Structure):

@@ -36,6 +36,8 @@ constexpr int kSmallScratchRing = 4;
 constexpr size_t kSmallScratchBytes = 2u << 20;
 constexpr int kDecodeMaxGrid = 160;                      // CTAs the scratch is sized for
 constexpr size_t kDecodePartialFloats = size_t(kDecodeMaxGrid) * 128 * 128;
+constexpr int kDecodeDynSlabs = 1024;                    // slab counters of the dynamic phase per scratch set
+constexpr size_t kDecodeDynFloats = size_t(4) << 20;     // 16 MB of partial tiles of the dynamic phase per scratch set
 
 struct DeviceCtx {
     bool ready = false;
@@ -49,6 +51,8 @@ struct DeviceCtx {
     std::atomic<unsigned> small_scratch_calls{0};
     float* decode_partials = nullptr;
     unsigned int* decode_flags = nullptr;
+    unsigned int* decode_dyn_words = nullptr;   // per set: 1 work counter + kDecodeDynSlabs slab counters, zeroed
+    float* decode_dyn_partials = nullptr;
     // one scratch set per stream that has used the kernel: calls on one stream are ordered by the stream, calls on different
     // streams never share a set
     cudaStream_t decode_stream[kDecodeRing] = {};
@@ -135,7 +139,12 @@ static int ensure_decode_scratch(DeviceCtx* c) {
     TKB_CUDA(cudaMalloc(&part, kDecodeRing * kDecodePartialFloats * sizeof(float)));
     TKB_CUDA(cudaMalloc(&flags, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
     TKB_CUDA(cudaMemset(flags, 0, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
+    unsigned int* dynw = nullptr; float* dynp = nullptr;
+    TKB_CUDA(cudaMalloc(&dynw, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
+    TKB_CUDA(cudaMemset(dynw, 0, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
+    TKB_CUDA(cudaMalloc(&dynp, kDecodeRing * kDecodeDynFloats * sizeof(float)));
     TKB_CUDA(cudaDeviceSynchronize());
+    c->decode_dyn_words = dynw; c->decode_dyn_partials = dynp;
     c->decode_flags = flags;
     c->decode_partials = part;
     return TKB_OK;
@@ -173,6 +182,8 @@ static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const fl
     d.max_grid = kDecodeMaxGrid;
     d.status = c->status; d.sm_count = c->sm_count; d.stream = static_cast<cudaStream_t>(stream); d.prof = g_prof;
     d.prefetch_weights = prefetch_weights;
+    d.dyn_ctr = c->decode_dyn_words + size_t(ring) * (kDecodeDynSlabs + 1); d.dyn_cnt = d.dyn_ctr + 1;
+    d.dyn_partials = c->decode_dyn_partials + size_t(ring) * kDecodeDynFloats; d.dyn_partial_floats = kDecodeDynFloats; d.dyn_max_slabs = kDecodeDynSlabs;
     TKB_CUDA(launch_decode(d));
     return TKB_OK;
 }
@@ -311,13 +322,14 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
 
 // tkb_nvfp4_quantize_sharded plus an optional stamp: `stamp_count` device words that the kernel fills with `epoch`.
 int api_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
-                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count, void* stream) {
+                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count,
+                         const unsigned int* epoch_ptr, void* stream) {
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: world must be 1..8 and 0 <= rank < world");
     if (layout != 0 && layout != 1) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: layout must be 0 (operand) or 1 (self-contained rows)");
     if (world > 1 && (!peer_slots || epoch == 0)) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot table or epoch 0");
     QuantExchange x;
     memset(&x, 0, sizeof(x));
-    x.world = world; x.rank = rank; x.epoch = epoch; x.stamp = stamp; x.stamp_count = stamp ? stamp_count : 0;
+    x.world = world; x.rank = rank; x.epoch = epoch; x.stamp = stamp; x.stamp_count = stamp ? stamp_count : 0; x.epoch_ptr = epoch_ptr;
     for (int i = 0; i < world && world > 1; i++) {
         if (!peer_slots[i]) return api_fail(TKB_ERR_INVALID_ARG, "nvfp4_quantize_sharded: null slot array for rank %d", i);
         x.slots[i] = static_cast<unsigned long long*>(peer_slots[i]);
@@ -352,7 +364,17 @@ int tkb_device_status(void* stream, int* status) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     TKB_CUDA(cudaStreamSynchronize(s));
     TKB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (*status) TKB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+    if (*status) {
+        TKB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+        // A kernel that gave up may have left its stream-K bookkeeping half way (flags raised, counters not put back): start
+        // the skinny-M scratch from zero again.  The caller has just synchronised its stream; other streams' calls in flight
+        // at this moment belong to the same failed state.
+        if (c->decode_flags) {
+            TKB_CUDA(cudaDeviceSynchronize());
+            TKB_CUDA(cudaMemset(c->decode_flags, 0, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
+            TKB_CUDA(cudaMemset(c->decode_dyn_words, 0, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
+        }
+    }
     return TKB_OK;
 }
 
@@ -375,7 +397,7 @@ int tkb_nvfp4_quantize_rows(const void* A_bf16, int64_t lda, void* rows, float* 
 
 int tkb_nvfp4_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
                                void* const* peer_slots, int world, int rank, unsigned int epoch, void* stream) {
-    return api_quantize_sharded(A_bf16, lda, codes, sc, sg, M, K, layout, arithmetic, peer_slots, world, rank, epoch, nullptr, 0, stream);
+    return api_quantize_sharded(A_bf16, lda, codes, sc, sg, M, K, layout, arithmetic, peer_slots, world, rank, epoch, nullptr, 0, nullptr, stream);
 }
 
 int tkb_absmax_bf16(const void* A_bf16, int64_t lda, int M, int K, float* amax, void* stream) {

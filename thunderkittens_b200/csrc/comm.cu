@@ -23,7 +23,8 @@ int api_fail(int code, const char* fmt, ...);          // api.cu
 int api_device(int* sm_count, int** status);
 unsigned long long* api_profile_buffer();             // api.cu: tkb_gemm_set_profile_buffer           // api.cu
 int api_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc, float* sg, int M, int K, int layout, int arithmetic,
-                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count, void* stream);   // api.cu
+                         void* const* peer_slots, int world, int rank, unsigned int epoch, unsigned int* stamp, int stamp_count,
+                         const unsigned int* epoch_ptr, void* stream);   // api.cu
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
 
@@ -294,9 +295,9 @@ int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* di
     return TKB_OK;
 }
 
-int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
-                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
-                      void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream) {
+static int ag_gemm_impl(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
+                        const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
+                        void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* epoch_counter, void* stream) {
     if (!peer_codes || !peer_scales || !X_sg || !W || !W_sc || !W_sg || !D || !peer_arrived)
         return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: null pointer");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: world must be 1..%d", kMaxWorld);
@@ -307,6 +308,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
     if (comm_ctas < 0 || comm_ctas % 2 || comm_ctas > sm - 2) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: comm_ctas must be even and leave compute CTAs");
     // comm_ctas == 0 with world > 1: the caller moves the rows itself (copy engines, see tkb_ag_linear_nvfp4) and raises the arrival flags
     if (peer_done && !exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: peer_done needs an exit counter");
+    if (epoch_counter && (!exit_counter || comm_ctas != 0)) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: a device-side epoch needs an exit counter and comm_ctas == 0");
     GemmArgs g;
     memset(&g, 0, sizeof(g));
     g.kind = KIND_NVFP4; g.config = 0;
@@ -330,10 +332,21 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
         }
         g.comm.ag.exit_counter = static_cast<unsigned int*>(exit_counter);
     }
+    if (epoch_counter) {
+        g.comm.ag.exit_counter = static_cast<unsigned int*>(exit_counter);
+        g.comm.ag.epoch_counter = static_cast<unsigned int*>(epoch_counter);
+    }
     g.comm.ag.epoch = epoch; g.comm.ag.rank = rank; g.comm.ag.world = world; g.comm.ag.blocks_per_rank = M / world / 256;
     g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
     TKB_CUDA_C(launch_gemm(g));
     return TKB_OK;
+}
+
+int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
+                      const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
+                      void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream) {
+    return ag_gemm_impl(peer_codes, peer_scales, X_sg, W, W_sc, W_sg, D, ldd, M, N_local, K, rank, world, peer_arrived, peer_done, exit_counter, epoch,
+                        comm_ctas, nullptr, stream);
 }
 
 int tkb_debug_struct_layout(int which, int field) {
@@ -346,7 +359,7 @@ int tkb_debug_struct_layout(int which, int field) {
             TKB_OFF(tkb_ag_state, rank) TKB_OFF(tkb_ag_state, world) TKB_OFF(tkb_ag_state, M) TKB_OFF(tkb_ag_state, K)
             TKB_OFF(tkb_ag_state, codes) TKB_OFF(tkb_ag_state, scales) TKB_OFF(tkb_ag_state, arrived) TKB_OFF(tkb_ag_state, slots)
             TKB_OFF(tkb_ag_state, done) TKB_OFF(tkb_ag_state, amax) TKB_OFF(tkb_ag_state, sg) TKB_OFF(tkb_ag_state, exit_counter)
-            TKB_OFF(tkb_ag_state, copy)
+            TKB_OFF(tkb_ag_state, copy) TKB_OFF(tkb_ag_state, epoch_counter)
             default: return -1;
         }
     }
@@ -435,6 +448,49 @@ int tkb_ag_copy_destroy(void* handle) {
     return TKB_OK;
 }
 
+// One step of the column-parallel layer with the gather done by copy engines.  `quantized` is recorded in `main` after the
+// quantize launch, copied[j] in copy stream j after the step's last copy there; with wait_prev, `main` first waits for
+// copied[] as left by the step two calls ago (the same buffer set).
+// Ordering argument: the amax exchange inside the quantize kernel is a barrier over the ranks for this epoch, and a rank only
+// reaches it after its GEMM of the previous step (same stream).  So once this rank's quantize kernel has finished, no peer
+// still reads the buffer set of two steps ago, which is the one written now; no separate acknowledgement is needed.  The copy
+// streams carry copies only (no kernels), so they never compete with the persistent GEMM kernel for an SM.  The epoch is
+// read on the device (st->epoch_counter), which is what makes the step replayable from a graph.
+static int ag_ce_step(const tkb_ag_state* st, AgCopyCtx* c, cudaEvent_t quantized, cudaEvent_t* copied, bool wait_prev, unsigned int epoch,
+                      const void* X_local, const void* W, const void* W_sc, const float* W_sg, void* D, int64_t ldd, int N_local, int arithmetic,
+                      cudaStream_t main) {
+    const int w = st->world, r = st->rank, b = int(epoch % 2u);
+    const int rows = st->M / w, flags_per_rank = rows / 64;
+    if (c->stamp_count < flags_per_rank) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: tkb_ag_copy_create was given fewer than M / world / 64 flags");
+    if (!st->epoch_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs st->epoch_counter");
+    uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
+    uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
+    if (wait_prev)
+        for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(main, copied[i], 0));
+    if (int e = api_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, c->stamp[b],
+                                     flags_per_rank, static_cast<const unsigned int*>(st->epoch_counter), main))
+        return e;
+    TKB_CUDA_C(cudaEventRecord(quantized, main));
+    // the GEMM goes into the queue first: it starts with this rank's own rows while the host is still issuing the copies
+    if (int e = ag_gemm_impl(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b], nullptr,
+                             st->exit_counter, epoch, 0, st->epoch_counter, main))
+        return e;
+    const size_t code_bytes = size_t(rows) * (st->K / 2), code_off = size_t(r) * code_bytes;
+    const size_t sc_bytes = size_t(rows / 128) * (st->K / 64) * 512, sc_off = size_t(r) * sc_bytes;
+    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(c->stream[i], quantized, 0));
+    for (int i = 1; i < w; i++) {
+        const int d = (r + w - i) % w;           // in the order in which the peers consume this rank's rows
+        cudaStream_t cs = c->stream[(i - 1) % c->n_streams];
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->codes[b][d]) + code_off, my_codes, code_bytes, cudaMemcpyDeviceToDevice, cs));
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->scales[b][d]) + sc_off, my_scales, sc_bytes, cudaMemcpyDeviceToDevice, cs));
+        // stream order: the flags leave after the rows they announce have been written
+        TKB_CUDA_C(cudaMemcpyAsync(static_cast<unsigned int*>(st->arrived[b][d]) + size_t(r) * flags_per_rank, c->stamp[b],
+                                   size_t(flags_per_rank) * sizeof(unsigned int), cudaMemcpyDeviceToDevice, cs));
+    }
+    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaEventRecord(copied[i], c->stream[i]));
+    return TKB_OK;
+}
+
 int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* X_local, const void* W, const void* W_sc, const float* W_sg,
                         void* D, int64_t ldd, int N_local, int comm_ctas, int arithmetic, void* stream) {
     if (!st || !X_local || epoch == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: null state/input or epoch 0");
@@ -454,39 +510,85 @@ int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* 
         return tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
                                  st->done, st->exit_counter, epoch, w > 1 ? comm_ctas : 0, stream);
     }
-    // ---- copy-engine gather.  Ordering argument: the amax exchange inside the quantize kernel is a barrier over the ranks
-    // for this epoch, and a rank only reaches it after its GEMM of the previous call (same stream).  So once this rank's
-    // quantize kernel has finished, no peer still reads the buffer set of epoch - 2, which is the one written now; no
-    // separate acknowledgement is needed.  The copy streams carry copies only (no kernels), so they never compete with the
-    // persistent GEMM kernel for an SM.
     AgCopyCtx* c = static_cast<AgCopyCtx*>(st->copy);
-    const int flags_per_rank = rows / 64;
-    if (!c || c->stamp_count < flags_per_rank)
-        return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs st->copy from tkb_ag_copy_create(n, >= M / world / 64)");
+    if (!c) return api_fail(TKB_ERR_INVALID_ARG, "ag_linear: the copy-engine gather needs st->copy from tkb_ag_copy_create");
     // the copies of epoch - 2 read the slice and the flag pattern that are about to be overwritten
-    if (epoch > 2)
-        for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(main, c->copied[b][i], 0));
-    if (int e = api_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, c->stamp[b],
-                                     flags_per_rank, stream))
-        return e;
-    TKB_CUDA_C(cudaEventRecord(c->quantized, main));
-    // the GEMM goes into the queue first: it starts with this rank's own rows while the host is still issuing the copies
-    if (int e = tkb_ag_gemm_nvfp4(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b],
-                                  nullptr, nullptr, epoch, 0, stream))
-        return e;
-    const size_t code_bytes = size_t(rows) * (st->K / 2), code_off = size_t(r) * code_bytes;
-    const size_t sc_bytes = size_t(rows / 128) * (st->K / 64) * 512, sc_off = size_t(r) * sc_bytes;
-    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaStreamWaitEvent(c->stream[i], c->quantized, 0));
-    for (int i = 1; i < w; i++) {
-        const int d = (r + w - i) % w;           // in the order in which the peers consume this rank's rows
-        cudaStream_t cs = c->stream[(i - 1) % c->n_streams];
-        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->codes[b][d]) + code_off, my_codes, code_bytes, cudaMemcpyDeviceToDevice, cs));
-        TKB_CUDA_C(cudaMemcpyAsync(static_cast<uint8_t*>(st->scales[b][d]) + sc_off, my_scales, sc_bytes, cudaMemcpyDeviceToDevice, cs));
-        // stream order: the flags leave after the rows they announce have been written
-        TKB_CUDA_C(cudaMemcpyAsync(static_cast<unsigned int*>(st->arrived[b][d]) + size_t(r) * flags_per_rank, c->stamp[b],
-                                   size_t(flags_per_rank) * sizeof(unsigned int), cudaMemcpyDeviceToDevice, cs));
+    return ag_ce_step(st, c, c->quantized, c->copied[b], epoch > 2, epoch, X_local, W, W_sc, W_sg, D, ldd, N_local, arithmetic, main);
+}
+
+// ---- the same step, recorded once and replayed: a CUDA graph of `steps` consecutive calls -------------------------------
+struct AgGraph { cudaGraph_t graph; cudaGraphExec_t exec; AgCopyCtx* copy; int steps; };
+
+int tkb_ag_graph_create(const tkb_ag_state* st, unsigned int first_epoch, int steps, const void* const* X_local, const void* const* W,
+                        const void* const* W_sc, const float* const* W_sg, void* const* D, int64_t ldd, int N_local, int arithmetic, void** handle) {
+    if (!st || !handle || !X_local || !W || !W_sc || !W_sg || !D) return api_fail(TKB_ERR_INVALID_ARG, "ag_graph_create: null pointer");
+    if (steps < 2 || steps % 2 || steps > 64) return api_fail(TKB_ERR_INVALID_ARG, "ag_graph_create: steps must be even (both buffer sets), 2..64");
+    if (first_epoch == 0) return api_fail(TKB_ERR_INVALID_ARG, "ag_graph_create: epochs start at 1");
+    AgCopyCtx* c = static_cast<AgCopyCtx*>(st->copy);
+    if (st->world < 2 || !c || !st->epoch_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_graph_create: needs world > 1, st->copy and st->epoch_counter");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;          // creates the per-device context before the capture starts
+    cudaStream_t cap = nullptr;
+    cudaEvent_t quantized[64] = {}, copied[64][kAgMaxCopyStreams] = {};
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = TKB_OK;
+    cudaError_t ce = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
+    for (int i = 0; i < steps && ce == cudaSuccess; i++) {
+        ce = cudaEventCreateWithFlags(&quantized[i], cudaEventDisableTiming);
+        for (int j = 0; j < c->n_streams && ce == cudaSuccess; j++) ce = cudaEventCreateWithFlags(&copied[i][j], cudaEventDisableTiming);
     }
-    for (int i = 0; i < c->n_streams; i++) TKB_CUDA_C(cudaEventRecord(c->copied[b][i], c->stream[i]));
+    bool capturing = false;
+    if (ce == cudaSuccess) { ce = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal); capturing = ce == cudaSuccess; }
+    for (int i = 0; i < steps && ce == cudaSuccess && rc == TKB_OK; i++) {
+        // inside the graph a step waits for the copies of the step two before it; the first two steps have nothing to wait for,
+        // because the graph ends only when all of its copies have ended and a launch starts after the previous one has ended
+        if (i >= 2)
+            for (int j = 0; j < c->n_streams && ce == cudaSuccess; j++) ce = cudaStreamWaitEvent(cap, copied[i - 2][j], 0);
+        if (ce == cudaSuccess)
+            rc = ag_ce_step(st, c, quantized[i], copied[i], false, first_epoch + unsigned(i), X_local[i], W[i], W_sc[i], W_sg[i], D[i], ldd, N_local,
+                            arithmetic, cap);
+    }
+    if (capturing) {
+        for (int i = steps - 2; i < steps && ce == cudaSuccess && rc == TKB_OK; i++)        // join the copy streams of the last two steps
+            for (int j = 0; j < c->n_streams && ce == cudaSuccess; j++) ce = cudaStreamWaitEvent(cap, copied[i][j], 0);
+        cudaError_t ee = cudaStreamEndCapture(cap, &graph);       // always ends the capture, also after an error
+        if (ce == cudaSuccess) ce = ee;
+    }
+    if (ce == cudaSuccess && rc == TKB_OK) ce = cudaGraphInstantiate(&exec, graph, 0);
+    for (int i = 0; i < steps; i++) {
+        if (quantized[i]) cudaEventDestroy(quantized[i]);
+        for (int j = 0; j < kAgMaxCopyStreams; j++) if (copied[i][j]) cudaEventDestroy(copied[i][j]);
+    }
+    if (cap) cudaStreamDestroy(cap);
+    if (rc != TKB_OK || ce != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != TKB_OK) return rc;
+        return api_fail(TKB_ERR_CUDA, "ag_graph_create: %s", cudaGetErrorString(ce));
+    }
+    AgGraph* g = new (std::nothrow) AgGraph{graph, exec, c, steps};
+    if (!g) { cudaGraphExecDestroy(exec); cudaGraphDestroy(graph); return api_fail(TKB_ERR_CUDA, "ag_graph_create: out of host memory"); }
+    *handle = g;
+    return TKB_OK;
+}
+
+int tkb_ag_graph_launch(void* handle, void* stream) {
+    AgGraph* g = static_cast<AgGraph*>(handle);
+    if (!g) return api_fail(TKB_ERR_INVALID_ARG, "ag_graph_launch: null handle");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // copies of earlier, individually issued steps may still read the slices that the graph's first steps overwrite
+    for (int b = 0; b < 2; b++)
+        for (int j = 0; j < g->copy->n_streams; j++) TKB_CUDA_C(cudaStreamWaitEvent(s, g->copy->copied[b][j], 0));
+    TKB_CUDA_C(cudaGraphLaunch(g->exec, s));
+    return TKB_OK;
+}
+
+int tkb_ag_graph_destroy(void* handle) {
+    AgGraph* g = static_cast<AgGraph*>(handle);
+    if (!g) return TKB_OK;
+    cudaGraphExecDestroy(g->exec);
+    cudaGraphDestroy(g->graph);
+    delete g;
     return TKB_OK;
 }
 

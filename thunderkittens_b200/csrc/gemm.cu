@@ -236,12 +236,13 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
 
 // Every CTA of the all-gather kernel calls this (one thread) when it has finished: the last one to arrive tells the
 // peers that this rank no longer reads the buffer set of this epoch.
-__device__ __forceinline__ void ag_exit(const AgParams& ag) {
+__device__ __forceinline__ void ag_exit(const AgParams& ag, unsigned int epoch_now) {
     if (ag.exit_counter == nullptr) return;
     __threadfence();
     const unsigned int prev = atomicAdd(ag.exit_counter, 1u);
     if (prev == gridDim.x - 1) {
         *reinterpret_cast<volatile unsigned int*>(ag.exit_counter) = 0u;       // ready for the next launch
+        if (ag.epoch_counter != nullptr) *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) = epoch_now;     // this step is complete
         __threadfence_system();
         for (int pr = 0; pr < ag.world; pr++)
             if (pr != ag.rank && ag.peer_done[pr] != nullptr)
@@ -433,7 +434,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (is_comm) {
             ag_push(ag, int(blockIdx.x), p.K / 2, (p.K / 64) * 512, wc, p.prof ? p.prof + blockIdx.x * 8 : nullptr);
             __syncthreads();
-            if (threadIdx.x == 0) ag_exit(ag);
+            if (threadIdx.x == 0) ag_exit(ag, ag.epoch);
             cluster_sync();      // matches the teardown barrier of the compute clusters' code path below
             return;
         }
@@ -446,6 +447,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             bool ok = true;
             long long waited = 0, waited_flags = 0;
             asm volatile("griddepcontrol.wait;" ::: "memory");      // operands may come from the previous kernel in the stream
+            // the arrival epoch of this step: given by the host, or one past the device's count of completed steps
+            unsigned int ag_epoch = 0;
+            if constexpr (AG) ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
+            (void)ag_epoch;
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
@@ -464,7 +469,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (src != ag.rank) {
                         const long long t0 = clock64();
                         for (int part = 0; part < kAgPartsPerBlock && ok; part++)
-                            ok = flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk * kAgPartsPerBlock + part, ag.epoch);
+                            ok = flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk * kAgPartsPerBlock + part, ag_epoch);
                         if (!ok) break;
                         fence_proxy_async_all();
                         waited_flags += clock64() - t0;
@@ -687,7 +692,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_dealloc<CTAS>(tmem_base, C::TMEM_COLS);
     }
     if constexpr (AG) {
-        if (threadIdx.x == 0) ag_exit(ag);      // after the barrier: this CTA's operand loads and output stores are complete
+        // (read before this CTA's own arrival on the exit counter, so before the last CTA can have advanced the count)
+        const unsigned int ag_epoch_exit = (threadIdx.x == 0 && ag.epoch_counter) ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
+        if (threadIdx.x == 0) ag_exit(ag, ag_epoch_exit);      // after the barrier: this CTA's operand loads and output stores are complete
     }
 }
 

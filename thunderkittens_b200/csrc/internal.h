@@ -35,6 +35,9 @@ struct AgParams {
     unsigned int* exit_counter;              // with peer_done: zeroed device word, counts the CTAs that have left the kernel
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
+    // optional (comm_ctas == 0 only): a device word that counts completed steps.  The kernel waits for arrival epoch
+    // *epoch_counter + 1 instead of `epoch`, and its last CTA to finish (exit_counter) adds one to the word.
+    unsigned int* epoch_counter;
 };
 
 // MoE mode: dispatch (pull of routed token rows from their home ranks) fused with the grouped expert GEMM.
@@ -82,6 +85,9 @@ struct DecodeArgs {
     int* status; int sm_count; cudaStream_t stream;
     unsigned long long* prof;   // optional per-CTA timeline, 8 x uint64 per CTA
     int prefetch_weights;       // TKB_GEMM_SKINNY_PREFETCH
+    // optional scratch of the dynamic phase (all null: static schedule only): a zeroed work counter, dyn_max_slabs zeroed slab
+    // counters, room for dyn_partial_floats floats of partial tiles
+    unsigned int* dyn_ctr; unsigned int* dyn_cnt; float* dyn_partials; size_t dyn_partial_floats; int dyn_max_slabs;
 };
 cudaError_t launch_decode(const DecodeArgs& a);
 int decode_padded_rows(int M);

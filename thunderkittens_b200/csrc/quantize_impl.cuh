@@ -88,12 +88,13 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
         __threadfence();
         const unsigned int prev = atomicAdd(&ws->arrived, 1u);
         const bool exchange = xch.world > 1;
+        const unsigned int epoch = xch.epoch_ptr ? *reinterpret_cast<const volatile unsigned int*>(xch.epoch_ptr) + 1u : xch.epoch;
         const unsigned int target = gridDim.x + (exchange ? 1u : 0u);
         const long long t0 = clock64();
         if (exchange && prev == gridDim.x - 1) {
             __threadfence();
             float g = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(&ws->amax_bits));
-            const unsigned long long mine = (static_cast<unsigned long long>(xch.epoch) << 32) | __float_as_uint(g);
+            const unsigned long long mine = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(g);
             for (int pr = 0; pr < xch.world; pr++)
                 if (pr != xch.rank) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(xch.slots[pr] + xch.rank), "l"(mine) : "memory");
             bool got_all = true;
@@ -102,7 +103,7 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
                 unsigned long long got;
                 while (true) {
                     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(xch.slots[xch.rank] + pr) : "memory");
-                    if (int(unsigned(got >> 32) - xch.epoch) >= 0) break;
+                    if (int(unsigned(got >> 32) - epoch) >= 0) break;
                     if (clock64() - t0 > spin_limit) { got_all = false; break; }
                 }
                 if (got_all) g = fmaxf(g, __uint_as_float(unsigned(got & 0xffffffffu)));
@@ -161,8 +162,10 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     // launched with programmatic stream serialization: everything above overlapped the previous kernel's tail
     pdl_wait();
     pdl_launch_dependents();
-    if (xch.stamp != nullptr && blockIdx.x == 0)
-        for (int i = threadIdx.x; i < xch.stamp_count; i += Q_THREADS) xch.stamp[i] = xch.epoch;
+    if (xch.stamp != nullptr && blockIdx.x == 0) {
+        const unsigned int epoch = xch.epoch_ptr ? *reinterpret_cast<const volatile unsigned int*>(xch.epoch_ptr) + 1u : xch.epoch;
+        for (int i = threadIdx.x; i < xch.stamp_count; i += Q_THREADS) xch.stamp[i] = epoch;
+    }
     float amax;
     uint4 v[8];
     if constexpr (FUSED_AMAX) {
@@ -313,8 +316,111 @@ inline bool nvfp4_quantize_resident_ok(const NvQuantArgs& a) {
     return tiles <= (long long)a.sm_count * 2;
 }
 
+
+// ------------------------------------------------------------------------------ NVFP4, at most 16 rows -----
+// Activations of a decode step (M <= 16): the whole tensor is a few hundred KB, so the general kernel's persistent grid
+// and global-memory grid barrier cost more than the work.  Here one thread-block cluster of ceil(K / 1024) <= 8 CTAs
+// covers the tensor: CTA c owns columns [1024 c, 1024 c + 1024), warp w of it the 16 x 128 tile at column 128 w, held in
+// registers for both passes (one read of the input).  The per-tensor amax crosses the cluster through distributed
+// shared memory and one cluster barrier; no global scratch, no atomics.  Same arithmetic, same output layout (rows of
+// the single 128-row scale block past M are written as zeros).
+constexpr int QS_MAX_ROWS = 16, QS_COLS_PER_CTA = 1024, QS_MAX_CTAS = 8;
+
+template <class Arith>
+__global__ void __launch_bounds__(Q_THREADS)
+nvfp4_quantize_skinny_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
+                             uint8_t* __restrict__ sc, float* __restrict__ sg, int M, int K) {
+    __shared__ __align__(16) uint8_t s_chunks[QS_COLS_PER_CTA / 64][512];     // this CTA's 16 scale chunks, as stored
+    __shared__ float s_warp[Q_THREADS / 32];
+    __shared__ float s_peer[QS_MAX_CTAS];                                     // written by every CTA of the cluster
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t cta, ncta;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ncta));
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < int(sizeof(s_chunks) / 16); i += Q_THREADS) reinterpret_cast<uint4*>(&s_chunks[0][0])[i] = make_uint4(0, 0, 0, 0);
+    const TileCoord tc{0, int(cta) * QS_COLS_PER_CTA + warp * QT_COLS};
+    uint4 v[8];
+    load_tile(A, lda, M, K, tc, 0, lane, v);          // rows 2 i + (lane >> 4), columns tc.col0 + 8 (lane & 15)
+    float local = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) local = fmaxf(local, amax8(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, o));
+    if (lane == 0) s_warp[warp] = local;
+    __syncthreads();
+    if (threadIdx.x < ncta) {          // thread t hands this CTA's maximum to CTA t of the cluster
+        float m = s_warp[0];
+#pragma unroll
+        for (int w = 1; w < Q_THREADS / 32; w++) m = fmaxf(m, s_warp[w]);
+        const uint32_t local_addr = static_cast<uint32_t>(__cvta_generic_to_shared(&s_peer[cta]));
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(uint32_t(threadIdx.x)));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(m) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    float amax = 0.f;
+    for (uint32_t i = 0; i < ncta; i++) amax = fmaxf(amax, s_peer[i]);
+    float sg_dec, sg_enc;
+    Arith::global_scales(amax, sg_dec, sg_enc);
+    if (cta == 0 && threadIdx.x == 0) *sg = sg_dec;
+
+    const int kb_local = (lane & 15) >> 1;            // 16-element block within the warp's 128 columns
+    const int col = tc.col0 + (lane & 15) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int r = 2 * i + (lane >> 4);
+        float a = amax8(v[i]);
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+        const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(a, sg_enc), __NV_SATFINITE, __NV_E4M3);
+        if ((lane & 1) == 0) s_chunks[warp * 2 + (kb_local >> 2)][r * 16 + (kb_local & 3)] = s8;        // rows < 32: byte r * 16 + k-block % 4
+        const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float2 f = bf16x2_to_f2(w[j]);
+            f.x = Arith::scale_value(f.x, s_enc);
+            f.y = Arith::scale_value(f.y, s_enc);
+            packed |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * j);
+        }
+        if (r < M && col < K) *reinterpret_cast<uint32_t*>(codes + int64_t(r) * ldc + col / 2) = packed;
+    }
+    __syncthreads();
+    const int k_chunks = K / 64;
+    for (int i = threadIdx.x; i < int(sizeof(s_chunks) / 16); i += Q_THREADS) {
+        const int kc = int(cta) * (QS_COLS_PER_CTA / 64) + i / 32;
+        if (kc < k_chunks) reinterpret_cast<uint4*>(sc + int64_t(kc) * 512)[i % 32] = reinterpret_cast<const uint4*>(&s_chunks[0][0])[i];
+    }
+}
+
+template <class Arith>
+inline cudaError_t launch_nvfp4_quantize_skinny(const NvQuantArgs& a) {
+    auto kern = nvfp4_quantize_skinny_kernel<Arith>;
+    const int ctas = (a.K + QS_COLS_PER_CTA - 1) / QS_COLS_PER_CTA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas); cfg.blockDim = dim3(Q_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = ctas; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<const __nv_bfloat16*>(a.A), a.lda, static_cast<uint8_t*>(a.codes), a.ldc,
+                              static_cast<uint8_t*>(a.sc), a.sg, a.M, a.K);
+}
+
+// The cluster kernel covers: fused amax, 1-D scales, operand layout, one GPU, M <= 16, K <= 8192.
+inline bool nvfp4_quantize_skinny_ok(const NvQuantArgs& a) {
+    return a.amax_in == nullptr && !a.scale_2d && !a.sc_rowmajor && a.xch.world <= 1 && a.xch.stamp == nullptr && a.M <= QS_MAX_ROWS &&
+           a.K <= QS_COLS_PER_CTA * QS_MAX_CTAS;
+}
+
 template <class Arith>
 inline cudaError_t launch_nvfp4_quantize(const NvQuantArgs& a) {
+    if (nvfp4_quantize_skinny_ok(a)) return launch_nvfp4_quantize_skinny<Arith>(a);
     const bool fused = a.amax_in == nullptr;
     const bool res = fused && nvfp4_quantize_resident_ok(a);
     if (a.scale_2d) {

@@ -21,6 +21,9 @@ struct QuantExchange {
     // optional: `stamp_count` words that block 0 fills with `epoch` (the arrival-flag pattern that copy engines
     // forward to the peers after the rows of this call, see tkb_ag_linear_nvfp4)
     unsigned int* stamp; int stamp_count;
+    // optional: the epoch lives on the device (a count of completed steps, see tkb_ag_state.epoch_counter); the kernel then uses
+    // *epoch_ptr + 1 and ignores `epoch`, so that the launch can be replayed from a CUDA graph
+    const unsigned int* epoch_ptr;
 };
 
 struct NvQuantArgs {

@@ -130,6 +130,7 @@ class AllGatherMatmulNVFP4:
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
         self.exit_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch_counter = torch.zeros(1, dtype=torch.int32, device=dev)     # copy-engine gather: completed steps, kept by the kernels
         self.epoch = 0
         self.rows = M // local_world_size
         st = L.AgState()
@@ -141,8 +142,10 @@ class AllGatherMatmulNVFP4:
         for i in range(local_world_size):
             st.done[i] = self.flags.peer_ptr(i)
         st.amax, st.sg, st.exit_counter = self.amax.data_ptr(), self.sg.data_ptr(), self.exit_counter.data_ptr()
+        st.epoch_counter = self.epoch_counter.data_ptr()
         self.copy_engines = bool(copy_engines) and local_world_size > 1
         self._copy = None
+        self._graphs = []
         if self.copy_engines:
             # the gather travels by peer copies on streams that the library owns
             h = C.c_void_p()
@@ -166,6 +169,29 @@ class AllGatherMatmulNVFP4:
         arith = ops._ARITH[self.arithmetic or ops.default_nvfp4_arithmetic]
         L.check(L.lib().tkb_ag_linear_nvfp4(C.byref(self._state), self.epoch, X_local.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
                                             D.data_ptr(), 0, n_local, -1 if self.copy_engines else self.num_comm_sms, arith, _stream()))
+
+    def capture(self, steps):
+        """Records len(steps) consecutive calls as one CUDA graph (copy-engine gather only).  `steps` is a list of
+        (X_local, W, W_sc, W_sg, D) tuples of even length; the tensors must stay alive and in place.  Returns a handle for
+        `replay`.  Every rank must capture and replay alike."""
+        if not self.copy_engines:
+            raise RuntimeError("capture needs the copy-engine gather (copy_engines=True, world > 1)")
+        n = len(steps)
+        arr = lambda k: (C.c_void_p * n)(*[s[k].data_ptr() for s in steps])
+        h = C.c_void_p()
+        arith = ops._ARITH[self.arithmetic or ops.default_nvfp4_arithmetic]
+        n_local = steps[0][1].shape[0]
+        first = self.epoch + 1
+        L.check(L.lib().tkb_ag_graph_create(C.byref(self._state), first, n, arr(0), arr(1), arr(2), arr(3), arr(4), 0, n_local, arith, C.byref(h)))
+        self._graphs.append(h.value)
+        return (h.value, n, first % 2)
+
+    def replay(self, graph) -> None:
+        handle, n, parity = graph
+        if (self.epoch + 1) % 2 != parity:
+            raise RuntimeError("the graph was recorded starting on the other buffer set: issue one single call first")
+        L.check(L.lib().tkb_ag_graph_launch(handle, _stream()))
+        self.epoch += n
 
     def step_by_step(self, X_local: torch.Tensor, W: torch.Tensor, W_sc: torch.Tensor, W_sg: torch.Tensor, D: torch.Tensor) -> None:
         lib = L.lib()
@@ -194,6 +220,9 @@ class AllGatherMatmulNVFP4:
 
     def close(self) -> None:
         torch.cuda.synchronize()
+        for g in self._graphs:
+            L.lib().tkb_ag_graph_destroy(g)
+        self._graphs = []
         if self._copy is not None:
             L.lib().tkb_ag_copy_destroy(self._copy)
             self._copy = None
