@@ -285,10 +285,27 @@ def measure_tp(args, D_) -> dict:
     warm = max(args.warmup, 3)
     for i in range(warm):
         step(i)
+    # With the copy-engine gather a step costs the host about thirty driver calls, more than the ~0.1 ms the GPUs need at
+    # 8 ranks: the steps are therefore recorded once as a CUDA graph of 2 * GROUPS calls (both buffer sets x every operand
+    # set) and replayed; what does not fill a whole graph is issued call by call.  Same kernels, same copies, same epochs.
+    graph, per_graph = None, 2 * GROUPS
+    if ce and not args.no_graph:
+        graph = op.capture([sets[i % GROUPS] for i in range(per_graph)])
+        op.replay(graph)
     D_.barrier()
+
+    def run_steps(n):
+        done = 0
+        if graph is not None and (op.epoch + 1) % 2 == graph[2]:
+            while n - done >= per_graph:
+                op.replay(graph)
+                done += per_graph
+        for i in range(n - done):
+            step(i)
+
     cs = ClockSampler(D_.local_rank)
     host = []
-    dt = event_time(torch, step, args.steps, sampler=cs, host=host)
+    dt = event_time(torch, lambda i: run_steps(args.steps) if i == 0 else None, args.steps, sampler=cs, host=host)
     clocks = cs.summary()
     status = _lib.device_status()
     dt = D_.max(dt)
@@ -328,7 +345,7 @@ def measure_tp(args, D_) -> dict:
     del sets, dX
     torch.cuda.empty_cache()
     return {"dt": dt, "dt_e2e": dt_e2e, "clocks": clocks, "status": status, "host_enqueue_us": statistics.median(host) * 1e6 if host else None,
-            "quant_us": quant_us, "gemm_us": gemm_us, "copy_engines": ce, "comm_ctas": comm, "warmup": warm, "groups": GROUPS,
+            "quant_us": quant_us, "gemm_us": gemm_us, "graph": (f"{per_graph} steps per replayed CUDA graph" if graph is not None else None), "copy_engines": ce, "comm_ctas": comm, "warmup": warm, "groups": GROUPS,
             "h2d": rows * TP_K * 2 * world, "d2h": TP_M * n_local * 2 * world}
 
 
@@ -446,7 +463,7 @@ def run_ours(args) -> None:
             "e2e": {"value": TP_FLOPS / dt_e2e * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": tp["h2d"], "d2h_bytes_per_step": tp["d2h"],
                     "ms_per_step": dt_e2e * 1e3,
                     "path": "pinned host bf16 rows -> H2D -> AllGatherMatmulNVFP4 (tkb_ag_linear_nvfp4) -> D2H of the rank's output columns"},
-            "gpu_launches": args.steps * 2 * world, "host_enqueue_us_per_step": tp["host_enqueue_us"],
+            "gpu_launches": args.steps * 2 * world, "host_enqueue_us_per_step": tp["host_enqueue_us"], "cuda_graph": tp["graph"],
             "step_breakdown_us": {"quantize": tp["quant_us"], "gemm": tp["gemm_us"]} if world == 1 else None,
             "clocks": tp["clocks"], "extra": extras,
         }
@@ -769,6 +786,7 @@ def main() -> None:
     ap.add_argument("--workload", default="auto", choices=["auto", "moe", "tp_timeline"],
                     help="auto: the tensor-parallel NVFP4 GEMM (plus the side measurements); moe: the MoE layer alone; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
     ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 or -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
+    ap.add_argument("--no-graph", action="store_true", help="tensor-parallel step at N > 1 with the copy-engine gather: issue every step call by call instead of replaying a CUDA graph")
     ap.add_argument("--copy-streams", type=int, default=3, help="streams the copy-engine gather spreads its peer copies over (1..4)")
     ap.add_argument("--moe-comm-sms", type=int, default=0, help="CTAs of the MoE kernel that pull token rows over NVLink (0 = 32)")
     args = ap.parse_args()

@@ -321,7 +321,9 @@ int tkb_moe_schedule(const int* experts_all, int T, int top_k, int E, int world,
  * codes [cap_rows, K/2] and scales [cap_rows/128, K/64, 512] are local operand buffers the kernel fills;
  * W [experts_local * I, K/2], W_sc [experts_local * I / 128, K/64, 512], W_sg[1]: the rank's stacked expert weights;
  * Y [cap_rows, I] bf16 (leading dimension ldy, 0 = I).  ready [world] / arrived [cap_rows/128]: epoch arrays.
- * comm_ctas CTAs pull rows over NVLink while the others multiply.  K % 256 == 0, I % 128 == 0. */
+ * comm_ctas > 0: that many CTAs of the GEMM kernel pull rows over NVLink while the others multiply.  comm_ctas == 0: a gather
+ * kernel on all SMs pulls the rows first (16-byte loads, NVLink for remote rows) and publishes per-block arrival epochs, then
+ * every SM multiplies; two launches.  K % 256 == 0, I % 128 == 0. */
 int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes, void* scales,
                           const void* W, const void* W_sc, const float* W_sg, void* Y, int64_t ldy, const int* pull_idx,
                           const int* block_expert, const int* num_blocks, const void* ready, void* arrived, unsigned int epoch, int K,

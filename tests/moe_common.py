@@ -14,16 +14,34 @@ def make_problem(T, H, I, E, seed=0):
     return X, logits, W
 
 
-def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=print):
+def make_problem_sharded(T, H, I, E, rank, world, seed=0):
+    """The same kind of problem for sizes whose full weight tensor is too large to build on every rank: activations and
+    logits are identical on all ranks (one seeded stream), the expert weights are generated for this rank's experts only."""
+    rng = np.random.default_rng(seed)
+    X = torch.from_numpy(rng.standard_normal((T, H), dtype=np.float32)).to(torch.bfloat16)
+    logits = torch.from_numpy(rng.standard_normal((T, E), dtype=np.float32))
+    El = E // world
+    rw = np.random.default_rng(seed * 1000 + 17 + rank)
+    Wl = torch.from_numpy(rw.standard_normal((El, I, H), dtype=np.float32) * np.float32(0.02)).to(torch.bfloat16)
+    return X, logits, Wl
+
+
+def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=print, edge=0):
+    """edge > 0: weights are generated per rank and the grouped GEMM is checked on the first and last `edge` rows of every
+    expert segment only (sizes at which the whole product is too much for the CPU oracle)."""
     from thunderkittens_b200 import parallel, _lib
     Tl, El = T // world, E // world
     layer = parallel.MoELayerNVFP4(T, H, I, E, top_k, rank, world, num_comm_sms=comm_sms)
     layer.arithmetic = _lib.NVFP4_SPEC          # the CPU-reproducible quantizer arithmetic
     ok = True
     for it in range(iters):
-        X, logits, W = make_problem(T, H, I, E, seed=100 + it)
-        # this rank's stacked expert weights, quantized as one tensor
-        Wl = W[rank * El:(rank + 1) * El].reshape(El * I, H)
+        if edge > 0:
+            X, logits, Wl = make_problem_sharded(T, H, I, E, rank, world, seed=100 + it)
+            Wl = Wl.reshape(El * I, H)
+        else:
+            X, logits, W = make_problem(T, H, I, E, seed=100 + it)
+            # this rank's stacked expert weights, quantized as one tensor
+            Wl = W[rank * El:(rank + 1) * El].reshape(El * I, H)
         wq = O.nvfp4_quantize(bf16_bits(Wl))
         # both host paths of the layer on alternating calls: the single library call and the spelled-out sequence
         step = layer.forward if it % 2 == 0 else layer.forward_step_by_step
@@ -59,13 +77,22 @@ def run_and_check(dev, rank, world, T, H, I, E, top_k, iters=2, comm_sms=4, log=
             n = padded[rank * El + el]
             if n == 0:
                 continue
-            seg = pull[start:start + n]
+            if edge > 0:
+                # the first and the last `edge` rows of the segment (padded to a whole 128-row scale block for the oracle)
+                sel = np.concatenate([np.arange(edge), np.arange(n - edge, n)])
+                seg = np.full((128, 2), -1, pull.dtype)
+                seg[:2 * edge] = pull[start + sel]
+                got = Y[start + sel]
+            else:
+                seg = pull[start:start + n]
+                got = Y[start:start + n]
             tok = np.where(seg[:, 0] >= 0, seg[:, 0] * Tl + seg[:, 1], 0)
             valid = seg[:, 0] >= 0
             a_codes = np.where(valid[:, None], xq[0][tok], 0).astype(np.uint8)
             a_sc = O.swizzle_scales(np.where(valid[:, None], x_sc_rows[tok], 0).astype(np.uint8))
             ref = O.nvfp4_gemm(a_codes, a_sc, xq[2], wq[0][el * I:(el + 1) * I], O.swizzle_scales(w_sc_rows[el * I:(el + 1) * I]), wq[2])
-            got = Y[start:start + n]
+            if edge > 0:
+                ref = ref[:2 * edge]
             err = rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(ref))
             rr = O.bf16_to_f32(ref)
             big = np.abs(rr) > 1e-2 * np.sqrt((rr.astype(np.float64) ** 2).mean() + 1e-30)

@@ -1,4 +1,13 @@
-"""Worker for the multi-GPU MoE test (one process per GPU, launched by torchrun)."""
+"""Worker for the multi-GPU MoE test (one process per GPU, launched by torchrun).
+
+Environment:
+  TKB_TEST_MOE_SIZE  "small" (default): T = 256 * world, H = 512, I = 256, 16 * world experts, top-4, every stage against the oracle;
+                     "c5": the benchmark's layer (16384 tokens, hidden 7168, 128 experts, intermediate 2048, top-8): routing,
+                     schedule and combine map bit-exact, the grouped GEMM on the first and last rows of every expert segment.
+  TKB_TEST_MOE_COMM  CTAs of the GEMM kernel that pull rows (default 4, "c5": 32); 0 = the gather kernel on all SMs.
+Combine is checked bit for bit at every world size: the oracle gets the gathered expert outputs of all ranks and adds in the
+same order with the same fused multiply-adds.
+"""
 import os
 import sys
 
@@ -16,29 +25,26 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     import oracle as O
-    from tests.moe_common import run_and_check, make_problem
+    from tests.moe_common import run_and_check
     from tests.util import bf16_bits
-    T, H, I, E, k = 256 * world, 512, 256, 16 * world, 4
-    ok, layer = run_and_check(dev, rank, world, T, H, I, E, k, iters=3, comm_sms=4)
-    # combine across ranks: gather every rank's Y rows on the host side and evaluate the oracle's weighted sum
-    Tl, El = T // world, E // world
-    X, logits, W = make_problem(T, H, I, E, seed=100 + 2)        # the last iteration's inputs
-    experts, weights = O.moe_route(logits.numpy(), k)
-    out = layer.out.float().cpu().numpy()
+    size = os.environ.get("TKB_TEST_MOE_SIZE", "small")
+    if size == "c5":
+        T, H, I, E, k, iters, edge, comm = 16384, 7168, 2048, 128, 8, 2, 4, 32
+    else:
+        T, H, I, E, k, iters, edge, comm = 256 * world, 512, 256, 16 * world, 4, 3, 0, 4
+    comm = int(os.environ.get("TKB_TEST_MOE_COMM", comm))
+    ok, layer = run_and_check(dev, rank, world, T, H, I, E, k, iters=iters, comm_sms=comm, edge=edge)
+    # combine across ranks, bit for bit: the oracle's weighted sum over the gathered expert outputs of every rank
+    Tl = T // world
     ys = [torch.empty_like(layer.Y.data_) for _ in range(world)]
     dist.all_gather(ys, layer.Y.data_.contiguous())
-    g_w = layer.weights.cpu().numpy()
-    ref = np.zeros((Tl, I), np.float32)
+    Yall = np.concatenate([bf16_bits(y) for y in ys], axis=0)
+    cap = layer.Y.data_.shape[0]
     comb = layer.comb_idx.cpu().numpy().reshape(Tl, k, 2)
-    yn = [y.float().cpu().numpy() for y in ys]
-    for t in range(Tl):
-        a = np.zeros(I, np.float32)
-        for j in range(k):
-            a = np.float32(g_w[t, j]) * yn[comb[t, j, 0]][comb[t, j, 1]] + a
-        ref[t] = a
-    err = np.abs(out - ref).max() / max(np.abs(ref).max(), 1e-30)
-    comb_ok = err < 1e-2          # bf16 output rounding; the fused order is checked bit-exactly at world size 1
-    print(f"rank {rank}: combine max rel err {err:.2e}", flush=True)
+    slot = (comb[..., 0].astype(np.int64) * cap + comb[..., 1]).astype(np.int32)
+    ref = O.moe_combine(Yall, slot, layer.weights.cpu().numpy())
+    comb_ok = np.array_equal(bf16_bits(layer.out), ref)
+    print(f"rank {rank} [{size}, comm {comm}]: combine bit-exact against the oracle over the gathered outputs: {comb_ok}", flush=True)
     ok = ok and comb_ok
     dist.barrier()
     layer.close()

@@ -13,6 +13,7 @@
 //     ring starting at the local rank); segments are padded to 128 rows with (-1, -1) entries as in the reference;
 //   * combine (no counterpart in the reference): out[t] = bf16(sum_j w[t,j] * Y[row(t,j)]), fp32 accumulation in
 //     ascending j, rows read from the expert ranks over NVLink.
+#include <atomic>
 #include <cstring>
 #include "../../include/tkb200.h"
 #include "internal.h"
@@ -274,6 +275,118 @@ moe_sched_assign_kernel(const int* __restrict__ experts_all, int total, int top_
     }
 }
 
+// ------------------------------------------------------------------------------ gather ------
+// Dispatch as a kernel of its own (comm_ctas == 0 in tkb_moe_dispatch_gemm): every SM pulls routed rows, instead of a few
+// CTAs inside the GEMM kernel.  One CTA per 128-row block of the local operand buffer at a time: the block's (source
+// rank, source row) pairs are read from the pull list, the rows' codes are copied with 16-byte loads (NVLink for remote
+// rows, up to 8 in flight per thread) into the operand rows, the rows' scales are dropped into the 512-byte chunk layout
+// in shared memory and stored as one contiguous span; then the block's arrival epoch is published, on which the GEMM's
+// producers wait.  Padding rows (-1) become zeros.
+struct PeerRowBytes { const uint8_t* p[kMaxWorld]; };
+
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(512)
+moe_gather_kernel(PeerRowBytes rows, const int* __restrict__ pull_idx, const int* __restrict__ num_blocks, uint8_t* __restrict__ codes,
+                  uint8_t* __restrict__ scales, unsigned int* arrived, const unsigned int* ready, unsigned int epoch, int k_bytes,
+                  int sc_row_bytes, int world, int rank, int* status, long long limit) {
+    extern __shared__ __align__(16) uint8_t s_sc[];          // [sc_row_bytes / 4][512]: the block's scales as stored
+    __shared__ int s_idx[256];
+    __shared__ int s_ok;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0) {
+        // the peers' tokens of this call are quantized (their kernels signalled it)
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int pr = 0; pr < world && ok; pr++) {
+            if (pr == rank) continue;
+            while (true) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ready + pr) : "memory");
+                if (int(v - epoch) >= 0) break;
+                if (clock64() - t0 > limit) { ok = 0; if (status) atomicExch(status, (int)TKB_DEV_TIMEOUT); break; }
+                __nanosleep(100);
+            }
+        }
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int nb = *num_blocks;
+    const int row_bytes = k_bytes + sc_row_bytes;
+    const int k16 = k_bytes / 16, words = sc_row_bytes / 4;
+    const int sc_block_bytes = sc_row_bytes * 128;
+    constexpr int UNROLL = 8;
+    for (int blk = blockIdx.x; blk < nb; blk += gridDim.x) {
+        __syncthreads();                                     // the previous block's staging has been stored
+        if (tid < 256) s_idx[tid] = pull_idx[size_t(blk) * 256 + tid];
+        __syncthreads();
+        // codes: 128 x k16 pieces of 16 bytes, consecutive threads on consecutive pieces of a row
+        const int pieces = 128 * k16;
+        for (int base = tid; base < pieces; base += nthr * UNROLL) {
+            uint4 v[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int pc = base + u * nthr;
+                v[u] = make_uint4(0, 0, 0, 0);
+                if (pc < pieces) {
+                    const int r = pc / k16, c = pc - r * k16;
+                    const int src = s_idx[2 * r];
+                    if (src >= 0) v[u] = ld_cg_v4(rows.p[src] + size_t(s_idx[2 * r + 1]) * row_bytes + size_t(c) * 16);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int pc = base + u * nthr;
+                if (pc < pieces) {
+                    const int r = pc / k16, c = pc - r * k16;
+                    *reinterpret_cast<uint4*>(codes + (size_t(blk) * 128 + r) * k_bytes + size_t(c) * 16) = v[u];
+                }
+            }
+        }
+        // scales: one 32-bit word (64 K-elements) per row and chunk
+        const int nwords = 128 * words;
+        for (int base = tid; base < nwords; base += nthr * UNROLL) {
+            uint32_t v[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int w = base + u * nthr;
+                v[u] = 0u;
+                if (w < nwords) {
+                    const int r = w / words, kc = w - r * words;
+                    const int src = s_idx[2 * r];
+                    if (src >= 0) v[u] = ld_cg_u32(rows.p[src] + size_t(s_idx[2 * r + 1]) * row_bytes + k_bytes + size_t(kc) * 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; u++) {
+                const int w = base + u * nthr;
+                if (w < nwords) {
+                    const int r = w / words, kc = w - r * words;
+                    *reinterpret_cast<uint32_t*>(s_sc + size_t(kc) * 512 + (r & 31) * 16 + (r >> 5) * 4) = v[u];
+                }
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < sc_block_bytes / 16; i += nthr)
+            reinterpret_cast<uint4*>(scales + size_t(blk) * sc_block_bytes)[i] = reinterpret_cast<const uint4*>(s_sc)[i];
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(arrived + blk), "r"(epoch) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------ combine ------
 struct PeerRows { const __nv_bfloat16* p[kMaxWorld]; };
 
@@ -389,10 +502,35 @@ int tkb_moe_dispatch_gemm(void* const* peer_rows, const float* X_sg, void* codes
     // dispatch staging per comm CTA: a block's scales (128 x K/16 bytes), a zero row and a ring of row slots of which 16 trail the
     // loads (two batches whose stores may still read them), so at least 24 are needed to keep a batch of 8 loads in flight;
     // one thread per 64 K-elements
-    if (moe_dispatch_ring(K) < 24 || K / 64 + 1 > 320)
+    if (comm_ctas > 0 && (moe_dispatch_ring(K) < 24 || K / 64 + 1 > 320))
         return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d is too large for the dispatch staging in shared memory (%d row slots, 24 needed)",
                         K, moe_dispatch_ring(K));
-    if (comm_ctas < 1 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [1, %d]", sm / 2);
+    if (comm_ctas < 0 || comm_ctas > sm / 2) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: comm_ctas must be in [0, %d]", sm / 2);
+    if (comm_ctas == 0) {
+        // dispatch by a gather kernel on all SMs; the GEMM that follows waits on the per-block arrival epochs it publishes
+        const size_t smem = size_t(K / 16) * 128;
+        if (smem > 200 * 1024) return api_fail(TKB_ERR_INVALID_ARG, "moe_dispatch_gemm: K=%d is too large for the gather kernel's scale staging", K);
+        static std::atomic<bool> attr_set[64] = {};
+        int dev = 0;
+        TKB_CUDA_M(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
+            TKB_CUDA_M(cudaFuncSetAttribute(moe_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
+        }
+        PeerRowBytes pr;
+        for (int i = 0; i < kMaxWorld; i++) pr.p[i] = i < world ? static_cast<const uint8_t*>(peer_rows[i]) : nullptr;
+        const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+        int grid = cap_rows / 128 < sm * per_sm ? cap_rows / 128 : sm * per_sm;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        TKB_CUDA_M(cudaLaunchKernelEx(&cfg, moe_gather_kernel, pr, pull_idx, num_blocks, static_cast<uint8_t*>(codes), static_cast<uint8_t*>(scales),
+                                      static_cast<unsigned int*>(arrived), static_cast<const unsigned int*>(ready), epoch, K / 2, K / 16, world, rank,
+                                      status, api_wait_limit()));
+    }
     if (ldy == 0) ldy = I;
     GemmArgs g;
     memset(&g, 0, sizeof(g));
