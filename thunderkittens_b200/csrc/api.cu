@@ -36,8 +36,6 @@ constexpr int kSmallScratchRing = 4;
 constexpr size_t kSmallScratchBytes = 2u << 20;
 constexpr int kDecodeMaxGrid = 160;                      // CTAs the scratch is sized for
 constexpr size_t kDecodePartialFloats = size_t(kDecodeMaxGrid) * 128 * 128;
-constexpr int kDecodeDynSlabs = 1024;                    // slab counters of the dynamic phase per scratch set
-constexpr size_t kDecodeDynFloats = size_t(4) << 20;     // 16 MB of partial tiles of the dynamic phase per scratch set
 
 struct DeviceCtx {
     bool ready = false;
@@ -51,8 +49,6 @@ struct DeviceCtx {
     std::atomic<unsigned> small_scratch_calls{0};
     float* decode_partials = nullptr;
     unsigned int* decode_flags = nullptr;
-    unsigned int* decode_dyn_words = nullptr;   // per set: 1 work counter + kDecodeDynSlabs slab counters, zeroed
-    float* decode_dyn_partials = nullptr;
     // one scratch set per stream that has used the kernel: calls on one stream are ordered by the stream, calls on different
     // streams never share a set
     cudaStream_t decode_stream[kDecodeRing] = {};
@@ -139,12 +135,7 @@ static int ensure_decode_scratch(DeviceCtx* c) {
     TKB_CUDA(cudaMalloc(&part, kDecodeRing * kDecodePartialFloats * sizeof(float)));
     TKB_CUDA(cudaMalloc(&flags, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
     TKB_CUDA(cudaMemset(flags, 0, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
-    unsigned int* dynw = nullptr; float* dynp = nullptr;
-    TKB_CUDA(cudaMalloc(&dynw, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
-    TKB_CUDA(cudaMemset(dynw, 0, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
-    TKB_CUDA(cudaMalloc(&dynp, kDecodeRing * kDecodeDynFloats * sizeof(float)));
     TKB_CUDA(cudaDeviceSynchronize());
-    c->decode_dyn_words = dynw; c->decode_dyn_partials = dynp;
     c->decode_flags = flags;
     c->decode_partials = part;
     return TKB_OK;
@@ -182,8 +173,6 @@ static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const fl
     d.max_grid = kDecodeMaxGrid;
     d.status = c->status; d.sm_count = c->sm_count; d.stream = static_cast<cudaStream_t>(stream); d.prof = g_prof;
     d.prefetch_weights = prefetch_weights;
-    d.dyn_ctr = c->decode_dyn_words + size_t(ring) * (kDecodeDynSlabs + 1); d.dyn_cnt = d.dyn_ctr + 1;
-    d.dyn_partials = c->decode_dyn_partials + size_t(ring) * kDecodeDynFloats; d.dyn_partial_floats = kDecodeDynFloats; d.dyn_max_slabs = kDecodeDynSlabs;
     TKB_CUDA(launch_decode(d));
     return TKB_OK;
 }
@@ -366,13 +355,12 @@ int tkb_device_status(void* stream, int* status) {
     TKB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (*status) {
         TKB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
-        // A kernel that gave up may have left its stream-K bookkeeping half way (flags raised, counters not put back): start
+        // A kernel that gave up may have left its stream-K bookkeeping half way (flags raised and not put back): start
         // the skinny-M scratch from zero again.  The caller has just synchronised its stream; other streams' calls in flight
         // at this moment belong to the same failed state.
         if (c->decode_flags) {
             TKB_CUDA(cudaDeviceSynchronize());
             TKB_CUDA(cudaMemset(c->decode_flags, 0, kDecodeRing * kDecodeMaxGrid * sizeof(unsigned int)));
-            TKB_CUDA(cudaMemset(c->decode_dyn_words, 0, kDecodeRing * (kDecodeDynSlabs + 1) * sizeof(unsigned int)));
         }
     }
     return TKB_OK;

@@ -47,19 +47,13 @@ struct DecodeParams {
     const float* sgX; const float* sgW;
     __nv_bfloat16* D; int64_t ldd;
     int M, N, K;
-    float* partials;            // [grid][NB][128] fp32: tail segments of the static phase
+    float* partials;            // [grid][NB][128] fp32
     unsigned int* flags;        // [grid]
     unsigned int epoch;
     int* status;
     unsigned long long* prof;   // optional (tkb_gemm_set_profile_buffer): 8 words per CTA, see decode_kernel
     long long wait_limit;       // clock cycles any wait of the kernel may last
     int prefetch_weights;       // the weights were complete before the previous kernel in the stream started: load them before the dependency wait
-    // dynamic phase (dyn_slabs == 0: off): the last dyn_slabs weight slabs are cut into dyn_split K-parts each and handed out
-    // through an atomic counter, so that SMs that stream faster take more of them
-    int dyn_slabs, dyn_split;
-    unsigned int* dyn_ctr;      // zeroed work counter; the last claim of a launch puts it back to zero
-    unsigned int* dyn_cnt;      // [dyn_slabs] zeroed arrival counters; the CTA that completes a slab puts its counter back
-    float* dyn_partials;        // [dyn_slabs][dyn_split][NB][128] fp32
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -92,11 +86,9 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
 }
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// A segment: K-blocks [kb0, kb1) of one 128-row weight slab.  unit < 0: a segment of the static phase (the CTA's contiguous
-// share of the first slabs); unit >= 0: part `unit % split` of slab `first dynamic slab + unit / split`.
-struct Segment { int slab, kb0, kb1, unit; };
+struct Segment { int slab, kb0, kb1; };
 
-// Static phase: work range of CTA g and iteration over its segments (identical in every role).
+// Work range of CTA g and iteration over its segments (identical in every role).
 struct WorkRange {
     long long item, end; int kblk;
     __device__ WorkRange(int g, int grid, int slabs, int kblk_) : kblk(kblk_) {
@@ -110,16 +102,10 @@ struct WorkRange {
         s.kb0 = int(item % kblk);
         const long long left = end - item;
         s.kb1 = int(min((long long)kblk, s.kb0 + left));
-        s.unit = -1;
         item += s.kb1 - s.kb0;
         return true;
     }
 };
-__device__ __forceinline__ Segment dyn_segment(int unit, int static_slabs, int split, int kblk) {
-    const int part = unit % split;
-    return Segment{static_slabs + unit / split, part * kblk / split, (part + 1) * kblk / split, unit};
-}
-constexpr int DQ = 4;      // depth of the queue through which the producer hands claimed units to the other roles
 
 template <int NB>
 __global__ void __launch_bounds__(DecodeCfg<NB>::THREADS, 1)
@@ -131,20 +117,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     __shared__ __align__(8) uint64_t bar_empty[C::STAGES];
     __shared__ __align__(8) uint64_t bar_acc_full[2];
     __shared__ __align__(8) uint64_t bar_acc_empty[2];
-    __shared__ __align__(8) uint64_t bar_dq_full[DQ];
-    __shared__ __align__(8) uint64_t bar_dq_empty[DQ];
-    __shared__ int s_dq[DQ];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_flag_ok;
-    __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // profile words of this CTA (global nanosecond timer): [0] CTA start, [1] producer past the dependency wait, [2] first
     // stage landed, [3] last MMA issued, [4] epilogue finished, [5] ns the epilogue waited for other CTAs' partial tiles,
-    // [6] ns the MMA thread waited for operands, [7] dynamic units this CTA processed
+    // [6] ns the MMA thread waited for operands, [7] SM id
     unsigned long long* prof = p.prof ? p.prof + size_t(blockIdx.x) * 8 : nullptr;
-    if (prof && threadIdx.x == 0) prof[0] = global_ns();
+    if (prof && threadIdx.x == 0) {
+        prof[0] = global_ns();
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        prof[7] = smid;
+    }
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sW = smem_base;
     const uint32_t sX = sW + C::STAGES * C::W_BYTES;
@@ -153,14 +140,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
     const int slabs = (p.N + 127) / 128;
     const int kblk = (p.K + 255) / 256;
-    const int static_slabs = slabs - p.dyn_slabs;
-    const int dyn_units = p.dyn_slabs * p.dyn_split;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < C::STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
         for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), 4); }
-        for (int q = 0; q < DQ; q++) { mbar_init(smem_u32(&bar_dq_full[q]), 1); mbar_init(smem_u32(&bar_dq_empty[q]), 5); }   // MMA thread + 4 epilogue warps
         fence_mbar_init();
         prefetch_tensormap(&tmW); prefetch_tensormap(&tmX); prefetch_tensormap(&tmSW); prefetch_tensormap(&tmSX);
     }
@@ -186,7 +170,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             // before the wait.
             int prefetched = 0;
             if (p.prefetch_weights) {
-                WorkRange wr(blockIdx.x, gridDim.x, static_slabs, kblk);
+                WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
                 Segment sg;
                 while (prefetched < C::STAGES && wr.next(sg))
                     for (int kb = sg.kb0; kb < sg.kb1 && prefetched < C::STAGES; kb++, prefetched++) {
@@ -198,12 +182,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             if (prof) prof[1] = global_ns();
+            WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+            Segment sg;
             int item = 0;
-            auto load_segment = [&](const Segment& sg) {
+            while (ok && wr.next(sg)) {
                 for (int kb = sg.kb0; kb < sg.kb1; kb++, item++) {
                     const uint32_t full = smem_u32(&bar_full[stage]);
                     if (item >= prefetched) {
-                        if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; return; }
+                        if (!mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1)) { ok = false; break; }
                         mbar_arrive_expect_tx(full, C::TX_BYTES);
                         tma_load_2d(sW + stage * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
                         tma_load_3d_d(sSW + stage * C::SF_BYTES, &tmSW, full, 0, kb * 4, sg.slab);
@@ -211,27 +197,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     tma_load_2d(sX + stage * C::X_BYTES, &tmX, full, kb * 128, 0);
                     tma_load_3d_d(sSX + stage * C::SF_BYTES, &tmSX, full, 0, kb * 4, 0);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                }
-            };
-            {
-                WorkRange wr(blockIdx.x, gridDim.x, static_slabs, kblk);
-                Segment sg;
-                while (ok && wr.next(sg)) load_segment(sg);
-            }
-            // dynamic phase: claim units until the counter runs past the last one; every claim, also the failing one, goes
-            // through the queue so that the other roles see the same sequence
-            if (dyn_units > 0) {
-                uint32_t qi = 0;
-                while (ok) {
-                    const unsigned int u = atomicAdd(p.dyn_ctr, 1u);
-                    if (u == unsigned(dyn_units) + gridDim.x - 1u) *reinterpret_cast<volatile unsigned int*>(p.dyn_ctr) = 0u;   // the launch's last claim
-                    const int unit = u < unsigned(dyn_units) ? int(u) : -1;
-                    if (!mbar_wait(wc, smem_u32(&bar_dq_empty[qi % DQ]), ((qi / DQ) & 1) ^ 1)) { ok = false; break; }
-                    s_dq[qi % DQ] = unit;
-                    mbar_arrive(smem_u32(&bar_dq_full[qi % DQ]));
-                    qi++;
-                    if (unit < 0) break;
-                    load_segment(dyn_segment(unit, static_slabs, p.dyn_split, kblk));
                 }
             }
             for (int s = 0; s < C::STAGES && ok; s++) {
@@ -248,19 +213,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             int seg_idx = 0;
             bool ok = true, first = true;
             unsigned long long waited = 0;
-            auto mma_segment = [&](const Segment& sg) {
+            WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+            Segment sg;
+            while (ok && wr.next(sg)) {
                 const int buf = seg_idx & 1;
-                if (!mbar_wait(wc, smem_u32(&bar_acc_empty[buf]), ((seg_idx >> 1) & 1) ^ 1)) { ok = false; return; }
+                if (!mbar_wait(wc, smem_u32(&bar_acc_empty[buf]), ((seg_idx >> 1) & 1) ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t acc_t = tmem_base + buf * C::ACC_STRIDE;
                 for (int kb = sg.kb0; kb < sg.kb1; kb++) {
                     if (prof) {
                         const unsigned long long t0 = global_ns();
-                        if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; return; }
+                        if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
                         const unsigned long long t1 = global_ns();
                         waited += t1 - t0;
                         if (first) { prof[2] = t1; first = false; }
-                    } else if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; return; }
+                    } else if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sfa_t = tmem_base + C::SF_BASE + slot * 32;
                     const uint32_t sfb_t = sfa_t + 16;
@@ -281,22 +248,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 }
                 tc_commit<1>(smem_u32(&bar_acc_full[buf]));
                 seg_idx++;
-            };
-            {
-                WorkRange wr(blockIdx.x, gridDim.x, static_slabs, kblk);
-                Segment sg;
-                while (ok && wr.next(sg)) mma_segment(sg);
-            }
-            if (dyn_units > 0) {
-                uint32_t qi = 0;
-                while (ok) {
-                    if (!mbar_wait(wc, smem_u32(&bar_dq_full[qi % DQ]), (qi / DQ) & 1)) { ok = false; break; }
-                    const int unit = s_dq[qi % DQ];
-                    mbar_arrive(smem_u32(&bar_dq_empty[qi % DQ]));
-                    qi++;
-                    if (unit < 0) break;
-                    mma_segment(dyn_segment(unit, static_slabs, p.dyn_split, kblk));
-                }
             }
             if (prof) { prof[3] = global_ns(); prof[6] = waited; }
         }
@@ -307,29 +258,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int n_local = quarter * 32 + lane;           // weight row inside the slab
         asm volatile("griddepcontrol.wait;" ::: "memory");   // the activation scale comes from the previous kernel; D / scratch may still be read by it
         const float alpha = __fmul_rn(*p.sgX, *p.sgW);
-        int seg_idx = 0, dyn_count = 0;
+        int seg_idx = 0;
         bool ok = true;
-        // bf16 results of one chunk of accumulator columns (= activation rows c0 .. c0 + CHUNK) for weight row n
-        auto store_rows = [&](const float (&v)[C::CHUNK], int c0, int n) {
-            if (n < p.N) {
-#pragma unroll
-                for (int i = 0; i < C::CHUNK; i++)
-                    if (c0 + i < p.M) p.D[int64_t(c0 + i) * p.ldd + n] = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
-            }
-        };
-        auto epilogue_segment = [&](const Segment& sg) {
+        WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
+        Segment sg;
+        while (ok && wr.next(sg)) {
             const int buf = seg_idx & 1;
-            if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; return; }
+            if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
-            const bool dyn = sg.unit >= 0;
             const bool head = sg.kb0 == 0;
-            const bool complete = head && sg.kb1 == kblk;          // the whole K range of the slab in one segment: no partial tiles
-            const bool static_head = !complete && !dyn && head, static_tail = !complete && !dyn && !head, dyn_part = !complete && dyn;
+            const bool complete = head && sg.kb1 == kblk;
             const int n = sg.slab * 128 + n_local;
-            // Static phase, incomplete head: which CTAs hold the rest of this slab?
+            // Which CTAs hold the rest of this slab (only meaningful for an incomplete head)?
             int contrib_lo = 0, contrib_hi = 0;
-            if (static_head) {
-                const long long items = (long long)static_slabs * kblk;
+            if (head && !complete) {
+                const long long items = (long long)slabs * kblk;
                 const long long slab_end = (long long)(sg.slab + 1) * kblk;
                 contrib_lo = int(blockIdx.x) + 1;
                 contrib_hi = contrib_lo;
@@ -355,8 +298,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 epi_barrier();
                 if (!s_flag_ok) ok = false;
             }
-            float* part_dst = static_tail ? p.partials + size_t(blockIdx.x) * NB * 128 + n_local
-                                          : (dyn_part ? p.dyn_partials + size_t(sg.unit) * NB * 128 + n_local : nullptr);
 #pragma unroll
             for (int c0 = 0; c0 < NB; c0 += C::CHUNK) {
                 float v[C::CHUNK];
@@ -379,28 +320,33 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
                 }
-                if (part_dst != nullptr) {
+                if (!head) {
+                    float* dst = p.partials + (size_t(blockIdx.x) * NB + c0) * 128 + n_local;
 #pragma unroll
-                    for (int i = 0; i < C::CHUNK; i++) __stcg(part_dst + (c0 + i) * 128, v[i]);
+                    for (int i = 0; i < C::CHUNK; i++) __stcg(dst + i * 128, v[i]);
                 } else {
-                    if (static_head && ok) {
+                    if (!complete && ok) {
                         for (int h = contrib_lo; h < contrib_hi; h++) {
                             const float* src = p.partials + (size_t(h) * NB + c0) * 128 + n_local;
 #pragma unroll
                             for (int i = 0; i < C::CHUNK; i++) v[i] += __ldcg(src + i * 128);
                         }
                     }
-                    store_rows(v, c0, n);
+                    if (n < p.N) {
+#pragma unroll
+                        for (int i = 0; i < C::CHUNK; i++)
+                            if (c0 + i < p.M) p.D[int64_t(c0 + i) * p.ldd + n] = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
+                    }
                 }
             }
-            if (static_head) {
+            if (head && !complete) {
                 // every epilogue thread has read the partial tiles: put the contributors' flags back to 0 so that a
                 // later launch that carries the same epoch (a replayed CUDA graph) does not mistake them for fresh
                 epi_barrier();
                 if (threadIdx.x == 64)
                     for (int h = contrib_lo; h < contrib_hi; h++) st_release_gpu(p.flags + h, 0u);
             }
-            if (static_tail) {
+            if (!head) {
                 // publish the partial tile: all four epilogue warps have stored, then one release
                 epi_barrier();
                 if (threadIdx.x == 64) {
@@ -408,57 +354,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     st_release_gpu(p.flags + blockIdx.x, p.epoch);
                 }
             }
-            if (dyn_part) {
-                // The CTA that brings a slab's arrival counter to `split` adds the parts up, always in part order, so the
-                // result does not depend on which CTA that is or on the order in which the parts arrived.
-                const int slab2 = sg.unit / p.dyn_split;
-                epi_barrier();
-                if (threadIdx.x == 64) {
-                    __threadfence();
-                    const unsigned int old = atomicAdd(p.dyn_cnt + slab2, 1u);
-                    const int last = old == unsigned(p.dyn_split) - 1u;
-                    if (last) *reinterpret_cast<volatile unsigned int*>(p.dyn_cnt + slab2) = 0u;      // ready for the next launch
-                    s_last = last;
-                }
-                epi_barrier();
-                if (s_last) {
-                    __threadfence();
-                    const float* base = p.dyn_partials + size_t(slab2) * p.dyn_split * NB * 128 + n_local;
-#pragma unroll
-                    for (int c0 = 0; c0 < NB; c0 += C::CHUNK) {
-                        float v[C::CHUNK];
-#pragma unroll
-                        for (int i = 0; i < C::CHUNK; i++) v[i] = __ldcg(base + (c0 + i) * 128);
-                        for (int part = 1; part < p.dyn_split; part++) {
-                            const float* src = base + size_t(part) * NB * 128;
-#pragma unroll
-                            for (int i = 0; i < C::CHUNK; i++) v[i] += __ldcg(src + (c0 + i) * 128);
-                        }
-                        store_rows(v, c0, n);
-                    }
-                }
-            }
             seg_idx++;
-        };
-        {
-            WorkRange wr(blockIdx.x, gridDim.x, static_slabs, kblk);
-            Segment sg;
-            while (ok && wr.next(sg)) epilogue_segment(sg);
         }
-        if (dyn_units > 0) {
-            uint32_t qi = 0;
-            while (ok) {
-                if (!mbar_wait(wc, smem_u32(&bar_dq_full[qi % DQ]), (qi / DQ) & 1)) { ok = false; break; }
-                const int unit = s_dq[qi % DQ];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_dq_empty[qi % DQ]));
-                qi++;
-                if (unit < 0) break;
-                epilogue_segment(dyn_segment(unit, static_slabs, p.dyn_split, kblk));
-                dyn_count++;
-            }
-        }
-        if (prof && threadIdx.x == 64) { prof[4] = global_ns(); prof[7] = (unsigned long long)dyn_count; }
+        if (prof && threadIdx.x == 64) prof[4] = global_ns();
         __syncwarp();
     }
 
@@ -488,24 +386,7 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     if (grid > a.max_grid) grid = a.max_grid;
     if (grid > items) grid = int(items);
     if (grid < 1) grid = 1;
-    // Dynamic phase: the last ~fifth of the slabs, cut into K-parts of a few blocks, is handed out through a counter (see
-    // DecodeParams).  It needs zeroed counters and room for the parts' fp32 tiles; without them everything is static.
-    const int slabs = (a.N + 127) / 128, kblk = (a.K + 255) / 256;
-    static const int dyn_pct_env = getenv("TKB_DECODE_DYN_PCT") ? atoi(getenv("TKB_DECODE_DYN_PCT")) : -1;
-    static const int dyn_split_env = getenv("TKB_DECODE_DYN_SPLIT") ? atoi(getenv("TKB_DECODE_DYN_SPLIT")) : 0;
-    int dyn_slabs = 0, dyn_split = 1;
-    if (a.dyn_ctr != nullptr && a.dyn_cnt != nullptr && a.dyn_partials != nullptr && items >= 8LL * grid) {
-        const int pct = dyn_pct_env >= 0 ? (dyn_pct_env > 100 ? 100 : dyn_pct_env) : 20;
-        dyn_split = dyn_split_env > 0 ? dyn_split_env : (NB <= 32 ? 8 : 4);
-        if (dyn_split > kblk) dyn_split = kblk;
-        dyn_slabs = int((long long)slabs * pct / 100);
-        const long long per_slab = (long long)dyn_split * NB * 128;
-        if (dyn_slabs > a.dyn_max_slabs) dyn_slabs = a.dyn_max_slabs;
-        if ((long long)dyn_slabs * per_slab > (long long)a.dyn_partial_floats) dyn_slabs = int((long long)a.dyn_partial_floats / per_slab);
-        if (dyn_split < 2) dyn_slabs = 0;
-    }
-    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof,
-                   api_wait_limit(), a.prefetch_weights, dyn_slabs, dyn_split, a.dyn_ctr, a.dyn_cnt, a.dyn_partials};
+    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights};
     CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
     void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
     (void)params;

@@ -18,7 +18,9 @@
 //   * warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2.. = epilogue.
 //   * Scale factors travel shared memory -> tensor memory with tcgen05.cp right before the MMAs
 //     that use them, into one of four rotating slots next to the accumulator.
-//   * The accumulator is single-buffered (256 fp32 columns + scale slots do not leave room for two):
+//   * Two accumulators where tensor memory has room for them next to the scale slots (the dense kinds and
+//     every kind with the 128-wide N tile): the epilogue of a tile overlaps the MMAs of the next.  The
+//     block-scaled kinds with the 256-wide tile have one (256 fp32 columns + scale slots leave no room):
 //     the epilogue first drains it into registers as packed bf16, hands TMEM back to the MMA warp,
 //     and only then writes D, so the stores overlap the next tile's main loop.  Each epilogue warp
 //     owns a private 4 KB staging box (32 rows x 64 columns, 128-byte swizzle) and issues its own
@@ -63,7 +65,11 @@ struct GemmCfg {
     static constexpr int SFB_COLS = SF_CHUNKS * 4 * (BN / 128);
     static constexpr int SF_SLOTS = 4;
     static constexpr int TMEM_COLS = 512;
-    static_assert(BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS, "tensor memory overflow");
+    // two accumulators where they fit next to the scale slots (dense kinds, or N tile 128): the epilogue of tile i then overlaps
+    // the MMAs of tile i + 1; otherwise one
+    static constexpr int ACC_BUFS = (2 * BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS) ? 2 : 1;
+    static constexpr int SF_BASE = ACC_BUFS * BN;
+    static_assert(ACC_BUFS * BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS, "tensor memory overflow");
     static_assert(STAGES >= 3, "not enough pipeline stages");
     static constexpr uint32_t TX_BYTES = CTAS * STAGE_BYTES;
 };
@@ -364,8 +370,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[C::STAGES];
     __shared__ __align__(8) uint64_t bar_empty[C::STAGES];
-    __shared__ __align__(8) uint64_t bar_tmem_full;
-    __shared__ __align__(8) uint64_t bar_tmem_empty;
+    __shared__ __align__(8) uint64_t bar_tmem_full[2];
+    __shared__ __align__(8) uint64_t bar_tmem_empty[2];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : 1];   // comm CTAs of the MoE / all-gather modes
@@ -398,8 +404,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < C::STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-        mbar_init(smem_u32(&bar_tmem_full), 1);
-        mbar_init(smem_u32(&bar_tmem_empty), CTAS * C::EPI_WARPS);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[b]), CTAS * C::EPI_WARPS);
+        }
         fence_mbar_init();
         prefetch_tensormap(&tmA); prefetch_tensormap(&tmB); prefetch_tensormap(&tmD);
         if (SCALED) { prefetch_tensormap(&tmSA); prefetch_tensormap(&tmSB); }
@@ -526,21 +534,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer ------------
         if (is_leader && elect_one()) {
-            uint32_t stage = 0, phase = 0, tile_phase = 0, slot = 0;
+            uint32_t stage = 0, phase = 0, tile_count = 0, slot = 0;
             bool ok = true;
             long long wait_acc = 0, wait_full = 0;
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 { const long long t0 = clock64();
-                  if (!mbar_wait(wc, smem_u32(&bar_tmem_empty), tile_phase ^ 1)) { ok = false; break; }
+                  if (!mbar_wait(wc, smem_u32(&bar_tmem_empty[tile_count % C::ACC_BUFS]), ((tile_count / C::ACC_BUFS) & 1u) ^ 1u)) { ok = false; break; }
                   wait_acc += clock64() - t0; }
                 tc_fence_after();
+                const uint32_t acc_t = tmem_base + (tile_count % C::ACC_BUFS) * BN;
                 for (int kb = 0; kb < num_kb; kb++) {
                     { const long long t0 = clock64();
                       if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
                       wait_full += clock64() - t0; }
                     tc_fence_after();
-                    const uint32_t sfa_t = tmem_base + BN + slot * (C::SFA_COLS + C::SFB_COLS);
+                    const uint32_t sfa_t = tmem_base + C::SF_BASE + slot * (C::SFA_COLS + C::SFB_COLS);
                     const uint32_t sfb_t = sfa_t + C::SFA_COLS;
                     if constexpr (SCALED) {
 #pragma unroll
@@ -559,13 +568,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
                         // +32 bytes of K inside the 128-byte swizzle panel = +2 in the (addr >> 4) field
                         if constexpr (KIND == KIND_BF16) {
-                            mma_f16<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::BM, BN), acc);
+                            mma_f16<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::BM, BN), acc);
                         } else if constexpr (KIND == KIND_FP8) {
-                            mma_f8<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_fp8(C::BM, BN), acc);
+                            mma_f8<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_fp8(C::BM, BN), acc);
                         } else if constexpr (KIND == KIND_MXFP8) {
-                            mma_mxfp8<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::BM, BN, j), acc, sfa_t, sfb_t);
+                            mma_mxfp8<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::BM, BN, j), acc, sfa_t, sfb_t);
                         } else {
-                            mma_nvfp4<CTAS>(tmem_base, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(C::BM, BN), acc, sfa_t + 4 * j,
+                            mma_nvfp4<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(C::BM, BN), acc, sfa_t + 4 * j,
                                             sfb_t + (BN / 128) * 4 * j);
                         }
                     }
@@ -573,8 +582,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                     slot = (slot + 1) % C::SF_SLOTS;
                 }
-                tc_commit<CTAS>(smem_u32(&bar_tmem_full));               // accumulator complete (both CTAs)
-                tile_phase ^= 1;
+                tc_commit<CTAS>(smem_u32(&bar_tmem_full[tile_count % C::ACC_BUFS]));     // accumulator complete (both CTAs)
+                tile_count++;
             }
             if (p.prof) { p.prof[blockIdx.x * 8 + 2] = wait_acc; p.prof[blockIdx.x * 8 + 3] = wait_full; p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin; }
         }
@@ -600,30 +609,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (blockIdx.x == 0 && warp == 2 && lane == 0) *p.q_sg = q_sg_dec;
         }
         (void)q_sg_dec; (void)q_sg_enc;
-        const uint32_t tmem_empty_leader = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty), 0) : smem_u32(&bar_tmem_empty);
+        const uint32_t tmem_empty_leader0 = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty[0]), 0) : smem_u32(&bar_tmem_empty[0]);
+        const uint32_t tmem_empty_leader1 = CTAS == 2 ? mapa(smem_u32(&bar_tmem_empty[1]), 0) : smem_u32(&bar_tmem_empty[1]);
         const uint32_t stage_box = sEpi + ew * C::EPI_WARP_BYTES;
         const uint64_t d_policy = l2_policy_evict_first();     // D is written once and never read here: keep the operands in L2 instead
-        uint32_t tile_phase = 0;
+        uint32_t tile_count = 0;
         bool ok = true;
         long long wait_tf = 0, drain = 0;
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
             int m_blk, n_blk;
             tile_to_block(tile, tiles_m, tiles_n, tile_group, tile_rot, m_blk, n_blk);
             const long long t0 = clock64();
-            if (!mbar_wait(wc, smem_u32(&bar_tmem_full), tile_phase)) { ok = false; break; }
+            const uint32_t buf = tile_count % C::ACC_BUFS;
+            if (!mbar_wait(wc, smem_u32(&bar_tmem_full[buf]), (tile_count / C::ACC_BUFS) & 1u)) { ok = false; break; }
             const long long t1 = clock64();
             wait_tf += t1 - t0;
-            tile_phase ^= 1;
+            tile_count++;
             tc_fence_after();
             // Drain: both halves of this warp's 128 accumulator columns are requested back to back and only waited
             // for once; tensor memory goes back to the MMA warp before any arithmetic on the values.
             uint32_t r0[64], r1[64];
-            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base, r0);
-            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + col_base + 64, r1);
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + col_base, r0);
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + col_base + 64, r1);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
+                const uint32_t tmem_empty_leader = buf ? tmem_empty_leader1 : tmem_empty_leader0;
                 if constexpr (CTAS == 2) mbar_arrive_cluster(tmem_empty_leader); else mbar_arrive(tmem_empty_leader);
             }
             uint32_t packed[C::COLS_PER_EPI_WARP / 2];

@@ -85,9 +85,6 @@ struct DecodeArgs {
     int* status; int sm_count; cudaStream_t stream;
     unsigned long long* prof;   // optional per-CTA timeline, 8 x uint64 per CTA
     int prefetch_weights;       // TKB_GEMM_SKINNY_PREFETCH
-    // optional scratch of the dynamic phase (all null: static schedule only): a zeroed work counter, dyn_max_slabs zeroed slab
-    // counters, room for dyn_partial_floats floats of partial tiles
-    unsigned int* dyn_ctr; unsigned int* dyn_cnt; float* dyn_partials; size_t dyn_partial_floats; int dyn_max_slabs;
 };
 cudaError_t launch_decode(const DecodeArgs& a);
 int decode_padded_rows(int M);

@@ -135,7 +135,18 @@ cudaError_t launch_absmax(const void* A, int64_t lda, int M, int K, unsigned int
 cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64_t ldc, void* sc, int M, int K, int sm_count,
                                   cudaStream_t s) {
     const int tiles = ((M + QT_ROWS - 1) / QT_ROWS) * ((K + QT_COLS - 1) / QT_COLS);
-    int grid = sm_count * 8 < tiles ? sm_count * 8 : tiles;
+    // a persistent grid of exactly the CTAs that are resident at once: with more, the second batch of CTAs starts when the first
+    // ends and the tiles no longer divide evenly (8 CTAs per SM over 4096 tiles: 3 or 4 tiles per CTA, two batches = 8 tile
+    // times for 6.9 tiles' worth of work per resident slot)
+    static int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        int b = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, mxfp8_quantize_kernel, Q_THREADS, 0) != cudaSuccess || b < 1) b = 4;
+        blocks_per_sm = b > 8 ? 8 : b;
+    }
+    static const int bps_env = getenv("TKB_MXQ_BLOCKS_PER_SM") ? atoi(getenv("TKB_MXQ_BLOCKS_PER_SM")) : 0;
+    const int per_sm = bps_env > 0 ? bps_env : blocks_per_sm;
+    int grid = sm_count * per_sm < tiles ? sm_count * per_sm : tiles;
     mxfp8_quantize_kernel<<<grid < 1 ? 1 : grid, Q_THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(A), lda,
                                                                   static_cast<uint8_t*>(codes), ldc, static_cast<uint8_t*>(sc), M, K);
     return cudaGetLastError();

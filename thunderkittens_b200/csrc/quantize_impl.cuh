@@ -283,7 +283,8 @@ inline cudaError_t launch_nvfp4_quantize_t(const NvQuantArgs& a) {
         if (e != cudaSuccess) return e;
         blocks_per_sm = b < 1 ? 1 : (b > 4 ? 4 : b);
     }
-    int grid = a.sm_count * blocks_per_sm;
+    static const int bps_env = getenv("TKB_NVQ_BLOCKS_PER_SM") ? atoi(getenv("TKB_NVQ_BLOCKS_PER_SM")) : 0;     // tuning aid; must not exceed what is resident
+    int grid = a.sm_count * (bps_env > 0 && bps_env <= blocks_per_sm ? bps_env : blocks_per_sm);
     if (grid > tiles) grid = tiles;
     if (grid < 1) grid = 1;
     if (RESIDENT) {

@@ -384,3 +384,78 @@ def tk_all_to_all(output: TKParallelTensor, input: TKParallelTensor, barrier: TK
     dims = (C.c_longlong * 4)(*input.shape_)
     L.check(L.lib().tkb_all_to_all_4d(output.peer_ptr_array(), input.data_.data_ptr(), dims, input.data_.element_size(), scatter_axis, gather_axis,
                                       r, w, barrier.peer_ptr_array(), 0, epoch, _stream()))
+
+
+class MoEDispatchGemmState:
+    """Buffers behind `moe_dispatch_gemm` (takes the place of the reference's `barrier` tensor): the quantized tokens of
+    every rank (two alternating sets, symmetric), the amax exchange slots, the epoch flags, and this rank's operand
+    staging for up to `cap_rows` dispatched rows."""
+
+    def __init__(self, tokens_per_rank: int, H: int, I: int, experts_local: int, cap_rows: int, local_rank: int, local_world_size: int, group=None):
+        w, r = local_world_size, local_rank
+        if H % 256 or I % 128 or cap_rows % 128:
+            raise RuntimeError("need H % 256 == 0, I % 128 == 0 and cap_rows % 128 == 0")
+        self.Tl, self.H, self.I, self.El, self.cap_rows, self.rank, self.world, self.group = tokens_per_rank, H, I, experts_local, cap_rows, r, w, group
+        mk = lambda shape, dt: TKParallelTensor(shape, dt, r, w, False, group)
+        self.xq_rows = [mk((tokens_per_rank, H // 2 + H // 16), torch.uint8) for _ in range(2)]
+        self.slots = [mk((w,), torch.int64) for _ in range(2)]
+        self.flags = mk((3 * w,), torch.int32)          # [0, w) tokens quantized, [2w, 3w) call finished
+        dev = self.flags.data_.device
+        self.codes = torch.zeros(cap_rows, H // 2, dtype=torch.uint8, device=dev)
+        self.scales = torch.zeros(cap_rows // 128, H // 64, 512, dtype=torch.uint8, device=dev)
+        self.block_expert = torch.zeros(cap_rows // 128, dtype=torch.int32, device=dev)
+        self.num_blocks = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.arrived = torch.zeros(cap_rows // 128, dtype=torch.int32, device=dev)
+        self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.arithmetic = L.NVFP4_KERNEL_FAST
+        self.epoch = 0
+        if w > 1:
+            dist.barrier(group=group)
+
+    def close(self) -> None:
+        for t in self.xq_rows + self.slots + [self.flags]:
+            t.close()
+
+
+def moe_dispatch_gemm(pre_tokens: TKParallelTensor, post_tokens, weights, outputs: torch.Tensor, padded_tokens_per_expert: torch.Tensor,
+                      pull_dispatch_indices: torch.Tensor, barrier: MoEDispatchGemmState, num_comm_sms: int, num_padded_local_tokens: int) -> None:
+    """The reference's entry (kernels/parallel/moe_dispatch_gemm/moe_dispatch_gemm_h100.cu:260-299) with its argument list and
+    its host-built schedule: `padded_tokens_per_expert` int32[E] over ALL experts, `pull_dispatch_indices` int32[rows, 2] of
+    (source rank, source row) per row of this rank's expert segments, (-1, -1) for padding (benchmark.py:112-149).
+    Differences, all on the data side: `weights` is this rank's stacked expert weights as the NVFP4 triple (codes
+    [E_local * I, H/2], scales, per-tensor scale) instead of a bf16 [E_local, H, I] tensor; the tokens of `pre_tokens`
+    (bf16 [T/world, H], this rank's rows) are quantized to NVFP4 with the amax of all ranks before they travel;
+    `post_tokens` (the reference's bf16 gather buffer) is not used and may be None; `barrier` is the state object above.
+    outputs [num_padded_local_tokens, I] bf16.  num_comm_sms == 0 dispatches with the gather kernel on all SMs."""
+    st = barrier
+    lib, s = L.lib(), _stream()
+    w, r = st.world, st.rank
+    W, W_sc, W_sg = weights
+    rows = int(num_padded_local_tokens)
+    if rows % 128 or rows > st.cap_rows or rows < 128:
+        raise RuntimeError("num_padded_local_tokens must be a positive multiple of 128 within the state's cap_rows")
+    if tuple(outputs.shape) != (rows, st.I) or outputs.dtype != torch.bfloat16 or not outputs.is_contiguous():
+        raise RuntimeError("outputs must be a contiguous bf16 tensor of shape (num_padded_local_tokens, I)")
+    if pull_dispatch_indices.dtype != torch.int32 or tuple(pull_dispatch_indices.shape) != (rows, 2) or not pull_dispatch_indices.is_contiguous():
+        raise RuntimeError("pull_dispatch_indices must be a contiguous int32 tensor of shape (num_padded_local_tokens, 2)")
+    X = pre_tokens.data_
+    st.epoch += 1
+    e, b = st.epoch, st.epoch % 2
+    fl = st.flags.data_.data_ptr()
+    # the token set of parity b was last read by the peers' kernels of call e - 2
+    if w > 1 and e > 2:
+        L.check(lib.tkb_wait_flags(fl + 4 * 2 * w, w, r, e - 2, s))
+    # local expert of every 128-row block, from the padded counts of this rank's experts (no host synchronisation)
+    local = padded_tokens_per_expert[r * st.El:(r + 1) * st.El].to(torch.int64) // 128
+    st.block_expert[:rows // 128] = torch.repeat_interleave(torch.arange(st.El, device=local.device, dtype=torch.int32), local, output_size=rows // 128)
+    st.num_blocks.fill_(rows // 128)
+    L.check(lib.tkb_nvfp4_quantize_sharded(X.data_ptr(), 0, st.xq_rows[b].data_.data_ptr(), None, st.sg.data_ptr(), st.Tl, st.H, 1, st.arithmetic,
+                                           st.slots[b].peer_ptr_array(), w, r, e, s))
+    if w > 1:
+        L.check(lib.tkb_signal_peers(st.flags.peer_ptr_array(), w, r, r, e, 0, s))
+    L.check(lib.tkb_moe_dispatch_gemm(st.xq_rows[b].peer_ptr_array(), st.sg.data_ptr(), st.codes.data_ptr(), st.scales.data_ptr(), W.data_ptr(),
+                                      W_sc.data_ptr(), W_sg.data_ptr(), outputs.data_ptr(), 0, pull_dispatch_indices.data_ptr(),
+                                      st.block_expert.data_ptr(), st.num_blocks.data_ptr(), fl, st.arrived.data_ptr(), e, st.H, st.I, st.El,
+                                      rows, r, w, num_comm_sms, s))
+    if w > 1:
+        L.check(lib.tkb_signal_peers(st.flags.peer_ptr_array(), w, r, 2 * w + r, e, 0, s))       # done with the peers' tokens of this call
