@@ -294,6 +294,28 @@ int tkb_ag_graph_create(const tkb_ag_state* st, unsigned int first_epoch, int st
 int tkb_ag_graph_launch(void* handle, void* stream);
 int tkb_ag_graph_destroy(void* handle);
 
+/* GEMM + reduce-scatter, NVFP4: the row-parallel partner of the all-gather GEMM.  Replaces gemm_rs / matmul_reduce_scatter
+ * (kernels/parallel/gemm_rs/gemm_rs_b200.cu:77-200, entry 204-233; bf16 and fp8 operands there).  Every rank holds a K-slice
+ * of both operands, A_r [M, K_local] and B_r [N, K_local] (NVFP4, each quantized on its own: the per-tensor scales are applied
+ * per rank), and ends up with its M / world rows of D = sum_r A_r . B_r^T as bf16.  As in the reference, the partial tiles are
+ * converted to bf16 and ADDED into the owner's rows by the memory system (cp.reduce.async.bulk.tensor ... add, over NVLink for
+ * remote owners), so the sum over the ranks is a bf16 accumulation whose order is not fixed: results agree with an fp32 sum to
+ * about 1e-2 relative, not bit for bit.  st->out[i]: rank i's output [M / world, N] bf16 (symmetric buffer), st->flags[i]:
+ * rank i's 2 * world zeroed 32-bit epochs, st->maps: from tkb_rs_maps_create (tensor maps of all outputs, in device memory).
+ * A call zeroes the rank's rows, exchanges flags (nobody adds before everybody has zeroed), multiplies, exchanges flags again
+ * (the rows are complete when every rank's kernel has finished); epoch grows by one per call on every rank alike.
+ * M % (256 * world) == 0, N % 8 == 0, K_local % 64 == 0. */
+typedef struct tkb_rs_state {
+    int rank, world, M, N;
+    void* out[8];
+    void* flags[8];
+    void* maps;
+} tkb_rs_state;
+int tkb_rs_maps_create(const tkb_rs_state* st, void** device_maps);
+int tkb_rs_maps_destroy(void* device_maps);
+int tkb_gemm_rs_nvfp4(const tkb_rs_state* st, unsigned int epoch, const void* A, const void* A_sc, const float* A_sg, const void* B,
+                      const void* B_sc, const float* B_sg, int K_local, void* stream);
+
 /* ---- MoE layer -----------------------------------------------------------------------------------
  * Replaces moe_dispatch_gemm(pre_tokens, post_tokens, weights, outputs, padded_tokens_per_expert,
  * pull_dispatch_indices, barrier, num_comm_sms, num_padded_local_tokens)
@@ -357,7 +379,7 @@ typedef struct tkb_moe_state {
 int tkb_moe_layer_nvfp4(const tkb_moe_state* st, unsigned int epoch, const float* logits_local, const void* X_local_bf16, const void* W,
                         const void* W_sc, const float* W_sg, void* out, int comm_ctas, int arithmetic, void* stream);
 
-/* For bindings that mirror the state structs by hand (ctypes, cgo, JNI ...): which = 0 tkb_ag_state, 1 tkb_moe_state;
+/* For bindings that mirror the state structs by hand (ctypes, cgo, JNI ...): which = 0 tkb_ag_state, 1 tkb_moe_state, 2 tkb_rs_state;
  * field 0 = sizeof, field i >= 1 = offsetof the i-th member in declaration order; -1 past the last member.  Host only. */
 int tkb_debug_struct_layout(int which, int field);
 

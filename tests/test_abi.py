@@ -52,7 +52,7 @@ def test_ctypes_mirrors_of_the_state_structs_match_the_header(lib):
     f = lib.tkb_debug_struct_layout
     f.argtypes = [ctypes.c_int, ctypes.c_int]
     f.restype = ctypes.c_int
-    for which, mirror in ((0, _lib.AgState), (1, _lib.MoeState)):
+    for which, mirror in ((0, _lib.AgState), (1, _lib.MoeState), (2, _lib.RsState)):
         assert f(which, 0) == ctypes.sizeof(mirror)
         for i, (name, *_rest) in enumerate(mirror._fields_, start=1):
             assert f(which, i) == getattr(mirror, name).offset, (mirror.__name__, name)

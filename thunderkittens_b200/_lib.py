@@ -51,6 +51,9 @@ _SIGNATURES = {
     "tkb_amax_allreduce": ([C.POINTER(_vp), _i, _i, C.c_uint, _vp, _vp, _vp], _i),
     "tkb_all_to_all": ([C.POINTER(_vp), _vp, _sz, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
     "tkb_all_to_all_4d": ([C.POINTER(_vp), _vp, C.POINTER(C.c_longlong), _i, _i, _i, _i, _i, C.POINTER(_vp), _i, C.c_uint, _vp], _i),
+    "tkb_rs_maps_create": ([_vp, C.POINTER(_vp)], _i),
+    "tkb_rs_maps_destroy": ([_vp], _i),
+    "tkb_gemm_rs_nvfp4": ([_vp, C.c_uint, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
     "tkb_ag_copy_create": ([_i, _i, C.POINTER(_vp)], _i),
     "tkb_ag_copy_destroy": ([_vp], _i),
     "tkb_ag_graph_create": ([_vp, C.c_uint, _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i64, _i, _i,
@@ -81,6 +84,11 @@ class AgState(C.Structure):
                 ("codes", (_vp * 8) * 2), ("scales", (_vp * 8) * 2), ("arrived", (_vp * 8) * 2), ("slots", (_vp * 8) * 2),
                 ("done", _vp * 8), ("amax", _vp), ("sg", _vp), ("exit_counter", _vp),
                 ("copy", _vp), ("epoch_counter", _vp)]
+
+
+class RsState(C.Structure):
+    """Mirror of tkb_rs_state (include/tkb200.h)."""
+    _fields_ = [("rank", _i), ("world", _i), ("M", _i), ("N", _i), ("out", _vp * 8), ("flags", _vp * 8), ("maps", _vp)]
 
 
 class MoeState(C.Structure):

@@ -185,6 +185,24 @@ static int pick_config(int config, int M, int N, int sm_count) {
     return 2;
 }
 
+// bf16 output map: box 64 columns x 32 rows, 128-byte swizzle (one epilogue warp's staging box)
+int api_make_output_map(CUtensorMap* m, void* D, int rows, int cols, int64_t ldd) {
+    cuuint64_t dims[2] = {uint64_t(cols), uint64_t(rows)};
+    cuuint64_t strides[1] = {uint64_t(ldd) * 2};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
+    return TKB_OK;
+}
+
+// NVFP4 A operand (codes + chunked scales) over M rows, for callers whose A has more rows than the output map they pass
+int api_make_operand_a_maps(GemmArgs* gp, const void* A, const void* A_sc, int M, int K) {
+    if (int e = make_operand_map(&gp->tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(K / 2), M, K / 2, 128)) return e;
+    return make_scale_map(&gp->tmSA, A_sc, (M + 127) / 128, K / 64, 4);
+}
+
 // Tensor maps of one GEMM call (g->kind / g->config already set).
 int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K) {
@@ -204,15 +222,7 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
     } else {
         g.tmSA = g.tmA; g.tmSB = g.tmB;
     }
-    {
-        cuuint64_t dims[2] = {uint64_t(N), uint64_t(M)};
-        cuuint64_t strides[1] = {uint64_t(ldd) * 2};
-        cuuint32_t box[2] = {64, 32};
-        cuuint32_t estr[2] = {1, 1};
-        CUresult r = g_encode(&g.tmD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with CUresult %d", int(r));
-    }
+    if (int e = api_make_output_map(&g.tmD, D, M, N, ldd)) return e;
     return TKB_OK;
 }
 

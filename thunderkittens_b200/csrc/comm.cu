@@ -27,6 +27,8 @@ int api_quantize_sharded(const void* A_bf16, int64_t lda, void* codes, void* sc,
                          const unsigned int* epoch_ptr, void* stream);   // api.cu
 int api_make_gemm_maps(GemmArgs* g, int kind, const void* A, int64_t lda_bytes, const void* A_sc, const void* B, int64_t ldb_bytes,
                        const void* B_sc, void* D, int64_t ldd, int M, int N, int K);   // api.cu
+int api_make_output_map(CUtensorMap* m, void* D, int rows, int cols, int64_t ldd);     // api.cu: bf16 [rows, cols], box 64 x 32, 128-byte swizzle
+int api_make_operand_a_maps(GemmArgs* g, const void* A, const void* A_sc, int M, int K);   // api.cu: NVFP4 A operand + scales over M rows
 
 struct PeerPtrs { unsigned int* p[kMaxWorld]; };
 constexpr int kAllToAll4dMaxGrid = 592;   // CTAs of tkb_all_to_all_4d at most (part of its counter protocol)
@@ -363,6 +365,15 @@ int tkb_debug_struct_layout(int which, int field) {
             default: return -1;
         }
     }
+    if (which == 2) {
+        if (field == 0) return int(sizeof(tkb_rs_state));
+        enum { base = __COUNTER__ };
+        switch (field) {
+            TKB_OFF(tkb_rs_state, rank) TKB_OFF(tkb_rs_state, world) TKB_OFF(tkb_rs_state, M) TKB_OFF(tkb_rs_state, N)
+            TKB_OFF(tkb_rs_state, out) TKB_OFF(tkb_rs_state, flags) TKB_OFF(tkb_rs_state, maps)
+            default: return -1;
+        }
+    }
     if (which == 1) {
         if (field == 0) return int(sizeof(tkb_moe_state));
         enum { base = __COUNTER__ };
@@ -399,6 +410,68 @@ int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int 
         n++;
     }
     return n;
+}
+
+// ---- GEMM + reduce-scatter (row-parallel partner of the all-gather GEMM) ------------------------------------------------
+int tkb_rs_maps_create(const tkb_rs_state* st, void** device_maps) {
+    if (!st || !device_maps) return api_fail(TKB_ERR_INVALID_ARG, "rs_maps_create: null pointer");
+    const int w = st->world;
+    if (w < 1 || w > kMaxWorld || st->M < 1 || st->M % (256 * w) || st->N < 8 || st->N % 8)
+        return api_fail(TKB_ERR_INVALID_ARG, "rs_maps_create: need world 1..%d, M %% (256 * world) == 0, N %% 8 == 0", kMaxWorld);
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    CUtensorMap maps[kMaxWorld];
+    memset(maps, 0, sizeof(maps));
+    for (int i = 0; i < w; i++) {
+        if (!st->out[i]) return api_fail(TKB_ERR_INVALID_ARG, "rs_maps_create: null output buffer of rank %d", i);
+        if (int e = api_make_output_map(&maps[i], st->out[i], st->M / w, st->N, st->N)) return e;
+    }
+    void* dev = nullptr;
+    TKB_CUDA_C(cudaMalloc(&dev, sizeof(maps)));
+    cudaError_t ce = cudaMemcpy(dev, maps, sizeof(maps), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) { cudaFree(dev); return api_fail(TKB_ERR_CUDA, "rs_maps_create: %s", cudaGetErrorString(ce)); }
+    *device_maps = dev;
+    return TKB_OK;
+}
+int tkb_rs_maps_destroy(void* device_maps) {
+    if (device_maps) TKB_CUDA_C(cudaFree(device_maps));
+    return TKB_OK;
+}
+
+int tkb_gemm_rs_nvfp4(const tkb_rs_state* st, unsigned int epoch, const void* A, const void* A_sc, const float* A_sg, const void* B,
+                      const void* B_sc, const float* B_sg, int K_local, void* stream) {
+    if (!st || !A || !A_sc || !A_sg || !B || !B_sc || !B_sg || epoch == 0) return api_fail(TKB_ERR_INVALID_ARG, "gemm_rs: null pointer or epoch 0");
+    const int w = st->world, r = st->rank;
+    if (w < 1 || w > kMaxWorld || r < 0 || r >= w || st->M % (256 * w) || st->N % 8 || !st->maps)
+        return api_fail(TKB_ERR_INVALID_ARG, "gemm_rs: bad world / rank / M / N, or no tensor maps (tkb_rs_maps_create)");
+    if (K_local < 64 || K_local % 64) return api_fail(TKB_ERR_INVALID_ARG, "gemm_rs: K_local must be a positive multiple of 64");
+    int sm; int* status;
+    if (int e = api_device(&sm, &status)) return e;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int rows = st->M / w;
+    // 1. this rank's output rows start from zero; nobody may add into them before that (first flag exchange)
+    TKB_CUDA_C(cudaMemsetAsync(st->out[r], 0, size_t(rows) * st->N * 2, s));
+    if (w > 1) {
+        if (int e = tkb_signal_peers(st->flags, w, r, r, epoch, 0, s)) return e;
+        if (int e = tkb_wait_flags(st->flags[r], w, r, epoch, s)) return e;
+    }
+    // 2. the GEMM; every 32 x 64 box of bf16 results is added into the owner's rows by the memory system
+    GemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.kind = KIND_NVFP4; g.config = 0;
+    if (int e = api_make_gemm_maps(&g, KIND_NVFP4, A, K_local / 2, A_sc, B, K_local / 2, B_sc, st->out[r], st->N, rows, st->N, K_local)) return e;
+    // (the output map built above only serves as a valid descriptor: this mode stores through rs_maps)
+    if (int e = api_make_operand_a_maps(&g, A, A_sc, st->M, K_local)) return e;
+    g.sgA = A_sg; g.sgB = B_sg; g.M = st->M; g.N = st->N; g.K = K_local; g.status = status; g.sm_count = sm; g.stream = s;
+    g.mode = MODE_RS;
+    g.rs_maps = static_cast<const CUtensorMap*>(st->maps); g.rs_rows_per_rank = rows; g.rs_rank = r; g.rs_world = w;
+    TKB_CUDA_C(launch_gemm(g));
+    // 3. the rows are complete when every rank's kernel has finished (second flag exchange)
+    if (w > 1) {
+        if (int e = tkb_signal_peers(st->flags, w, r, w + r, epoch, 0, s)) return e;
+        if (int e = tkb_wait_flags(static_cast<unsigned int*>(st->flags[r]) + w, w, r, epoch, s)) return e;
+    }
+    return TKB_OK;
 }
 
 // Streams, events and the arrival-flag pattern of the copy-engine gather (tkb_ag_copy_create).

@@ -54,6 +54,7 @@ struct DecodeParams {
     unsigned long long* prof;   // optional (tkb_gemm_set_profile_buffer): 8 words per CTA, see decode_kernel
     long long wait_limit;       // clock cycles any wait of the kernel may last
     int prefetch_weights;       // the weights were complete before the previous kernel in the stream started: load them before the dependency wait
+    int stages;                 // operand-ring stages to use (clamped to what the instance has)
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -124,14 +125,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // profile words of this CTA (global nanosecond timer): [0] CTA start, [1] producer past the dependency wait, [2] first
     // stage landed, [3] last MMA issued, [4] epilogue finished, [5] ns the epilogue waited for other CTAs' partial tiles,
-    // [6] ns the MMA thread waited for operands, [7] SM id
+    // [6] ns the MMA thread waited for operands, [7] ns the epilogue spent on its segments after their accumulators were complete
     unsigned long long* prof = p.prof ? p.prof + size_t(blockIdx.x) * 8 : nullptr;
-    if (prof && threadIdx.x == 0) {
-        prof[0] = global_ns();
-        unsigned int smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        prof[7] = smid;
-    }
+    if (prof && threadIdx.x == 0) prof[0] = global_ns();
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sW = smem_base;
     const uint32_t sX = sW + C::STAGES * C::W_BYTES;
@@ -140,6 +136,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
     const int slabs = (p.N + 127) / 128;
     const int kblk = (p.K + 255) / 256;
+    // stages of the operand ring in use: fewer than fit spreads the start-up burst (every SM filling its whole ring at once
+    // queues ~180 KB per SM in the memory system, and the SMs served last stay that far behind to the end)
+    const int nst = p.stages < 3 ? 3 : (p.stages > C::STAGES ? C::STAGES : p.stages);
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -172,8 +171,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if (p.prefetch_weights) {
                 WorkRange wr(blockIdx.x, gridDim.x, slabs, kblk);
                 Segment sg;
-                while (prefetched < C::STAGES && wr.next(sg))
-                    for (int kb = sg.kb0; kb < sg.kb1 && prefetched < C::STAGES; kb++, prefetched++) {
+                while (prefetched < nst && wr.next(sg))
+                    for (int kb = sg.kb0; kb < sg.kb1 && prefetched < nst; kb++, prefetched++) {
                         const uint32_t full = smem_u32(&bar_full[prefetched]);
                         mbar_arrive_expect_tx(full, C::TX_BYTES);
                         tma_load_2d(sW + prefetched * C::W_BYTES, &tmW, full, kb * 128, sg.slab * 128);
@@ -196,14 +195,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     }
                     tma_load_2d(sX + stage * C::X_BYTES, &tmX, full, kb * 128, 0);
                     tma_load_3d_d(sSX + stage * C::SF_BYTES, &tmSX, full, 0, kb * 4, 0);
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == uint32_t(nst)) { stage = 0; phase ^= 1; }
                 }
             }
-            for (int s = 0; s < C::STAGES && ok; s++) {
+            for (int s = 0; s < nst && ok; s++) {
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == uint32_t(nst)) { stage = 0; phase ^= 1; }
             }
-            if (!ok) drain_ring(bar_full, C::STAGES, uint32_t(item > prefetched ? item : prefetched), p.wait_limit);   // giving up: let the issued copies land
+            if (!ok) drain_ring(bar_full, nst, uint32_t(item > prefetched ? item : prefetched), p.wait_limit);   // giving up: let the issued copies land
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -243,7 +242,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         mma_nvfp4<1>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(128, NB), (kb > sg.kb0 || j > 0) ? 1u : 0u,
                                      sfa_t + 4 * j, sfb_t + 4 * j);
                     tc_commit<1>(smem_u32(&bar_empty[stage]));
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == uint32_t(nst)) { stage = 0; phase ^= 1; }
                     slot = (slot + 1) % C::SF_SLOTS;
                 }
                 tc_commit<1>(smem_u32(&bar_acc_full[buf]));
@@ -266,6 +265,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             const int buf = seg_idx & 1;
             if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
+            const unsigned long long t_seg = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
             const bool head = sg.kb0 == 0;
             const bool complete = head && sg.kb1 == kblk;
             const int n = sg.slab * 128 + n_local;
@@ -354,6 +354,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     st_release_gpu(p.flags + blockIdx.x, p.epoch);
                 }
             }
+            if (prof && threadIdx.x == 64) prof[7] += global_ns() - t_seg;
             seg_idx++;
         }
         if (prof && threadIdx.x == 64) prof[4] = global_ns();
@@ -386,7 +387,9 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     if (grid > a.max_grid) grid = a.max_grid;
     if (grid > items) grid = int(items);
     if (grid < 1) grid = 1;
-    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights};
+    static const int stages_env = getenv("TKB_DECODE_STAGES") ? atoi(getenv("TKB_DECODE_STAGES")) : 0;      // tuning aid
+    const int stages = stages_env > 0 ? stages_env : C::STAGES;
+    DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights, stages};
     CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
     void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
     (void)params;

@@ -78,11 +78,14 @@ struct GemmParams {
     const float* sgA; const float* sgB;
     int M, N, K;
     int group;                  // row blocks that share a sweep over the columns
+    int rot;                    // row block at which the tile order starts (reduce-scatter mode)
     int* status;
     unsigned long long* prof;   // optional: per-CTA wait-cycle counters (see tkb_gemm_set_profile_buffer)
     long long wait_limit;       // clock cycles any wait of the kernel may last
     // quantizing epilogue (MODE_QUANT): the bf16 result is quantized to NVFP4 before it leaves the SM
     uint8_t* q_codes; uint8_t* q_sc; float* q_sg; const float* q_amax; int q_arith;
+    // reduce-scatter epilogue (MODE_RS): tensor maps (device memory) of every rank's output rows, rows per rank
+    const CUtensorMap* rs_maps; int rs_rows;
 };
 
 // NVFP4 quantization of one 16-value block held as 8 packed bf16 pairs, with the IEEE arithmetic of the standalone
@@ -399,7 +402,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int first_tile = (CTAS == 2 ? int(cluster_id_x()) : int(blockIdx.x)) - comm_units;
     const int tile_stride = (CTAS == 2 ? int(num_clusters_x()) : int(gridDim.x)) - comm_units;
     const int tile_group = AG ? ag.blocks_per_rank : (MOE ? 1 : p.group);
-    const int tile_rot = AG ? ag.rank * ag.blocks_per_rank : 0;
+    const int tile_rot = AG ? ag.rank * ag.blocks_per_rank : p.rot;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -686,7 +689,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0 && row0 < p.M && col0 + 64 * h < p.N) {
-                    tma_store_2d_hint(&tmD, stage_box, col0 + 64 * h, row0, d_policy);
+                    if constexpr (MODE == MODE_RS) {
+                        // the rank that owns these 32 rows adds the box to its output (over NVLink unless it is this rank)
+                        const int owner = row0 / p.rs_rows;
+                        tma_reduce_add_2d(p.rs_maps + owner, stage_box, col0 + 64 * h, row0 - owner * p.rs_rows);
+                    } else {
+                        tma_store_2d_hint(&tmD, stage_box, col0 + 64 * h, row0, d_policy);
+                    }
                     tma_store_commit();
                 }
             }
@@ -744,8 +753,13 @@ static cudaError_t launch_t(const GemmArgs& a) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
     static const int group_env = getenv("TKB_GEMM_GROUP") ? atoi(getenv("TKB_GEMM_GROUP")) : 0;
-    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, a.status, a.prof, api_wait_limit(),
-                 static_cast<uint8_t*>(a.q_codes), static_cast<uint8_t*>(a.q_sc), a.q_sg, a.q_amax, a.q_arith};
+    GemmParams p{a.sgA, a.sgB, a.M, a.N, a.K, group_env > 0 ? group_env : 16, 0, a.status, a.prof, api_wait_limit(),
+                 static_cast<uint8_t*>(a.q_codes), static_cast<uint8_t*>(a.q_sc), a.q_sg, a.q_amax, a.q_arith, a.rs_maps, a.rs_rows_per_rank};
+    if (MODE == MODE_RS && a.rs_world > 0) {
+        // start with the rows of the next rank, so that the ranks do not all add into the same owner at the same time
+        p.group = a.rs_rows_per_rank / C::BM;
+        p.rot = ((a.rs_rank + 1) % a.rs_world) * p.group;
+    }
     return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmB, a.tmSA, a.tmSB, a.tmD, p, a.comm);
 }
 
@@ -774,6 +788,7 @@ int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
 cudaError_t launch_gemm(const GemmArgs& a) {
     if (a.mode == MODE_AG) return launch_t<KIND_NVFP4, 2, 256, MODE_AG>(a);
     if (a.mode == MODE_QUANT) return launch_t<KIND_NVFP4, 2, 256, MODE_QUANT>(a);
+    if (a.mode == MODE_RS) return launch_t<KIND_NVFP4, 2, 256, MODE_RS>(a);
     if (a.mode == MODE_MOE) return launch_t<KIND_NVFP4, 1, 256, MODE_MOE>(a);
     switch (a.kind) {
         case KIND_BF16: return launch_k<KIND_BF16>(a);

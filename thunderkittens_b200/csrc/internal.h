@@ -52,7 +52,7 @@ struct MoeParams {
     unsigned int epoch;
     int rank, world, comm_ctas, expert_rows; // expert_rows = rows of one expert's weight matrix (the GEMM's N)
 };
-enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2, MODE_QUANT = 4 };   // QUANT: the epilogue writes D as NVFP4
+enum GemmMode : int { MODE_PLAIN = 0, MODE_AG = 1, MODE_MOE = 2, MODE_QUANT = 4, MODE_RS = 8 };   // QUANT: the epilogue writes D as NVFP4; RS: reduce-scatter
 struct CommParams { AgParams ag; MoeParams moe; };
 
 struct GemmArgs {
@@ -69,6 +69,9 @@ struct GemmArgs {
     CommParams comm;
     // MODE_QUANT: D leaves the kernel as NVFP4 codes + chunked scales quantized with a caller-supplied amax
     void* q_codes; void* q_sc; float* q_sg; const float* q_amax; int q_arith;   // q_arith: 0 = spec association, 1 = kernel association (IEEE)
+    // MODE_RS: the bf16 tiles are reduce-added into the output of the rank that owns their rows.  rs_maps: `rs_world` tensor maps in
+    // DEVICE memory, map i over rank i's output [M / world, N] bf16 (box 64 x 32, 128-byte swizzle, as tmD); rs_rank rotates the tile order
+    const CUtensorMap* rs_maps; int rs_rows_per_rank, rs_rank, rs_world;
 };
 cudaError_t launch_gemm(const GemmArgs& a);
 int moe_dispatch_ring(int K);     // row slots the MoE dispatch ring gets for hidden size K (needs >= 24)

@@ -167,6 +167,13 @@ __device__ __forceinline__ void tma_store_2d_hint(const void* map, uint32_t src,
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "l"(policy)
                  : "memory");
 }
+// Tiled reduce-add of a shared-memory box into global memory (possibly another GPU's): element-wise add in the tensor map's
+// data type, performed by the memory system; completion is tracked like a store (bulk group).
+__device__ __forceinline__ void tma_reduce_add_2d(const void* map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }

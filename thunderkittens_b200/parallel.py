@@ -459,3 +459,46 @@ def moe_dispatch_gemm(pre_tokens: TKParallelTensor, post_tokens, weights, output
                                       rows, r, w, num_comm_sms, s))
     if w > 1:
         L.check(lib.tkb_signal_peers(st.flags.peer_ptr_array(), w, r, 2 * w + r, e, 0, s))       # done with the peers' tokens of this call
+
+
+class GemmReduceScatterNVFP4:
+    """Row-parallel linear layer with NVFP4 operands (the partner of AllGatherMatmulNVFP4; mirrors the reference's
+    matmul_reduce_scatter, kernels/parallel/gemm_rs/gemm_rs_b200.cu:204-233): every rank holds a K-slice of the activations
+    [M, K/world] and of the weights [N, K/world], both NVFP4, and receives rows [rank * M/world, (rank+1) * M/world) of their
+    product summed over the ranks.  `out` is this rank's bf16 [M/world, N] result, valid after a call in stream order."""
+
+    def __init__(self, M: int, N: int, local_rank: int, local_world_size: int, group=None):
+        w = local_world_size
+        if M % (256 * w) or N % 8:
+            raise RuntimeError("M must be a multiple of 256 * world size and N of 8")
+        self.M, self.N, self.rank, self.world = M, N, local_rank, w
+        self._out = TKParallelTensor((M // w, N), torch.bfloat16, local_rank, w, False, group)
+        self._flags = TKParallelTensor((2 * w,), torch.int32, local_rank, w, False, group)
+        self.out = self._out.data_
+        st = L.RsState()
+        st.rank, st.world, st.M, st.N = local_rank, w, M, N
+        for i in range(w):
+            st.out[i] = self._out.peer_ptr(i); st.flags[i] = self._flags.peer_ptr(i)
+        maps = C.c_void_p()
+        L.check(L.lib().tkb_rs_maps_create(C.byref(st), C.byref(maps)))
+        st.maps = maps.value
+        self._state, self._maps, self.epoch = st, maps.value, 0
+        if w > 1:
+            dist.barrier(group=group)
+
+    def __call__(self, A, A_sc, A_sg, B, B_sc, B_sg) -> torch.Tensor:
+        k_local = A.shape[1] * 2
+        if A.shape[0] != self.M or B.shape[0] != self.N or B.shape[1] != A.shape[1]:
+            raise RuntimeError("A must be [M, K_local/2] and B [N, K_local/2] packed NVFP4 codes")
+        self.epoch += 1
+        L.check(L.lib().tkb_gemm_rs_nvfp4(C.byref(self._state), self.epoch, A.data_ptr(), A_sc.data_ptr(), A_sg.data_ptr(), B.data_ptr(),
+                                          B_sc.data_ptr(), B_sg.data_ptr(), k_local, _stream()))
+        return self.out
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        if self._maps is not None:
+            L.lib().tkb_rs_maps_destroy(self._maps)
+            self._maps = None
+        self.out = None
+        self._out.close(); self._flags.close()
