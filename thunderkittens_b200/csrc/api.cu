@@ -127,6 +127,19 @@ static int make_scale_map(CUtensorMap* m, const void* base, uint64_t row_blocks,
     return TKB_OK;
 }
 
+// 2-D map over a bf16 matrix for the quantizers' TMA ring: box = one 128 x 128 tile, rows 256 bytes apart in shared memory
+// (no swizzle).  Rows and columns past the matrix read as zeros.
+static int make_tile_map_bf16(CUtensorMap* m, const void* A, int64_t lda, int M, int K) {
+    cuuint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+    cuuint64_t strides[1] = {uint64_t(lda) * 2};
+    cuuint32_t box[2] = {128, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(tile) failed with CUresult %d", int(r));
+    return TKB_OK;
+}
+
 static int ensure_decode_scratch(DeviceCtx* c) {
     if (c->decode_partials) return TKB_OK;
     std::lock_guard<std::mutex> lk(g_ctx_mu);
@@ -419,7 +432,9 @@ int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, i
     if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
-    TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
+    CUtensorMap tile_map;
+    if (int e = make_tile_map_bf16(&tile_map, A_bf16, lda, M, K)) return e;
+    TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream), &tile_map, c->status));
     return TKB_OK;
 }
 
