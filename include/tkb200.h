@@ -53,10 +53,12 @@ enum {
     TKB_GEMM_PAIR_N128 = 3,    /* two-CTA 256 x 128 tiles */
     TKB_GEMM_SINGLE_N128 = 4,  /* one-CTA 128 x 128 tiles */
     TKB_GEMM_SKINNY = 5,       /* NVFP4, M <= 128: weight-streaming stream-K kernel (the default for such M) */
-    TKB_GEMM_SKINNY_PREFETCH = 6 /* the same kernel for STATIC weights: the caller states that B, B_sc were complete before the
+    TKB_GEMM_SKINNY_PREFETCH = 6, /* the same kernel for STATIC weights: the caller states that B, B_sc were complete before the
                                   kernel that precedes this call in the stream started (weights quantized ahead of time), so
                                   the kernel may load them while that kernel (typically the activation quantizer) still runs.
                                   With any other config nothing is read before the preceding kernel has finished. */
+    TKB_GEMM_PAIR_M512_N256 = 7 /* dense kinds (bf16, fp8) only: two-CTA 512 x 256 tiles, two 128-row halves of A per CTA against the
+                                  same B rows (the default for these kinds once the tiles fill the GPU) */
 };
 
 int tkb_version(void);

@@ -21,3 +21,16 @@ def test_fp8_gemm_matches_oracle(cuda, lib, M, N, K, cfg):
     ops.fp8_gemm(torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda), D, cfg)
     torch.cuda.synchronize()
     _check(bf16_bits(D), O.fp8_gemm(A, B), f"fp8 {M}x{N}x{K} {cfg}")
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 512, 512), (600, 264, 272), (2048, 2048, 1024)])
+def test_fp8_gemm_tall_tile(cuda, lib, M, N, K):
+    """The 512 x 256 cluster tile of the dense kinds (two 128-row halves of A per CTA), forced, including ragged edges."""
+    import thunderkittens_b200.ops as ops
+    rng = np.random.default_rng(M + N + K + 1)
+    A = O.f32_to_e4m3(rng.standard_normal((M, K)).astype(np.float32))
+    B = O.f32_to_e4m3((rng.standard_normal((N, K)) * 0.5).astype(np.float32))
+    D = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda)
+    ops.fp8_gemm(torch.from_numpy(A).to(cuda), torch.from_numpy(B).to(cuda), D, "pair_m512_n256")
+    torch.cuda.synchronize()
+    _check(bf16_bits(D), O.fp8_gemm(A, B), f"fp8 tall {M}x{N}x{K}")

@@ -72,7 +72,7 @@ def test_mxfp8_gemm_vs_oracle(cuda, lib, config, M, N, K):
     _check(bf16_bits(D), O.mxfp8_gemm(ac, asc, bc, bsc), f"mxfp8 {M}x{N}x{K} {config}")
 
 
-@pytest.mark.parametrize("config", CONFIGS)
+@pytest.mark.parametrize("config", CONFIGS + ["pair_m512_n256"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 256, 1024), (512, 768, 2048), (130, 200, 72), (1024, 1024, 1024)])
 def test_bf16_gemm_vs_oracle(cuda, lib, config, M, N, K):
     ops = _ops()

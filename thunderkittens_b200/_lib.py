@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libtkb200.so")
 
 OK, ERR_INVALID_ARG, ERR_BAD_ALIGNMENT, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_CAPACITY = range(7)
 NVFP4_SPEC, NVFP4_KERNEL_IEEE, NVFP4_KERNEL_FAST = 0, 1, 2
-GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY, GEMM_SKINNY_PREFETCH = range(7)
+GEMM_DEFAULT, GEMM_PAIR_N256, GEMM_SINGLE_N256, GEMM_PAIR_N128, GEMM_SINGLE_N128, GEMM_SKINNY, GEMM_SKINNY_PREFETCH, GEMM_PAIR_M512_N256 = range(8)
 
 
 class TkbError(RuntimeError):

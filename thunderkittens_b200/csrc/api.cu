@@ -127,19 +127,6 @@ static int make_scale_map(CUtensorMap* m, const void* base, uint64_t row_blocks,
     return TKB_OK;
 }
 
-// 2-D map over a bf16 matrix for the quantizers' TMA ring: box = one 128 x 128 tile, rows 256 bytes apart in shared memory
-// (no swizzle).  Rows and columns past the matrix read as zeros.
-static int make_tile_map_bf16(CUtensorMap* m, const void* A, int64_t lda, int M, int K) {
-    cuuint64_t dims[2] = {uint64_t(K), uint64_t(M)};
-    cuuint64_t strides[1] = {uint64_t(lda) * 2};
-    cuuint32_t box[2] = {128, 128};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(tile) failed with CUresult %d", int(r));
-    return TKB_OK;
-}
-
 static int ensure_decode_scratch(DeviceCtx* c) {
     if (c->decode_partials) return TKB_OK;
     std::lock_guard<std::mutex> lk(g_ctx_mu);
@@ -190,8 +177,12 @@ static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const fl
     return TKB_OK;
 }
 
-static int pick_config(int config, int M, int N, int sm_count) {
+static int pick_config(int kind, int config, int M, int N, int sm_count) {
+    const bool dense = kind == KIND_BF16 || kind == KIND_FP8;
+    if (config == TKB_GEMM_PAIR_M512_N256) return 4;
     if (config >= TKB_GEMM_PAIR_N256 && config <= TKB_GEMM_SINGLE_N128) return config - 1;
+    // dense kinds: 512 x 256 cluster tiles (two 128-row halves of A per CTA) once they fill two waves of CTA pairs
+    if (dense && long((M + 511) / 512) * ((N + 255) / 256) >= sm_count) return 4;
     // default: CTA pairs; 256-wide N tiles unless that leaves most of the SMs without a tile
     const long tiles256 = long((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 * 2 >= sm_count || (N % 256 == 0 && tiles256 * 4 >= sm_count)) return 0;
@@ -225,7 +216,7 @@ int api_make_gemm_maps(GemmArgs* gp, int kind, const void* A, int64_t lda_bytes,
     const int elem_bytes = kind == KIND_BF16 ? 2 : 1;
     const CUtensorMapDataType dt = kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const uint64_t inner = kind == KIND_NVFP4 ? uint64_t(K / 2) : uint64_t(K);
-    if (int e = make_operand_map(&g.tmA, A, dt, elem_bytes, inner, M, lda_bytes, 128)) return e;
+    if (int e = make_operand_map(&g.tmA, A, dt, elem_bytes, inner, M, lda_bytes, (g.config & 4) ? 256 : 128)) return e;
     if (int e = make_operand_map(&g.tmB, B, dt, elem_bytes, inner, N, ldb_bytes, bn / ctas)) return e;
     if (kind == KIND_NVFP4 || kind == KIND_MXFP8) {
         const int kc = kind == KIND_NVFP4 ? K / 64 : K / 128;
@@ -275,7 +266,9 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
     // pure argument errors first: they are reported the same way with or without a device
     if (!A || !B || !D) return api_fail(TKB_ERR_INVALID_ARG, "gemm: null operand pointer");
     if (M < 1 || N < 1 || K < 1) return api_fail(TKB_ERR_INVALID_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
-    if (config < 0 || config > TKB_GEMM_SKINNY_PREFETCH) return api_fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
+    if (config < 0 || config > TKB_GEMM_PAIR_M512_N256) return api_fail(TKB_ERR_INVALID_ARG, "gemm: unknown config %d", config);
+    if (config == TKB_GEMM_PAIR_M512_N256 && kind != KIND_BF16 && kind != KIND_FP8)
+        return api_fail(TKB_ERR_INVALID_ARG, "gemm: the 512 x 256 tile exists for the dense kinds only (the block-scaled kinds need the tensor memory for their scales)");
     if ((config == TKB_GEMM_SKINNY || config == TKB_GEMM_SKINNY_PREFETCH) && (kind != KIND_NVFP4 || M > 128))
         return api_fail(TKB_ERR_INVALID_ARG, "gemm: the skinny-M kernel needs NVFP4 operands and M <= 128");
     const int kmult = kind == KIND_NVFP4 ? 64 : (kind == KIND_MXFP8 ? 128 : (kind == KIND_FP8 ? 16 : 8));
@@ -299,7 +292,7 @@ static int gemm_common(int kind, const void* A, int64_t lda_bytes, const void* A
     GemmArgs g;
     memset(&g, 0, sizeof(g));
     g.kind = kind;
-    g.config = pick_config(config, M, N, c->sm_count);
+    g.config = pick_config(kind, config, M, N, c->sm_count);
     if (int e = api_make_gemm_maps(&g, kind, A, lda_bytes, A_sc, B, ldb_bytes, B_sc, D, ldd, M, N, K)) return e;
     g.sgA = A_sg; g.sgB = B_sg; g.M = M; g.N = N; g.K = K;
     g.status = c->status; g.prof = g_prof; g.sm_count = c->sm_count; g.stream = static_cast<cudaStream_t>(stream);
@@ -432,9 +425,7 @@ int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, i
     if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
-    CUtensorMap tile_map;
-    if (int e = make_tile_map_bf16(&tile_map, A_bf16, lda, M, K)) return e;
-    TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream), &tile_map, c->status));
+    TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
     return TKB_OK;
 }
 
@@ -510,7 +501,7 @@ int tkb_fp8_gemm_ex(const void* A, int64_t lda, const void* B, int64_t ldb, void
     if (lda == 0) lda = K;
     if (ldb == 0) ldb = K;
     if (lda < K || ldb < K) return api_fail(TKB_ERR_INVALID_ARG, "fp8_gemm: lda/ldb must be >= K");
-    if (config >= TKB_GEMM_SKINNY) return api_fail(TKB_ERR_INVALID_ARG, "fp8_gemm: no skinny-M kernel for this format");
+    if (config == TKB_GEMM_SKINNY || config == TKB_GEMM_SKINNY_PREFETCH) return api_fail(TKB_ERR_INVALID_ARG, "fp8_gemm: no skinny-M kernel for this format");
     return gemm_common(KIND_FP8, A, lda, nullptr, nullptr, B, ldb, nullptr, nullptr, D, ldd, M, N, K, config, stream);
 }
 int tkb_fp8_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K, void* stream) {

@@ -126,7 +126,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // profile words of this CTA (global nanosecond timer): [0] CTA start, [1] producer past the dependency wait, [2] first
     // stage landed, [3] last MMA issued, [4] epilogue finished, [5] ns the epilogue waited for other CTAs' partial tiles,
     // [6] ns the MMA thread waited for operands, [7] ns the epilogue spent on its segments after their accumulators were complete
-    unsigned long long* prof = p.prof ? p.prof + size_t(blockIdx.x) * 8 : nullptr;
+    unsigned long long* prof = p.prof ? p.prof + size_t(blockIdx.x) * 16 : nullptr;      // ([8] tensor-memory reads, [9] partial-tile
+    // stores and their publication, [10] stores of D, [11] segments: epilogue thread 64, ns)
     if (prof && threadIdx.x == 0) prof[0] = global_ns();
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sW = smem_base;
@@ -263,13 +264,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         Segment sg;
         while (ok && wr.next(sg)) {
             const int buf = seg_idx & 1;
-            if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
-            tc_fence_after();
-            const unsigned long long t_seg = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
             const bool head = sg.kb0 == 0;
             const bool complete = head && sg.kb1 == kblk;
             const int n = sg.slab * 128 + n_local;
-            // Which CTAs hold the rest of this slab (only meaningful for an incomplete head)?
+            // An incomplete head adds the partial tiles of the CTAs that hold the rest of its slab.  Those CTAs met that slab
+            // first thing, so their tiles are normally there long before this segment's own MMAs end: wait for their flags and
+            // fetch the tiles into registers (summed in CTA order) BEFORE waiting for the accumulator, so that the round trip
+            // to L2 overlaps the main loop instead of following it.
+            float psum[NB];
             int contrib_lo = 0, contrib_hi = 0;
             if (head && !complete) {
                 const long long items = (long long)slabs * kblk;
@@ -277,7 +279,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 contrib_lo = int(blockIdx.x) + 1;
                 contrib_hi = contrib_lo;
                 while (contrib_hi < int(gridDim.x) && items * contrib_hi / gridDim.x < slab_end) contrib_hi++;
-                // wait for their partial tiles
                 if (threadIdx.x == 64) {
                     int good = 1;
                     const unsigned long long tw0 = prof ? global_ns() : 0ull;
@@ -297,10 +298,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 }
                 epi_barrier();
                 if (!s_flag_ok) ok = false;
+#pragma unroll
+                for (int c = 0; c < NB; c++) psum[c] = 0.f;
+                if (ok) {
+                    for (int h = contrib_lo; h < contrib_hi; h++) {
+                        const float* src = p.partials + size_t(h) * NB * 128 + n_local;
+#pragma unroll
+                        for (int c = 0; c < NB; c++) psum[c] += __ldcg(src + c * 128);
+                    }
+                }
             }
+            if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned long long t_seg = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
 #pragma unroll
             for (int c0 = 0; c0 < NB; c0 += C::CHUNK) {
                 float v[C::CHUNK];
+                const unsigned long long t_c0 = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
                 if constexpr (C::CHUNK == 32) {
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * C::ACC_STRIDE + c0, r);
@@ -314,6 +328,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
                     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
                 }
+                const unsigned long long t_ld = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
+                if (prof && threadIdx.x == 64) prof[8] += t_ld - t_c0;
                 if (c0 + C::CHUNK >= NB) {
                     // last chunk read: the accumulator buffer can be reused
                     tc_fence_before();
@@ -324,19 +340,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     float* dst = p.partials + (size_t(blockIdx.x) * NB + c0) * 128 + n_local;
 #pragma unroll
                     for (int i = 0; i < C::CHUNK; i++) __stcg(dst + i * 128, v[i]);
+                    if (prof && threadIdx.x == 64) prof[9] += global_ns() - t_ld;
                 } else {
-                    if (!complete && ok) {
-                        for (int h = contrib_lo; h < contrib_hi; h++) {
-                            const float* src = p.partials + (size_t(h) * NB + c0) * 128 + n_local;
+                    if (!complete) {
 #pragma unroll
-                            for (int i = 0; i < C::CHUNK; i++) v[i] += __ldcg(src + i * 128);
-                        }
+                        for (int i = 0; i < C::CHUNK; i++) v[i] += psum[c0 + i];
                     }
                     if (n < p.N) {
 #pragma unroll
                         for (int i = 0; i < C::CHUNK; i++)
                             if (c0 + i < p.M) p.D[int64_t(c0 + i) * p.ldd + n] = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
                     }
+                    if (prof && threadIdx.x == 64) prof[10] += global_ns() - t_ld;
                 }
             }
             if (head && !complete) {
@@ -348,13 +363,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
             if (!head) {
                 // publish the partial tile: all four epilogue warps have stored, then one release
+                const unsigned long long t_pub = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
                 epi_barrier();
                 if (threadIdx.x == 64) {
                     __threadfence();
                     st_release_gpu(p.flags + blockIdx.x, p.epoch);
+                    if (prof) prof[9] += global_ns() - t_pub;
                 }
             }
-            if (prof && threadIdx.x == 64) prof[7] += global_ns() - t_seg;
+            if (prof && threadIdx.x == 64) { prof[7] += global_ns() - t_seg; prof[11] += 1; }
             seg_idx++;
         }
         if (prof && threadIdx.x == 64) prof[4] = global_ns();
@@ -388,7 +405,9 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     if (grid > items) grid = int(items);
     if (grid < 1) grid = 1;
     static const int stages_env = getenv("TKB_DECODE_STAGES") ? atoi(getenv("TKB_DECODE_STAGES")) : 0;      // tuning aid
-    const int stages = stages_env > 0 ? stages_env : C::STAGES;
+    // 6 stages (~108 KB of weights per SM) measured best: with all 10 the start-up burst queues so much that the SMs served
+    // last trail by ~4 us to the end; with 4 or fewer the HBM pipe is no longer full
+    const int stages = stages_env > 0 ? stages_env : 6;
     DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights, stages};
     CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
     void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};

@@ -38,14 +38,19 @@
 
 namespace tkb {
 
-template <int KIND, int CTAS, int BN>
+template <int KIND, int CTAS, int BN, int MH = 1>
 struct GemmCfg {
     static_assert(CTAS == 1 || CTAS == 2, "");
     static_assert(BN == 128 || BN == 256, "");
-    static constexpr int BM = 128 * CTAS;                 // rows of D per cluster tile
+    // MH = 2 (dense kinds, CTA pairs, N tile 256): every CTA carries TWO 128-row halves of A per stage against the same B rows,
+    // i.e. a 512 x 256 cluster tile with one accumulator per half: a third more FLOPs per byte that crosses from L2 into
+    // shared memory than the 256 x 256 tile, which is what bounds the dense kernels
+    static_assert(MH == 1 || (MH == 2 && CTAS == 2 && BN == 256 && (KIND == KIND_BF16 || KIND == KIND_FP8)), "");
+    static constexpr int BM = 128 * CTAS * MH;            // rows of D per cluster tile
+    static constexpr int MMA_M = 128 * CTAS;              // rows of one MMA instruction (per CTA pair)
     static constexpr int BN_CTA = BN / CTAS;              // rows of B each CTA loads
     static constexpr int KB = KIND == KIND_BF16 ? 64 : (KIND == KIND_NVFP4 ? 256 : 128);   // K elements per stage (128 bytes)
-    static constexpr int A_BYTES = 128 * 128;
+    static constexpr int A_BYTES = MH * 128 * 128;
     static constexpr int B_BYTES = BN_CTA * 128;
     static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP8 ? 1 : 0);  // 512-byte chunks per 128 rows per stage
     static constexpr int SFA_BYTES = SF_CHUNKS * 512;
@@ -67,9 +72,10 @@ struct GemmCfg {
     static constexpr int TMEM_COLS = 512;
     // two accumulators where they fit next to the scale slots (dense kinds, or N tile 128): the epilogue of tile i then overlaps
     // the MMAs of tile i + 1; otherwise one
-    static constexpr int ACC_BUFS = (2 * BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS) ? 2 : 1;
-    static constexpr int SF_BASE = ACC_BUFS * BN;
-    static_assert(ACC_BUFS * BN + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS, "tensor memory overflow");
+    static constexpr int ACC_COLS = MH * BN;              // columns of one accumulator set (half h at column h * BN)
+    static constexpr int ACC_BUFS = (2 * ACC_COLS + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS) ? 2 : 1;
+    static constexpr int SF_BASE = ACC_BUFS * ACC_COLS;
+    static_assert(ACC_BUFS * ACC_COLS + SF_SLOTS * (SFA_COLS + SFB_COLS) <= TMEM_COLS, "tensor memory overflow");
     static_assert(STAGES >= 3, "not enough pipeline stages");
     static constexpr uint32_t TX_BYTES = CTAS * STAGE_BYTES;
 };
@@ -356,12 +362,12 @@ __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc
     }
 }
 
-template <int KIND, int CTAS, int BN, int MODE>
-__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN>::THREADS, 1)
+template <int KIND, int CTAS, int BN, int MODE, int MH = 1>
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN, MH>::THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
             const __grid_constant__ CUtensorMap tmD, const GemmParams p, const CommParams cp) {
-    using C = GemmCfg<KIND, CTAS, BN>;
+    using C = GemmCfg<KIND, CTAS, BN, MH>;
     constexpr bool SCALED = KIND == KIND_NVFP4 || KIND == KIND_MXFP8;
     constexpr bool AG = MODE == MODE_AG;
     constexpr bool MOE = MODE == MODE_MOE;
@@ -466,7 +472,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
                 tile_to_block(tile, tiles_m, tiles_n, tile_group, tile_rot, m_blk, n_blk);
-                const int a_row = m_blk * C::BM + int(cta_rank) * 128;
+                const int a_row = m_blk * C::BM + int(cta_rank) * 128 * MH;
                 // MoE mode: the B operand is the weight matrix of the expert that owns this row block
                 const int expert = MOE ? moe.block_expert[m_blk] : 0;
                 const int b_row = expert * (MOE ? moe.expert_rows : 0) + n_blk * BN + int(cta_rank) * C::BN_CTA;
@@ -546,7 +552,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   if (!mbar_wait(wc, smem_u32(&bar_tmem_empty[tile_count % C::ACC_BUFS]), ((tile_count / C::ACC_BUFS) & 1u) ^ 1u)) { ok = false; break; }
                   wait_acc += clock64() - t0; }
                 tc_fence_after();
-                const uint32_t acc_t = tmem_base + (tile_count % C::ACC_BUFS) * BN;
+                const uint32_t acc_t = tmem_base + (tile_count % C::ACC_BUFS) * C::ACC_COLS;
                 for (int kb = 0; kb < num_kb; kb++) {
                     { const long long t0 = clock64();
                       if (!mbar_wait(wc, smem_u32(&bar_full[stage]), phase)) { ok = false; break; }
@@ -564,21 +570,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                                   smem_desc_scale(sSB + stage * C::SFB_BYTES + j * C::SFA_BYTES + c * 512));
                         }
                     }
-                    const uint64_t a_desc = smem_desc_sw128(sA + stage * C::A_BYTES);
                     const uint64_t b_desc = smem_desc_sw128(sB + stage * C::B_BYTES);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-                        // +32 bytes of K inside the 128-byte swizzle panel = +2 in the (addr >> 4) field
-                        if constexpr (KIND == KIND_BF16) {
-                            mma_f16<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::BM, BN), acc);
-                        } else if constexpr (KIND == KIND_FP8) {
-                            mma_f8<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_fp8(C::BM, BN), acc);
-                        } else if constexpr (KIND == KIND_MXFP8) {
-                            mma_mxfp8<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::BM, BN, j), acc, sfa_t, sfb_t);
-                        } else {
-                            mma_nvfp4<CTAS>(acc_t, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(C::BM, BN), acc, sfa_t + 4 * j,
-                                            sfb_t + (BN / 128) * 4 * j);
+                    for (int h = 0; h < MH; h++) {
+                        const uint64_t a_desc = smem_desc_sw128(sA + stage * C::A_BYTES + h * 128 * 128);
+                        const uint32_t acc_h = acc_t + h * BN;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+                            // +32 bytes of K inside the 128-byte swizzle panel = +2 in the (addr >> 4) field
+                            if constexpr (KIND == KIND_BF16) {
+                                mma_f16<CTAS>(acc_h, a_desc + 2 * j, b_desc + 2 * j, idesc_bf16(C::MMA_M, BN), acc);
+                            } else if constexpr (KIND == KIND_FP8) {
+                                mma_f8<CTAS>(acc_h, a_desc + 2 * j, b_desc + 2 * j, idesc_fp8(C::MMA_M, BN), acc);
+                            } else if constexpr (KIND == KIND_MXFP8) {
+                                mma_mxfp8<CTAS>(acc_h, a_desc + 2 * j, b_desc + 2 * j, idesc_mxfp8(C::MMA_M, BN, j), acc, sfa_t, sfb_t);
+                            } else {
+                                mma_nvfp4<CTAS>(acc_h, a_desc + 2 * j, b_desc + 2 * j, idesc_nvfp4(C::MMA_M, BN), acc, sfa_t + 4 * j,
+                                                sfb_t + (BN / 128) * 4 * j);
+                            }
                         }
                     }
                     tc_commit<CTAS>(smem_u32(&bar_empty[stage]));       // frees the stage (in both CTAs)
@@ -631,13 +641,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             tc_fence_after();
             // Drain: both halves of this warp's 128 accumulator columns are requested back to back and only waited
             // for once; tensor memory goes back to the MMA warp before any arithmetic on the values.
+#pragma unroll
+            for (int mh = 0; mh < MH; mh++) {                // the accumulator halves of a tall tile, one after the other
             uint32_t r0[64], r1[64];
-            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + col_base, r0);
-            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + col_base + 64, r1);
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * C::ACC_COLS + mh * BN + col_base, r0);
+            tmem_ld_32x64(tmem_base + (uint32_t(quarter * 32) << 16) + buf * C::ACC_COLS + mh * BN + col_base + 64, r1);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && mh == MH - 1) {                 // the last half is in registers: tensor memory goes back
                 const uint32_t tmem_empty_leader = buf ? tmem_empty_leader1 : tmem_empty_leader0;
                 if constexpr (CTAS == 2) mbar_arrive_cluster(tmem_empty_leader); else mbar_arrive(tmem_empty_leader);
             }
@@ -648,7 +660,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 packed[32 + i] = pack_bf16x2(__fmul_rn(__uint_as_float(r1[2 * i]), alpha), __fmul_rn(__uint_as_float(r1[2 * i + 1]), alpha));
             }
             drain += clock64() - t1;
-            const int row0 = m_blk * C::BM + int(cta_rank) * 128 + quarter * 32;
+            const int row0 = m_blk * C::BM + int(cta_rank) * 128 * MH + mh * 128 + quarter * 32;
             const int col0 = n_blk * BN + col_base;
             if constexpr (MODE == MODE_QUANT) {
                 // This thread holds row `row0 + lane`, columns col0 .. col0 + 127 of D as bf16: eight 16-value blocks.
@@ -699,6 +711,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     tma_store_commit();
                 }
             }
+            }       // accumulator halves
         }
         if (lane == 0) tma_store_wait<0>();
         __syncwarp();
@@ -720,10 +733,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ------------------------------------------------------------------------------ host -------
-template <int KIND, int CTAS, int BN, int MODE = MODE_PLAIN>
+template <int KIND, int CTAS, int BN, int MODE = MODE_PLAIN, int MH = 1>
 static cudaError_t launch_t(const GemmArgs& a) {
-    using C = GemmCfg<KIND, CTAS, BN>;
-    auto kern = gemm_kernel<KIND, CTAS, BN, MODE>;
+    using C = GemmCfg<KIND, CTAS, BN, MH>;
+    auto kern = gemm_kernel<KIND, CTAS, BN, MODE, MH>;
     // the attribute belongs to the (kernel, device) pair: remember it per device, not per process
     static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
@@ -765,6 +778,9 @@ static cudaError_t launch_t(const GemmArgs& a) {
 
 template <int KIND>
 static cudaError_t launch_k(const GemmArgs& a) {
+    if constexpr (KIND == KIND_BF16 || KIND == KIND_FP8) {
+        if (a.config & 4) return launch_t<KIND, 2, 256, MODE_PLAIN, 2>(a);      // 512 x 256 cluster tiles
+    }
     switch (a.config & 3) {
         case 0: return launch_t<KIND, 2, 256>(a);
         case 1: return launch_t<KIND, 1, 256>(a);
@@ -783,7 +799,7 @@ int moe_dispatch_ring(int K) {
 }
 
 int gemm_tile_n(int config) { return (config & 2) ? 128 : 256; }
-int gemm_tile_m(int config) { return (config & 1) ? 128 : 256; }
+int gemm_tile_m(int config) { return (config & 4) ? 512 : ((config & 1) ? 128 : 256); }
 
 cudaError_t launch_gemm(const GemmArgs& a) {
     if (a.mode == MODE_AG) return launch_t<KIND_NVFP4, 2, 256, MODE_AG>(a);

@@ -14,9 +14,8 @@ struct NvQuantArgs;
 // quantize.cu / quantize_fast.cu
 cudaError_t launch_nvfp4_quantize_mode(const NvQuantArgs& a, int mode);
 cudaError_t launch_absmax(const void* A, int64_t lda, int M, int K, unsigned int* out_bits, int sm_count, cudaStream_t s);
-// tile_map (optional): 2-D map over A, bf16, box 128 x 128, no swizzle: large tensors then stream through a TMA ring
 cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64_t ldc, void* sc, int M, int K, int sm_count,
-                                  cudaStream_t s, const CUtensorMap* tile_map, int* status);
+                                  cudaStream_t s);
 cudaError_t launch_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, cudaStream_t s);
 cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cudaStream_t s);
 

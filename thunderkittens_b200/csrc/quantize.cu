@@ -1,6 +1,4 @@
 // NVFP4 / MXFP8 quantize: IEEE arithmetic policies and host launchers.
-#include <atomic>
-#include "ptx.cuh"
 #include "quantize_impl.cuh"
 #include "internal.h"
 
@@ -56,6 +54,14 @@ absmax_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, int M, int K, un
 }
 
 // ------------------------------------------------------------------------------ MXFP8 -----
+// e8m0 code of a positive, finite or infinite, normal float, rounded toward +inf and saturated to the largest finite code:
+// what __nv_cvt_float_to_e8m0(x, __NV_SATFINITE, cudaRoundPosInf) returns for such x (the reference's call,
+// mxfp8_b200_gemm.cu:396), in three integer instructions: any mantissa bit carries into the exponent field.
+__device__ __forceinline__ uint32_t e8m0_round_up(float x) {
+    const uint32_t e = (__float_as_uint(x) + 0x007fffffu) >> 23;
+    return e > 254u ? 254u : e;
+}
+
 __global__ void __launch_bounds__(Q_THREADS)
 mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t* __restrict__ codes, int64_t ldc,
                       uint8_t* __restrict__ sc, int M, int K) {
@@ -78,10 +84,10 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
             a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
             a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
             const float scale = fmaxf(__fmul_rn(a, 0.002232142857f), 0.000000000001f);
-            const uint8_t s8 = (uint8_t)__nv_cvt_float_to_e8m0(scale, __NV_SATFINITE, cudaRoundPosInf);
-            if ((lane & 3) == 0) s_sc[buf][(r & 31) * 16 + (r >> 5) * 4 + kb_local] = (tc.row0 + r < M) ? s8 : uint8_t(0);   // rows past M: 0
-            // 1 / 2^(s8-127): exact for every finite e8m0 code
-            const float inv = __frcp_rn(s8 == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(uint32_t(s8) << 23));
+            const uint32_t s8 = e8m0_round_up(scale);
+            if ((lane & 3) == 0) s_sc[buf][(r & 31) * 16 + (r >> 5) * 4 + kb_local] = (tc.row0 + r < M) ? uint8_t(s8) : uint8_t(0);   // rows past M: 0
+            // 1 / 2^(s8-127) = 2^(127-s8), exact for every finite e8m0 code: exponent field 254 - s8, and the denormal 2^-127 for s8 = 254
+            const float inv = __uint_as_float(s8 == 254u ? 0x00400000u : (254u - s8) << 23);
             const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
             uint32_t out[2] = {0, 0};
 #pragma unroll
@@ -102,104 +108,6 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     }
 }
 
-
-// ------------------------------------------------------------------------------ MXFP8, TMA ring -----
-// The same tile arithmetic fed from a ring of shared-memory tiles that a producer warp keeps full with TMA loads
-// (128 x 128 bf16 = 32 KB per tile, QR_STAGES tiles in flight per SM): the loads of the next tiles are in the air while the
-// eight consumer warps convert the current one, which plain register loads (8 x 16 bytes per thread, then a long
-// dependent chain of conversions) could not keep up.  One persistent CTA per SM.
-constexpr int QR_STAGES = 6, QR_TILE_BYTES = QT_ROWS * QT_COLS * 2, QR_THREADS = Q_THREADS + 32;
-
-__device__ __forceinline__ void ring_read_tile(uint32_t tile_smem, int warp, int lane, uint4 (&v)[8]) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int r = warp * 16 + 2 * i + (lane >> 4);
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w)
-                     : "r"(tile_smem + uint32_t(r) * 256u + uint32_t(lane & 15) * 16u));
-    }
-}
-
-__global__ void __launch_bounds__(QR_THREADS, 1)
-mxfp8_quantize_ring_kernel(const __grid_constant__ CUtensorMap tmA, uint8_t* __restrict__ codes, int64_t ldc, uint8_t* __restrict__ sc,
-                           int M, int K, int* status, long long wait_limit) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[QR_STAGES];
-    __shared__ __align__(8) uint64_t bar_empty[QR_STAGES];
-    __shared__ __align__(16) uint8_t s_sc[2][512];
-    __shared__ int s_abort;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
-    const int tiles_n = (K + QT_COLS - 1) / QT_COLS;
-    const int num_tiles = ((M + QT_ROWS - 1) / QT_ROWS) * tiles_n;
-    const int k_chunks = K / 128;
-    if (threadIdx.x == 0) {
-        s_abort = 0;
-        for (int s = 0; s < QR_STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), Q_THREADS / 32); }
-        fence_mbar_init();
-        prefetch_tensormap(&tmA);
-    }
-    __syncthreads();
-    WaitCtx wc{&s_abort, status, wait_limit};
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (warp == Q_THREADS / 32) {
-        // ---- producer: one elected lane
-        if (elect_one()) {
-            uint32_t n = 0;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, n++) {
-                const uint32_t s = n % QR_STAGES;
-                if (n >= QR_STAGES && !mbar_wait(wc, smem_u32(&bar_empty[s]), ((n / QR_STAGES) & 1u) ^ 1u)) break;
-                const TileCoord tc = tile_coord(t, tiles_n);
-                mbar_arrive_expect_tx(smem_u32(&bar_full[s]), QR_TILE_BYTES);
-                tma_load_2d(ring + s * QR_TILE_BYTES, &tmA, smem_u32(&bar_full[s]), tc.col0, tc.row0);
-            }
-            if (s_abort) drain_ring(bar_full, QR_STAGES, n, wait_limit);
-        }
-        __syncwarp();
-        return;
-    }
-    // ---- consumers: the arithmetic of mxfp8_quantize_kernel on tiles read from the ring
-    uint32_t n = 0;
-    int buf = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, n++, buf ^= 1) {
-        const uint32_t s = n % QR_STAGES;
-        if (!mbar_wait(wc, smem_u32(&bar_full[s]), (n / QR_STAGES) & 1u)) break;
-        const TileCoord tc = tile_coord(t, tiles_n);
-        uint4 v[8];
-        ring_read_tile(ring + s * QR_TILE_BYTES, warp, lane, v);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));      // the tile is in registers: the stage can be refilled
-        const int kb_local = (lane & 15) >> 2;
-        const int col = tc.col0 + (lane & 15) * 8;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int r = warp * 16 + 2 * i + (lane >> 4);
-            float a = amax8(v[i]);
-            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-            const float scale = fmaxf(__fmul_rn(a, 0.002232142857f), 0.000000000001f);
-            const uint8_t s8 = (uint8_t)__nv_cvt_float_to_e8m0(scale, __NV_SATFINITE, cudaRoundPosInf);
-            if ((lane & 3) == 0) s_sc[buf][(r & 31) * 16 + (r >> 5) * 4 + kb_local] = (tc.row0 + r < M) ? s8 : uint8_t(0);
-            const float inv = __frcp_rn(s8 == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(uint32_t(s8) << 23));
-            const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-            uint32_t out[2] = {0, 0};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float2 f = bf16x2_to_f2(w[j]);
-                f.x = __fmul_rn(f.x, inv);
-                f.y = __fmul_rn(f.y, inv);
-                out[j >> 1] |= uint32_t(__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3)) << (16 * (j & 1));
-            }
-            const int row = tc.row0 + r;
-            if (row < M && col < K) *reinterpret_cast<uint2*>(codes + int64_t(row) * ldc + col) = make_uint2(out[0], out[1]);
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(Q_THREADS) : "memory");      // the consumer warps only
-        if (threadIdx.x < 128 && tc.col0 / 128 < k_chunks) {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(sc + (int64_t(tc.row0 / 128) * k_chunks + tc.col0 / 128) * 512);
-            dst[threadIdx.x] = reinterpret_cast<const uint32_t*>(&s_sc[buf][0])[threadIdx.x];
-        }
-    }
-}
 
 // fp32 <-> packed e2m1 helpers (nvfp4_utils::fp32_to_fp4x2_kernel / fp4x2_to_fp32_kernel,
 // nvfp4_b200_gemm.cu:568-583)
@@ -234,28 +142,7 @@ cudaError_t launch_absmax(const void* A, int64_t lda, int M, int K, unsigned int
 }
 
 cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64_t ldc, void* sc, int M, int K, int sm_count,
-                                  cudaStream_t s, const CUtensorMap* tile_map, int* status) {
-    static const int ring_env = getenv("TKB_MXQ_RING") ? atoi(getenv("TKB_MXQ_RING")) : 1;      // tuning aid: 0 = register-load kernel
-    const int tiles_all = ((M + QT_ROWS - 1) / QT_ROWS) * ((K + QT_COLS - 1) / QT_COLS);
-    if (tile_map != nullptr && ring_env && tiles_all >= 2 * sm_count) {
-        // large tensors: persistent CTAs fed by a TMA ring
-        constexpr int smem = QR_STAGES * QR_TILE_BYTES + 256;
-        static std::atomic<bool> attr_set[64] = {};
-        int dev = 0;
-        if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
-        if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-            if (cudaError_t e = cudaFuncSetAttribute(mxfp8_quantize_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); e != cudaSuccess) return e;
-            if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
-        }
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(sm_count); cfg.blockDim = dim3(QR_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, mxfp8_quantize_ring_kernel, *tile_map, static_cast<uint8_t*>(codes), ldc, static_cast<uint8_t*>(sc), M, K, status,
-                                  api_wait_limit());
-    }
+                                  cudaStream_t s) {
     const int tiles = ((M + QT_ROWS - 1) / QT_ROWS) * ((K + QT_COLS - 1) / QT_COLS);
     // a persistent grid of exactly the CTAs that are resident at once: with more, the second batch of CTAs starts when the first
     // ends and the tiles no longer divide evenly (8 CTAs per SM over 4096 tiles: 3 or 4 tiles per CTA, two batches = 8 tile

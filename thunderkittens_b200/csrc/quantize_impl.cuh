@@ -139,6 +139,68 @@ __device__ __forceinline__ void grid_amax_depart(QuantWork* ws) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Quantizes one 128 x 128 tile held in registers (thread layout of load_tile) and stores codes and scales.  s_sc: this
+// iteration's 1 KB staging buffer for the tile's scale bytes.  RING: the calling CTA has a producer warp besides the
+// Q_THREADS consumer threads, which synchronise among themselves on a named barrier.
+template <class Arith, bool SCALE_2D, bool RING>
+__device__ __forceinline__ void nv_quantize_store_tile(const uint4 (&v)[8], TileCoord tc, int warp, int lane, float sg_dec, float sg_enc,
+                                                       uint8_t (&s_sc)[2][512], uint8_t* __restrict__ codes, int64_t ldc, uint8_t* __restrict__ sc,
+                                                       int64_t ldsc, int sc_rowmajor, int M, int K, int k_chunks) {
+    float am[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float a = amax8(v[i]);
+        am[i] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    }
+    if constexpr (SCALE_2D) {
+        float a = am[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++) a = fmaxf(a, am[i]);
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+#pragma unroll
+        for (int i = 0; i < 8; i++) am[i] = a;
+    }
+    const int kb_local = (lane & 15) >> 1;        // 16-element block within the 128-column tile
+    const int col = tc.col0 + (lane & 15) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int r = warp * 16 + 2 * i + (lane >> 4);     // row within the tile
+        const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(am[i], sg_enc), __NV_SATFINITE, __NV_E4M3);
+        if ((lane & 1) == 0) {
+            if (sc_rowmajor) (&s_sc[0][0])[r * 8 + kb_local] = s8;                       // [row][8 blocks of the tile]
+            else s_sc[kb_local >> 2][(r & 31) * 16 + (r >> 5) * 4 + (kb_local & 3)] = s8;   // 512-byte chunk layout
+        }
+        const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float2 f = bf16x2_to_f2(w[j]);
+            f.x = Arith::scale_value(f.x, s_enc);
+            f.y = Arith::scale_value(f.y, s_enc);
+            packed |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * j);
+        }
+        const int row = tc.row0 + r;
+        if (row < M && col < K) *reinterpret_cast<uint32_t*>(codes + int64_t(row) * ldc + col / 2) = packed;
+    }
+    if constexpr (RING) asm volatile("bar.sync 1, %0;" ::"n"(Q_THREADS) : "memory");      // the consumer warps only
+    else __syncthreads();
+    if (sc_rowmajor) {
+        // plain [M, K/16] scale rows (used where rows travel individually, e.g. MoE dispatch)
+        const int r = threadIdx.x >> 1, half = threadIdx.x & 1;     // 4 scale bytes (64 columns) per thread
+        if (tc.row0 + r < M && tc.col0 + half * 64 < K)
+            *reinterpret_cast<uint32_t*>(sc + int64_t(tc.row0 + r) * ldsc + tc.col0 / 16 + half * 4) =
+                reinterpret_cast<const uint32_t*>(&s_sc[0][0])[r * 2 + half];
+    } else {
+        const int c = threadIdx.x >> 7, word = threadIdx.x & 127;
+        const int kc = tc.col0 / 64 + c;
+        if (kc < k_chunks) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(sc + (int64_t(tc.row0 / 128) * k_chunks + kc) * 512);
+            dst[word] = reinterpret_cast<const uint32_t*>(&s_sc[c][0])[word];
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------ NVFP4 -----
 // Arith supplies:
 //   static void global_scales(float amax, float& sg_dec, float& sg_enc)
@@ -206,58 +268,7 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     for (int t = RESIDENT ? int(blockIdx.x) : num_tiles - 1 - int(blockIdx.x); t >= 0; t -= RESIDENT ? num_tiles : int(gridDim.x), buf ^= 1) {
         const TileCoord tc = tile_coord(t, tiles_n);
         if (!(RESIDENT && FUSED_AMAX)) load_tile(A, lda, M, K, tc, warp, lane, v);
-        float am[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float a = amax8(v[i]);
-            am[i] = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-        }
-        if constexpr (SCALE_2D) {
-            float a = am[0];
-#pragma unroll
-            for (int i = 1; i < 8; i++) a = fmaxf(a, am[i]);
-            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
-#pragma unroll
-            for (int i = 0; i < 8; i++) am[i] = a;
-        }
-        const int kb_local = (lane & 15) >> 1;        // 16-element block within the 128-column tile
-        const int col = tc.col0 + (lane & 15) * 8;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int r = warp * 16 + 2 * i + (lane >> 4);     // row within the tile
-            const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(am[i], sg_enc), __NV_SATFINITE, __NV_E4M3);
-            if ((lane & 1) == 0) {
-                if (sc_rowmajor) (&s_sc[buf][0][0])[r * 8 + kb_local] = s8;                       // [row][8 blocks of the tile]
-                else s_sc[buf][kb_local >> 2][(r & 31) * 16 + (r >> 5) * 4 + (kb_local & 3)] = s8;   // 512-byte chunk layout
-            }
-            const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
-            const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-            uint32_t packed = 0;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float2 f = bf16x2_to_f2(w[j]);
-                f.x = Arith::scale_value(f.x, s_enc);
-                f.y = Arith::scale_value(f.y, s_enc);
-                packed |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * j);
-            }
-            const int row = tc.row0 + r;
-            if (row < M && col < K) *reinterpret_cast<uint32_t*>(codes + int64_t(row) * ldc + col / 2) = packed;
-        }
-        __syncthreads();
-        if (sc_rowmajor) {
-            // plain [M, K/16] scale rows (used where rows travel individually, e.g. MoE dispatch)
-            const int r = threadIdx.x >> 1, half = threadIdx.x & 1;     // 4 scale bytes (64 columns) per thread
-            if (tc.row0 + r < M && tc.col0 + half * 64 < K)
-                *reinterpret_cast<uint32_t*>(sc + int64_t(tc.row0 + r) * ldsc + tc.col0 / 16 + half * 4) =
-                    reinterpret_cast<const uint32_t*>(&s_sc[buf][0][0])[r * 2 + half];
-        } else {
-            const int c = threadIdx.x >> 7, word = threadIdx.x & 127;
-            const int kc = tc.col0 / 64 + c;
-            if (kc < k_chunks) {
-                uint32_t* dst = reinterpret_cast<uint32_t*>(sc + (int64_t(tc.row0 / 128) * k_chunks + kc) * 512);
-                dst[word] = reinterpret_cast<const uint32_t*>(&s_sc[buf][c][0])[word];
-            }
-        }
+        nv_quantize_store_tile<Arith, SCALE_2D, false>(v, tc, warp, lane, sg_dec, sg_enc, s_sc[buf], codes, ldc, sc, ldsc, sc_rowmajor, M, K, k_chunks);
         // the next iteration writes the other staging buffer; the one after that is fenced by the
         // __syncthreads() of the iteration in between
     }

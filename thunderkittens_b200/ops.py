@@ -17,7 +17,7 @@ from . import _lib as L
 _ARITH = {"spec": L.NVFP4_SPEC, "kernel_ieee": L.NVFP4_KERNEL_IEEE, "kernel_fast": L.NVFP4_KERNEL_FAST}
 _CONFIG = {None: L.GEMM_DEFAULT, "default": L.GEMM_DEFAULT, "pair_n256": L.GEMM_PAIR_N256, "single_n256": L.GEMM_SINGLE_N256,
            "pair_n128": L.GEMM_PAIR_N128, "single_n128": L.GEMM_SINGLE_N128, "skinny": L.GEMM_SKINNY,
-           "skinny_prefetch": L.GEMM_SKINNY_PREFETCH}
+           "skinny_prefetch": L.GEMM_SKINNY_PREFETCH, "pair_m512_n256": L.GEMM_PAIR_M512_N256}
 
 #: default NVFP4 arithmetic (see include/tkb200.h): the reference KERNEL's arithmetic, bit-exact with it on a B200;
 #: "spec" is the reference's torch specification (IEEE), reproducible on a CPU
