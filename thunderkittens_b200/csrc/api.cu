@@ -181,8 +181,10 @@ static int pick_config(int kind, int config, int M, int N, int sm_count) {
     const bool dense = kind == KIND_BF16 || kind == KIND_FP8;
     if (config == TKB_GEMM_PAIR_M512_N256) return 4;
     if (config >= TKB_GEMM_PAIR_N256 && config <= TKB_GEMM_SINGLE_N128) return config - 1;
-    // dense kinds: 512 x 256 cluster tiles (two 128-row halves of A per CTA) once they fill two waves of CTA pairs
-    if (dense && long((M + 511) / 512) * ((N + 255) / 256) >= sm_count) return 4;
+    // bf16: 512 x 256 cluster tiles (two 128-row halves of A per CTA) once they fill two waves of CTA pairs: measured 705 against
+    // 728 us at 8192^3.  Not for fp8: its 4 stages of 48 KB hold half the K-time of the 6 x 32 KB ring (379 against 358-367 us).
+    if (kind == KIND_BF16 && long((M + 511) / 512) * ((N + 255) / 256) >= sm_count) return 4;
+    (void)dense;
     // default: CTA pairs; 256-wide N tiles unless that leaves most of the SMs without a tile
     const long tiles256 = long((M + 255) / 256) * ((N + 255) / 256);
     if (tiles256 * 2 >= sm_count || (N % 256 == 0 && tiles256 * 4 >= sm_count)) return 0;
