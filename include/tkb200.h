@@ -79,7 +79,11 @@ int tkb_set_wait_limit_cycles(long long cycles);
  * GEMM kernels record per-CTA wait cycles: [0] producer waiting for a free stage, [1] producer total,
  * [2] MMA thread waiting for the accumulator to be drained, [3] MMA thread waiting for operands, [4] MMA total,
  * [5] epilogue waiting for the accumulator, [6] epilogue drain, [7] producer waiting for rows of other ranks (all-gather
- * mode; its comm CTAs record [0] total, [1] waiting for peers' done flags, [2] fences and flag stores).  NULL (default) switches it off. */
+ * mode; its comm CTAs record [0] total, [1] waiting for peers' done flags, [2] fences and flag stores).  The skinny-M kernel
+ * (M <= 128) records 16 words per CTA instead, in nanoseconds of the global timer: [0] start, [1] past the dependency wait, [2] first
+ * stage issued, [3] last MMA issued, [4] epilogue done, [5] waiting for partial tiles of other CTAs, [6] MMA thread waiting for
+ * operands, [7] epilogue busy, [8] tensor-memory loads, [9] partial-tile stores and publish, [10] output stores, [11] segments.
+ * NULL (default) switches it off. */
 int tkb_gemm_set_profile_buffer(void* device_u64);
 
 /* ---- quantize ----------------------------------------------------------------------------- */

@@ -152,6 +152,15 @@ static int decode_common(DeviceCtx* c, const void* X, const void* X_sc, const fl
     if (int e = make_operand_map(&d.tmX, X, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(K / 2), M, K / 2, nb)) return e;
     if (int e = make_scale_map(&d.tmSW, W_sc, (N + 127) / 128, K / 64, 4)) return e;
     if (int e = make_scale_map(&d.tmSX, X_sc, 1, K / 64, 4)) return e;
+    {   // output tile of one 128-row weight slab: 128 columns of D x the padded activation rows, not swizzled
+        cuuint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+        cuuint64_t strides[1] = {uint64_t(ldd) * 2};
+        cuuint32_t box[2] = {128, uint32_t(nb)};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode(&d.tmD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(skinny output) failed with CUresult %d", int(r));
+    }
     unsigned call = 0;
     int ring = -1;
     {

@@ -31,9 +31,13 @@ struct DecodeCfg {
     static constexpr int X_BYTES = NB * 128;
     static constexpr int SF_BYTES = 4 * 512;             // 4 scale chunks (4 x 64 K) per 128 rows
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
-    static constexpr int STAGES_RAW = (227 * 1024 - 3072) / STAGE_BYTES;
+    // 32 or more activation rows: the output tile (NB rows x 128 weight rows, bf16) is staged in shared memory and leaves as one
+    // TMA store; 16 rows are few enough to store from registers (16 stores of 64 contiguous bytes per warp)
+    static constexpr bool STAGED_OUT = NB >= 32;
+    static constexpr int OUT_BYTES = STAGED_OUT ? NB * 256 : 0;
+    static constexpr int STAGES_RAW = (227 * 1024 - 3072 - OUT_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 2048;
     static constexpr int THREADS = 6 * 32;
     static constexpr int SF_SLOTS = 4;
     static constexpr int SF_BASE = 2 * (NB < 32 ? 32 : NB);      // accumulators at columns 0 and ACC_STRIDE
@@ -111,7 +115,8 @@ struct WorkRange {
 template <int NB>
 __global__ void __launch_bounds__(DecodeCfg<NB>::THREADS, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-              const __grid_constant__ CUtensorMap tmSW, const __grid_constant__ CUtensorMap tmSX, const DecodeParams p) {
+              const __grid_constant__ CUtensorMap tmSW, const __grid_constant__ CUtensorMap tmSX, const __grid_constant__ CUtensorMap tmD,
+              const DecodeParams p) {
     using C = DecodeCfg<NB>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[C::STAGES];
@@ -134,6 +139,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const uint32_t sX = sW + C::STAGES * C::W_BYTES;
     const uint32_t sSW = (sX + C::STAGES * C::X_BYTES + 1023u) & ~1023u;
     const uint32_t sSX = sSW + C::STAGES * C::SF_BYTES;
+    const uint32_t sOut = sSX + C::STAGES * C::SF_BYTES;      // [NB][128] bf16: D rows of one slab, stored by TMA (128-byte aligned)
 
     const int slabs = (p.N + 127) / 128;
     const int kblk = (p.K + 255) / 256;
@@ -147,6 +153,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         for (int b = 0; b < 2; b++) { mbar_init(smem_u32(&bar_acc_full[b]), 1); mbar_init(smem_u32(&bar_acc_empty[b]), 4); }
         fence_mbar_init();
         prefetch_tensormap(&tmW); prefetch_tensormap(&tmX); prefetch_tensormap(&tmSW); prefetch_tensormap(&tmSX);
+        if (C::STAGED_OUT) prefetch_tensormap(&tmD);
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(&s_tmem_base), C::TMEM_COLS);
@@ -308,6 +315,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     }
                 }
             }
+            if (C::STAGED_OUT && head) {
+                // this segment writes D through the staging tile: the TMA store of the previous one must have read it
+                if (threadIdx.x == 64) tma_store_wait_read<0>();
+                epi_barrier();
+            }
             if (!mbar_wait(wc, smem_u32(&bar_acc_full[buf]), (seg_idx >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
             const unsigned long long t_seg = (prof && threadIdx.x == 64) ? global_ns() : 0ull;
@@ -346,7 +358,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
                         for (int i = 0; i < C::CHUNK; i++) v[i] += psum[c0 + i];
                     }
-                    if (n < p.N) {
+                    if constexpr (C::STAGED_OUT) {
+                        // D[m][n] for this thread's weight row n: one 2-byte shared-memory store per activation row (a warp fills
+                        // 64 contiguous bytes, no bank conflict); the tile leaves as ONE TMA store of NB rows x 256 bytes below
+#pragma unroll
+                        for (int i = 0; i < C::CHUNK; i++) {
+                            const __nv_bfloat16 b = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
+                            asm volatile("st.shared.b16 [%0], %1;" ::"r"(sOut + uint32_t(c0 + i) * 256u + uint32_t(n_local) * 2u), "h"(__bfloat16_as_ushort(b)) : "memory");
+                        }
+                    } else if (n < p.N) {
 #pragma unroll
                         for (int i = 0; i < C::CHUNK; i++)
                             if (c0 + i < p.M) p.D[int64_t(c0 + i) * p.ldd + n] = __float2bfloat16_rn(__fmul_rn(v[i], alpha));
@@ -354,10 +374,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     if (prof && threadIdx.x == 64) prof[10] += global_ns() - t_ld;
                 }
             }
+            if (C::STAGED_OUT && head) {
+                fence_proxy_async();
+                epi_barrier();
+                if (threadIdx.x == 64) {          // rows past M and columns past N are clipped by the TMA unit
+                    tma_store_2d(&tmD, sOut, sg.slab * 128, 0);
+                    tma_store_commit();
+                }
+            }
             if (head && !complete) {
                 // every epilogue thread has read the partial tiles: put the contributors' flags back to 0 so that a
                 // later launch that carries the same epoch (a replayed CUDA graph) does not mistake them for fresh
-                epi_barrier();
+                if (!C::STAGED_OUT) epi_barrier();          // (the staged path has just passed a barrier)
                 if (threadIdx.x == 64)
                     for (int h = contrib_lo; h < contrib_hi; h++) st_release_gpu(p.flags + h, 0u);
             }
@@ -374,6 +402,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if (prof && threadIdx.x == 64) { prof[7] += global_ns() - t_seg; prof[11] += 1; }
             seg_idx++;
         }
+        if (C::STAGED_OUT && threadIdx.x == 64) tma_store_wait<0>();
         if (prof && threadIdx.x == 64) prof[4] = global_ns();
         __syncwarp();
     }
@@ -409,9 +438,7 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     // last trail by ~4 us to the end; with 4 or fewer the HBM pipe is no longer full
     const int stages = stages_env > 0 ? stages_env : 6;
     DecodeParams p{a.sgX, a.sgW, static_cast<__nv_bfloat16*>(a.D), a.ldd, a.M, a.N, a.K, a.partials, a.flags, a.epoch, a.status, a.prof, api_wait_limit(), a.prefetch_weights, stages};
-    CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX;
-    void* params[] = {&tmW, &tmX, &tmSW, &tmSX, &p};
-    (void)params;
+    CUtensorMap tmW = a.tmW, tmX = a.tmX, tmSW = a.tmSW, tmSX = a.tmSX, tmD = a.tmD;
     // Programmatic stream serialization: the kernel may start while its predecessor in the stream drains; it prefetches
     // weights, and executes griddepcontrol.wait before anything that depends on (or could disturb) earlier kernels.
     // All CTAs of the grid are expected to be resident together (grid <= SM count, one CTA per SM); the stream-K waits
@@ -422,7 +449,7 @@ static cudaError_t launch_decode_t(const DecodeArgs& a) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmSW, tmSX, p);
+    return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, tmSW, tmSX, tmD, p);
 }
 
 int decode_padded_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
@@ -503,6 +530,7 @@ extern "C" int tkb_nvfp4_gemm_skinny_static(const void* X, const void* X_sc, con
     if (N < 1 || K < 64 || K % 64 || N % 8) return api_fail(1, "gemm_skinny_static: need N %% 8 == 0 and K a positive multiple of 64 (N=%d K=%d)", N, K);
     if (ldd == 0) ldd = N;
     if (ldd < N) return api_fail(1, "gemm_skinny_static: ldd must be >= N");
+    // (M <= 16 stores D from registers: the output tensor map of the wider instances stays unset and is never touched)
     if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(X_sc) | reinterpret_cast<uintptr_t>(W_sc)) & 15u)
         return api_fail(2, "gemm_skinny_static: operand and scale pointers must be 16-byte aligned");
     int dev = 0;

@@ -81,6 +81,7 @@ int gemm_tile_m(int config);
 // decode.cu
 struct DecodeArgs {
     CUtensorMap tmW, tmX, tmSW, tmSX;
+    CUtensorMap tmD;          // D [M, N] bf16, leading dimension ldd: box 128 columns x padded rows, no swizzle
     const float* sgX; const float* sgW;
     void* D; int64_t ldd;
     int M, N, K;
