@@ -241,12 +241,19 @@ class Dist:
 
 
 def gather_settings(args, world):
-    """--comm-sms: 0 = default (copy engines for N > 1), -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel."""
+    """--comm-sms: 0 or -2 = two push warps in every CTA of the GEMM kernel (default for N > 1), -1 = copy engines,
+    k > 0 = k comm CTAs inside the GEMM kernel.  Returns (mode, comm CTAs)."""
     if world == 1:
-        return False, 0
+        return "none", 0
     if args.comm_sms > 0:
-        return False, args.comm_sms
-    return True, 0
+        return "comm_ctas", args.comm_sms
+    return ("copy_engines", 0) if args.comm_sms == -1 else ("push_warps", 0)
+
+
+GATHER_TEXT = {"none": "none (one GPU)",
+               "push_warps": "two push warps in every CTA of the GEMM kernel (plain 16-byte loads / peer stores, 16-row units, one arrival flag each)",
+               "copy_engines": "copy engines: one peer cudaMemcpyAsync per destination for codes, scales and arrival flags",
+               "comm_ctas": "comm CTAs of the GEMM kernel"}
 
 
 def measure_tp(args, D_) -> dict:
@@ -258,8 +265,10 @@ def measure_tp(args, D_) -> dict:
     n_local, rows = TP_N // world, TP_M // world
     u8 = torch.uint8
     GROUPS = 3
-    ce, comm = gather_settings(args, world)
-    op = parallel.AllGatherMatmulNVFP4(TP_M, TP_K, D_.local_rank, world, num_comm_sms=max(comm, 2), copy_engines=ce, copy_streams=args.copy_streams)
+    mode, comm = gather_settings(args, world)
+    ce = mode == "copy_engines"
+    op = parallel.AllGatherMatmulNVFP4(TP_M, TP_K, D_.local_rank, world, num_comm_sms=max(comm, 2), copy_engines=ce, copy_streams=args.copy_streams,
+                                       push_warps=mode == "push_warps")
     sets = []
     amax_w = torch.zeros(1, dtype=torch.float32, device=dev)
     for gi in range(GROUPS):
@@ -345,7 +354,7 @@ def measure_tp(args, D_) -> dict:
     del sets, dX
     torch.cuda.empty_cache()
     return {"dt": dt, "dt_e2e": dt_e2e, "clocks": clocks, "status": status, "host_enqueue_us": statistics.median(host) * 1e6 if host else None,
-            "quant_us": quant_us, "gemm_us": gemm_us, "graph": (f"{per_graph} steps per replayed CUDA graph" if graph is not None else None), "copy_engines": ce, "comm_ctas": comm, "warmup": warm, "groups": GROUPS,
+            "quant_us": quant_us, "gemm_us": gemm_us, "graph": (f"{per_graph} steps per replayed CUDA graph" if graph is not None else None), "copy_engines": ce, "gather": mode, "comm_ctas": comm, "warmup": warm, "groups": GROUPS,
             "h2d": rows * TP_K * 2 * world, "d2h": TP_M * n_local * 2 * world}
 
 
@@ -446,8 +455,7 @@ def run_ours(args) -> None:
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {"workload": WORKLOAD, "parallelism": f"tp{world}" if world > 1 else "single GPU",
                        "l2": f"{tp['groups']} rotating weight / activation / output sets (> 126 MB L2)",
-                       "gather": "none (one GPU)" if world == 1 else ("copy engines: one peer cudaMemcpyAsync per destination for codes, scales and "
-                                 "arrival flags" if tp["copy_engines"] else f"{tp['comm_ctas']} comm CTAs of the GEMM kernel"),
+                       "gather": (f"{tp['comm_ctas']} " if tp["gather"] == "comm_ctas" else "") + GATHER_TEXT[tp["gather"]],
                        "launches_per_step": "tkb_nvfp4_quantize_sharded + tkb_ag_gemm_nvfp4 (one call: tkb_ag_linear_nvfp4)"},
             "roofline": {"bound": "tensor", "achieved": gemm_tf, "peak": peak, "unit": "TFLOP/s per GPU", "frac": gemm_tf / peak,
                          "peak_derived": True, "peak_source": f"4 x {pk['source']} cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s (derived dense-FP4 ceiling; "
@@ -685,9 +693,10 @@ def run_tp_timeline(args) -> None:
     D_ = Dist(torch)
     rank, world, dev = D_.rank, D_.world, D_.dev
     nl, rows = TP_N // world, TP_M // world
-    ce, comm = gather_settings(args, world)
+    mode, comm = gather_settings(args, world)
+    ce = mode == "copy_engines"
     op = parallel.AllGatherMatmulNVFP4(TP_M, TP_K, D_.local_rank, world, num_comm_sms=max(comm, 2), copy_engines=ce,
-                                       copy_streams=args.copy_streams)
+                                       copy_streams=args.copy_streams, push_warps=mode == "push_warps")
     X = synth(torch, dev, rows, TP_K, 700 + rank)
     W = synth(torch, dev, nl, TP_K, 800 + rank, std=0.02)
     u8 = torch.uint8
@@ -713,13 +722,13 @@ def run_tp_timeline(args) -> None:
     setp(None)
     per = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]) * 1e3
     pr = prof.cpu().numpy().reshape(160, 8)
-    ncomm = 0 if ce else op.num_comm_sms
+    ncomm = op.num_comm_sms if mode == "comm_ctas" else 0
     lead = pr[ncomm::2]
     lead = lead[lead[:, 4] > 0]
     if len(lead) == 0:
         lead = np.zeros((1, 8), np.int64)
     med = lambda a: float(np.median(a))
-    out = {"rank": rank, "n_gpus": world, "gather": "copy engines" if ce else f"{ncomm} comm CTAs", "step_us_median_max": [med(per), float(per.max())],
+    out = {"rank": rank, "n_gpus": world, "gather": mode if mode != "comm_ctas" else f"{ncomm} comm CTAs", "step_us_median_max": [med(per), float(per.max())],
            "cycles_of_last_step": {"mma_total": med(lead[:, 4]), "mma_waiting_for_operands": med(lead[:, 3]), "mma_waiting_for_drain": med(lead[:, 2]),
                                    "producer_waiting_for_remote_rows_median_max": [med(lead[:, 7]), float(lead[:, 7].max())]},
            "device_status": L.device_status()}
@@ -785,7 +794,7 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "moe", "tp_timeline"],
                     help="auto: the tensor-parallel NVFP4 GEMM (plus the side measurements); moe: the MoE layer alone; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
-    ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 or -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
+    ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 or -2 = push warps in every CTA of the GEMM kernel, -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
     ap.add_argument("--no-graph", action="store_true", help="tensor-parallel step at N > 1 with the copy-engine gather: issue every step call by call instead of replaying a CUDA graph")
     ap.add_argument("--copy-streams", type=int, default=3, help="streams the copy-engine gather spreads its peer copies over (1..4)")
     ap.add_argument("--moe-comm-sms", type=int, default=-1, help="k > 0: k CTAs of the MoE GEMM kernel pull the token rows; 0 (default): dispatch by the gather kernel on all SMs")

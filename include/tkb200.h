@@ -239,14 +239,18 @@ int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* di
  * from this rank; entry `rank` is local.  Each rank quantizes its M/world rows (with the all-reduced per-tensor
  * amax, so X_sg is the same everywhere) into its own slice of its own buffers; comm_ctas CTAs of the kernel push
  * that slice into every peer's buffers over NVLink while the rest multiply, own rows first.  peer_arrived[i]: rank
- * i's array of M/64 32-bit arrival epochs, one per 64 gathered rows (entry `rank` local); a rank writes the entries
- * of its own rows on every peer.  Before a buffer set is reused every peer must have finished reading it:
+ * i's array of M/16 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own rows on every peer:
+ * 4 per 256 gathered rows with comm CTAs or copy engines, 16 per 256 rows with push warps.
+ * comm_ctas == TKB_AG_PUSH_WARPS: no CTA is set aside; every CTA of the kernel carries two extra warps that push a share of
+ * the slice (16-row units) while its other warps multiply; peer_done must be NULL (the caller orders the steps).  Before a buffer set is reused every peer must have finished reading it:
  *   - peer_done == NULL: the caller sees to that itself (tkb_signal_peers / tkb_wait_flags);
  *   - else peer_done[i] is rank i's array of `world` 32-bit epochs and exit_counter a zeroed device word owned by
  *     this rank: the kernel's last CTA stores `epoch` into entry `rank` of every peer's array, and its comm CTAs
  *     wait (bounded) for entry d of the local array to reach epoch - 2 before they first write to rank d
  *     (two buffer sets alternate, so epoch - 2 was the last reader of this one).
  * M % (256 * world) == 0. */
+#define TKB_AG_COPY_ENGINES (-1)
+#define TKB_AG_PUSH_WARPS (-2)
 int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const float* X_sg, const void* W, const void* W_sc,
                       const float* W_sg, void* D, int64_t ldd, int M, int N_local, int K, int rank, int world, void* const* peer_arrived,
                       void* const* peer_done, void* exit_counter, unsigned int epoch, int comm_ctas, void* stream);
@@ -256,12 +260,18 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
  * destination rank, span (0 codes, 1 scales), byte offset in the gathered buffer, bytes, arrival-flag index, 1 if the
  * piece completes its unit.  Returns the number of pieces (even if larger than max_pieces), or -code on bad arguments. */
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces);
+/* The same with `parts` flagged parts per 256-row block: 4 (comm CTAs) or 16 (push warps: comm_ctas = CTAs of the kernel). */
+int tkb_debug_ag_schedule_parts(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, int parts, long long* out,
+                                int max_pieces);
 
 /* One call for a whole step of the column-parallel layer: tkb_nvfp4_quantize_sharded of the local rows into this rank's
  * slice, then the gather and the GEMM.  `st` holds the symmetric buffers of both buffer sets as seen from this rank (index
  * [set][rank]); the set used is epoch % 2, and epoch must grow by one per call, starting at 1, on every rank alike.
  *   comm_ctas > 0: the gather is done by that many CTAs of the GEMM kernel (tkb_ag_gemm_nvfp4, epoch hand-shake inside).
- *   comm_ctas < 0: the gather is done by the GPU's copy engines: per peer one cudaMemcpyAsync for the codes, one for the
+ *   comm_ctas == TKB_AG_PUSH_WARPS (-2): the gather is done by two extra warps in EVERY CTA of the GEMM kernel (SM-issued stores to
+ *     a peer are bounded per SM, so all SMs pushing a little fills the links where a few comm CTAs cannot); two launches per
+ *     step, no acknowledgement flags: the amax exchange inside the quantize kernel orders a step after every peer's previous one.
+ *   comm_ctas == TKB_AG_COPY_ENGINES (-1): the gather is done by the GPU's copy engines: per peer one cudaMemcpyAsync for the codes, one for the
  *     scales and one for the arrival flags (stream order makes the flags land last), spread over the streams of st->copy in
  *     the order in which the peers need this rank's rows, while every SM multiplies (the GEMM kernel waits, bounded, on the
  *     arrival flags of each 256-row block).  One peer copy per call: no batched-copy API is involved.  In this mode the
@@ -272,7 +282,7 @@ typedef struct tkb_ag_state {
     int rank, world, M, K;
     void* codes[2][8];      /* [M, K/2] gathered codes */
     void* scales[2][8];     /* [M/128, K/64, 512] gathered scales */
-    void* arrived[2][8];    /* [M/64] arrival epochs */
+    void* arrived[2][8];    /* [M/16] arrival epochs (M/64 in use unless push warps gather) */
     void* slots[2][8];      /* [world] 64-bit amax all-reduce slots */
     void* done[8];          /* [world] 32-bit "my kernel of epoch e is finished" flags */
     float* amax;            /* device scratch, 1 float */

@@ -7,6 +7,7 @@ Environment:
                     settings; the gathered codes and scales are compared bit for bit with the oracle's quantize(full X)
                     and D on row slabs that touch the first and the last rows of EVERY source shard.
   TKB_TEST_TP_CE    "1": gather by copy engines instead of comm CTAs.
+  TKB_TEST_TP_PUSH  "1": gather by two push warps in every CTA of the GEMM kernel.
 """
 import os
 import sys
@@ -42,6 +43,7 @@ def main():
     from thunderkittens_b200 import parallel, _lib
     size = os.environ.get("TKB_TEST_TP_SIZE", "small")
     ce = os.environ.get("TKB_TEST_TP_CE", "0") == "1"       # gather by copy engines instead of comm CTAs
+    push = os.environ.get("TKB_TEST_TP_PUSH", "0") == "1"   # gather by push warps in every CTA
     if size == "c4":
         M, K, N, comm, iters, edge = 8192, 8192, 28672, (8 if world <= 2 else 20), 3, 8
     else:
@@ -51,7 +53,7 @@ def main():
     rng = np.random.default_rng(1234)                       # the activations: the same stream on every rank
     wq = O.nvfp4_quantize(bf16_bits(normal_bf16(np.random.default_rng(4321 + rank), (n_local, K), 0.02)))    # this rank's weight shard
     Wd, Wsc, Wsg = to_dev_u8(wq[0], dev), to_dev_u8(wq[1], dev), torch.from_numpy(wq[2]).to(dev)
-    op = parallel.AllGatherMatmulNVFP4(M, K, local, world, num_comm_sms=comm, arithmetic="spec", copy_engines=ce)
+    op = parallel.AllGatherMatmulNVFP4(M, K, local, world, num_comm_sms=comm, arithmetic="spec", copy_engines=ce, push_warps=push)
     ok = True
     for it in range(iters):      # several calls: both buffer sets, acknowledgements, growing epochs
         X = normal_bf16(rng, (M, K), 1.0 + it)
@@ -77,7 +79,7 @@ def main():
                     err, ulp = max(err, e1), max(ulp, u1)
             nan_free = not bool(torch.isnan(D).any().item())        # every tile of D was written
         good = st == 0 and err <= 1e-3 and ulp <= 2 and codes_ok and scales_ok and nan_free
-        print(f"rank {rank} iter {it} [{size}, {'copy engines' if ce else 'comm CTAs'}]: status={st} rel_fro={err:.2e} max_ulp={ulp} "
+        print(f"rank {rank} iter {it} [{size}, {'copy engines' if ce else ('push warps' if push else 'comm CTAs')}]: status={st} rel_fro={err:.2e} max_ulp={ulp} "
               f"gathered_codes_bit_exact={codes_ok} scales={scales_ok} all_written={nan_free}", flush=True)
         ok = ok and good
     if ce:

@@ -33,7 +33,8 @@ def test_ag_gemm_world1(cuda, lib):
 
 
 def _run_workers(world, gather, size):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TKB_TEST_TP_CE="1" if gather == "copy_engines" else "0", TKB_TEST_TP_SIZE=size)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TKB_TEST_TP_CE="1" if gather == "copy_engines" else "0",
+               TKB_TEST_TP_PUSH="1" if gather == "push_warps" else "0", TKB_TEST_TP_SIZE=size)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
                         "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "mp_tp_worker.py")],
                        capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
@@ -42,7 +43,7 @@ def _run_workers(world, gather, size):
     assert r.stdout.count("PASS") == world
 
 
-@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines"])
+@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines", "push_warps"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ag_gemm_multi_gpu(cuda, lib, world, gather):
     if torch.cuda.device_count() < world:
@@ -50,7 +51,7 @@ def test_ag_gemm_multi_gpu(cuda, lib, world, gather):
     _run_workers(world, gather, "small")
 
 
-@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines"])
+@pytest.mark.parametrize("gather", ["comm_ctas", "copy_engines", "push_warps"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ag_gemm_multi_gpu_benchmark_size(cuda, lib, world, gather):
     """M = 8192, N = 28672, K = 8192 with the benchmark's gather settings: gathered operand bit-exact, D on slabs of every shard."""

@@ -64,6 +64,7 @@ _SIGNATURES = {
     "tkb_ag_gemm_nvfp4": ([C.POINTER(_vp), C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp,
                            C.c_uint, _i, _vp], _i),
     "tkb_debug_ag_schedule": ([_i, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong), _i], _i),
+    "tkb_debug_ag_schedule_parts": ([_i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong), _i], _i),
     "tkb_nvfp4_quantize_sharded": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_vp), _i, _i, C.c_uint, _vp], _i),
     "tkb_nvfp4_quantize_rows": ([_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "tkb_moe_route": ([_vp, _i, _i, _i, _vp, _vp, _vp], _i),

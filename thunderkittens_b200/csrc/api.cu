@@ -436,6 +436,35 @@ int tkb_mxfp8_quantize(const void* A_bf16, int64_t lda, void* codes, void* sc, i
     if (!aligned16(A_bf16) || !aligned16(codes) || !aligned16(sc)) return api_fail(TKB_ERR_BAD_ALIGNMENT, "mxfp8_quantize: buffers must be 16-byte aligned");
     DeviceCtx* c;
     if (int e = get_ctx(&c)) return e;
+    // Large tensors: one 128 x 128 tile per CTA, moved by TMA in both directions.  Small ones (fewer tiles than two per SM) keep
+    // the register-tile kernel, whose 32-row tiles spread over more SMs.
+    static const int tma_env = getenv("TKB_MXQ_TMA") ? atoi(getenv("TKB_MXQ_TMA")) : -1;      // tuning aid: 0 / 1 force a kernel
+    const long tiles128 = long((M + 127) / 128) * (K / 128);
+    const bool use_tiles = tma_env >= 0 ? tma_env != 0 : tiles128 >= 2L * c->sm_count;
+    if (use_tiles) {
+        CUtensorMap tmA, tmC;
+        {
+            cuuint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+            cuuint64_t strides[1] = {uint64_t(lda) * 2};
+            cuuint32_t box[2] = {64, 128};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = g_encode(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A_bf16), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(mxfp8_quantize input) failed with CUresult %d", int(r));
+        }
+        {
+            cuuint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+            cuuint64_t strides[1] = {uint64_t(K)};
+            cuuint32_t box[2] = {128, 128};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = g_encode(&tmC, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, codes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(mxfp8_quantize output) failed with CUresult %d", int(r));
+        }
+        TKB_CUDA(launch_mxfp8_quantize_tiles(tmA, tmC, sc, M, K, c->status, api_wait_limit(), static_cast<cudaStream_t>(stream)));
+        return TKB_OK;
+    }
     TKB_CUDA(launch_mxfp8_quantize(A_bf16, lda, codes, K, sc, M, K, c->sm_count, static_cast<cudaStream_t>(stream)));
     return TKB_OK;
 }

@@ -307,6 +307,8 @@ static int ag_gemm_impl(void* const* peer_codes, void* const* peer_scales, const
     if (K < 64 || K % 64 || N_local < 8 || N_local % 8) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: K %% 64 and N %% 8 must be 0");
     int sm; int* status;
     if (int e = api_device(&sm, &status)) return e;
+    const bool push_warps = comm_ctas == TKB_AG_PUSH_WARPS;      // two push warps in every CTA instead of dedicated comm CTAs
+    if (push_warps) comm_ctas = 0;
     if (comm_ctas < 0 || comm_ctas % 2 || comm_ctas > sm - 2) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: comm_ctas must be even and leave compute CTAs");
     // comm_ctas == 0 with world > 1: the caller moves the rows itself (copy engines, see tkb_ag_linear_nvfp4) and raises the arrival flags
     if (peer_done && !exit_counter) return api_fail(TKB_ERR_INVALID_ARG, "ag_gemm: peer_done needs an exit counter");
@@ -340,6 +342,8 @@ static int ag_gemm_impl(void* const* peer_codes, void* const* peer_scales, const
     }
     g.comm.ag.epoch = epoch; g.comm.ag.rank = rank; g.comm.ag.world = world; g.comm.ag.blocks_per_rank = M / world / 256;
     g.comm.ag.comm_ctas = world > 1 ? comm_ctas : 0;
+    g.comm.ag.push_warps = push_warps && world > 1 ? 1 : 0;
+    g.comm.ag.parts = push_warps ? kAgPartsPushWarps : kAgPartsPerBlock;
     TKB_CUDA_C(launch_gemm(g));
     return TKB_OK;
 }
@@ -393,10 +397,15 @@ int tkb_debug_struct_layout(int which, int field) {
 }
 
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces) {
-    if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || M < 1 || M % (256 * world) || K < 64 || K % 64 || comm_ctas < 1 ||
+    return tkb_debug_ag_schedule_parts(M, K, rank, world, comm_ctas, comm_idx, piece_bytes, kAgPartsPerBlock, out, max_pieces);
+}
+
+int tkb_debug_ag_schedule_parts(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, int parts, long long* out,
+                                int max_pieces) {
+    if ((parts != kAgPartsPerBlock && parts != kAgPartsPushWarps) || world < 2 || world > kMaxWorld || rank < 0 || rank >= world || M < 1 || M % (256 * world) || K < 64 || K % 64 || comm_ctas < 1 ||
         comm_idx < 0 || comm_idx >= comm_ctas || piece_bytes < 16 || piece_bytes % 16 || (!out && max_pieces > 0))
         return -api_fail(TKB_ERR_INVALID_ARG, "debug_ag_schedule: bad arguments");
-    const AgGeometry geo{rank, world, M / world / 256, K / 2, (K / 64) * 512};
+    const AgGeometry geo{rank, world, M / world / 256, K / 2, (K / 64) * 512, parts};
     const int units = ag_units(geo);
     AgCursor c{comm_idx, 0, 0u};
     int n = 0;
@@ -574,6 +583,14 @@ int tkb_ag_linear_nvfp4(const tkb_ag_state* st, unsigned int epoch, const void* 
     uint8_t* my_codes = static_cast<uint8_t*>(st->codes[b][r]) + size_t(r) * rows * (st->K / 2);
     uint8_t* my_scales = static_cast<uint8_t*>(st->scales[b][r]) + size_t(r) * (rows / 128) * (st->K / 64) * 512;
     cudaStream_t main = static_cast<cudaStream_t>(stream);
+    if (comm_ctas == TKB_AG_PUSH_WARPS) {
+        // Two launches: the quantize kernel (whose amax exchange orders this step after every peer's previous one, so that
+        // nobody still reads the buffer set that the pushes overwrite) and the GEMM with push warps in every CTA.
+        if (int e = tkb_nvfp4_quantize_sharded(X_local, 0, my_codes, my_scales, st->sg, rows, st->K, 0, arithmetic, st->slots[b], w, r, epoch, stream))
+            return e;
+        return ag_gemm_impl(st->codes[b], st->scales[b], st->sg, W, W_sc, W_sg, D, ldd, st->M, N_local, st->K, r, w, st->arrived[b], nullptr,
+                            nullptr, epoch, TKB_AG_PUSH_WARPS, nullptr, stream);
+    }
     const bool ce = w > 1 && comm_ctas < 0;          // gather by copy engines instead of comm CTAs
     if (!ce) {
         // This rank's slice of its own buffers is only read by its own kernels (earlier in this stream); what the peers

@@ -213,7 +213,7 @@ __device__ __forceinline__ void ag_copy_span(const uint8_t* src, uint8_t* dst, u
     }
 }
 __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, const WaitCtx& wc, unsigned long long* prof) {
-    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock};
+    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts};
     const int units = ag_units(geo);
     const unsigned int* done = ag.peer_done[ag.rank];
     const int tid = threadIdx.x, nthr = int(blockDim.x) - 32;
@@ -247,6 +247,28 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
         }
     }
     if (prof && tid == 0) { prof[0] = clock64() - t_begin; prof[1] = t_done; prof[2] = t_pub; prof[3] = 0; prof[4] = 0; }
+}
+
+// The same push spread over EVERY CTA of the kernel: two extra warps per CTA (threads t = 0..63 of them) move units
+// cta, cta + n_ctas, ... while the CTA's other warps multiply.  What limits SM-issued stores to a peer is a per-SM bound
+// (about 10 GB/s, whether 2 or 8 warps issue them and whether they are plain or bulk stores), so the way to fill the links
+// is to use all the SMs a little instead of a few SMs entirely: 148 x 10 GB/s is twice what the links carry, and no SM is
+// taken from the GEMM.  Units are 16-row parts (ag.parts = 16) in the same consumption order as above.  No done-flag
+// wait: the caller's amax exchange orders the steps (see tkb_ag_linear_nvfp4).
+__device__ void ag_push_warps(const AgParams& ag, unsigned int epoch, int cta, int n_ctas, int t, int k_bytes, int sc_bytes_per_mblock) {
+    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts};
+    const int units = ag_units(geo);
+    for (int u = cta; u < units; u += n_ctas) {
+        const AgPiece codes = ag_piece(geo, AgCursor{u, 0, 0u}, 0xffffffffu);
+        const AgPiece scales = ag_piece(geo, AgCursor{u, 1, 0u}, 0xffffffffu);
+        ag_copy_span(ag.codes + codes.off, const_cast<uint8_t*>(ag.peer_codes[codes.dst_rank]) + codes.off, codes.bytes, t, 64);
+        ag_copy_span(ag.scales + scales.off, const_cast<uint8_t*>(ag.peer_scales[scales.dst_rank]) + scales.off, scales.bytes, t, 64);
+        asm volatile("bar.sync 2, 64;" ::: "memory");       // both push warps have issued the unit's stores
+        if (t == 0) {
+            __threadfence_system();                           // cumulative over the stores ordered before the barrier
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ag.peer_arrived[codes.dst_rank] + codes.flag), "r"(epoch) : "memory");
+        }
+    }
 }
 
 // Every CTA of the all-gather kernel calls this (one thread) when it has finished: the last one to arrive tells the
@@ -363,7 +385,7 @@ __device__ void moe_pull(const MoeParams& moe, int comm_idx, int k_bytes, int sc
 }
 
 template <int KIND, int CTAS, int BN, int MODE, int MH = 1>
-__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN, MH>::THREADS, 1)
+__global__ void __launch_bounds__(GemmCfg<KIND, CTAS, BN, MH>::THREADS + (MODE == MODE_AG ? 64 : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmSA, const __grid_constant__ CUtensorMap tmSB,
             const __grid_constant__ CUtensorMap tmD, const GemmParams p, const CommParams cp) {
@@ -468,6 +490,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             unsigned int ag_epoch = 0;
             if constexpr (AG) ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
             (void)ag_epoch;
+            unsigned long long ag_seen = 0ull;      // all-gather mode: row blocks whose arrival this thread has already observed
+            (void)ag_seen;
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
@@ -485,10 +509,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
                         const long long t0 = clock64();
-                        for (int part = 0; part < kAgPartsPerBlock && ok; part++)
-                            ok = flag_wait(wc, ag.peer_arrived[ag.rank] + m_blk * kAgPartsPerBlock + part, ag_epoch);
-                        if (!ok) break;
-                        fence_proxy_async_all();
+                        // a block that was seen complete stays complete for the rest of the step: one check per block and CTA
+                        if (m_blk >= 64 || !((ag_seen >> m_blk) & 1ull)) {
+                            const unsigned int* fl = ag.peer_arrived[ag.rank] + m_blk * ag.parts;
+                            // all flags of the block with independent (relaxed, system-scope) loads first; only a block that is
+                            // not complete yet is waited for flag by flag.  The fence below turns the observation into an acquire.
+                            bool all = true;
+                            for (int q = 0; q < ag.parts; q += 4) {
+                                uint4 f;
+                                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(f.x), "=r"(f.y), "=r"(f.z), "=r"(f.w) : "l"(fl + q) : "memory");
+                                all = all && int(f.x - ag_epoch) >= 0 && int(f.y - ag_epoch) >= 0 && int(f.z - ag_epoch) >= 0 && int(f.w - ag_epoch) >= 0;
+                            }
+                            if (!all)
+                                for (int part = 0; part < ag.parts && ok; part++) ok = flag_wait(wc, fl + part, ag_epoch);
+                            if (!ok) break;
+                            __threadfence_system();
+                            fence_proxy_async_all();
+                            if (m_blk < 64) ag_seen |= 1ull << m_blk;
+                        }
                         waited_flags += clock64() - t0;
                     }
                 }
@@ -601,7 +639,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (p.prof) { p.prof[blockIdx.x * 8 + 2] = wait_acc; p.prof[blockIdx.x * 8 + 3] = wait_full; p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin; }
         }
         __syncwarp();
-    } else {
+    } else if (warp < 2 + C::EPI_WARPS) {
         // ------------------------------------------------------------- epilogue --------------
         const int ew = warp - 2;
         const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
@@ -716,6 +754,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) tma_store_wait<0>();
         __syncwarp();
         if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 8 + 5] = wait_tf; p.prof[blockIdx.x * 8 + 6] = drain; }
+    } else {
+        // ------------------------------------------------------------- push warps (all-gather mode) ----
+        if constexpr (AG) {
+            if (ag.push_warps && ag.world > 1) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");      // the rows come from the quantize kernel before this one
+                const unsigned int ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
+                ag_push_warps(ag, ag_epoch, int(blockIdx.x), int(gridDim.x), int(threadIdx.x) - C::THREADS, p.K / 2, (p.K / 64) * 512);
+            }
+        }
     }
 
     // ----------------------------------------------------------------- teardown --------------
@@ -754,7 +801,7 @@ static cudaError_t launch_t(const GemmArgs& a) {
     units += comm_units;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units * CTAS, 1, 1);
-    cfg.blockDim = dim3(C::THREADS, 1, 1);
+    cfg.blockDim = dim3(C::THREADS + (MODE == MODE_AG ? 64 : 0), 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = a.stream;
     cudaLaunchAttribute attr[2];

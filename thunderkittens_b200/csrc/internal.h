@@ -16,6 +16,8 @@ cudaError_t launch_nvfp4_quantize_mode(const NvQuantArgs& a, int mode);
 cudaError_t launch_absmax(const void* A, int64_t lda, int M, int K, unsigned int* out_bits, int sm_count, cudaStream_t s);
 cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64_t ldc, void* sc, int M, int K, int sm_count,
                                   cudaStream_t s);
+cudaError_t launch_mxfp8_quantize_tiles(const CUtensorMap& tmA, const CUtensorMap& tmC, void* sc, int M, int K, int* status, long long limit,
+                                        cudaStream_t s);
 cudaError_t launch_fp32_to_fp4x2(const float* in, void* out, size_t n_pairs, cudaStream_t s);
 cudaError_t launch_fp4x2_to_fp32(const void* in, float* out, size_t n_pairs, cudaStream_t s);
 
@@ -28,13 +30,15 @@ struct AgParams {
     const uint8_t* peer_codes[kMaxWorld];    // base of every rank's gathered-codes buffer [M, K/2] (own entry = local)
     const uint8_t* peer_scales[kMaxWorld];   // base of every rank's gathered-scales buffer [M/128, K/64, 512]
     uint8_t* codes; uint8_t* scales;         // this rank's buffers (same as peer_*[rank], writable)
-    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs, one per 64 gathered rows ([M / 64]); the entries of
+    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs, `parts` per 256 gathered rows ([M / 16] words allocated); the entries of
                                              // rank s's rows in rank r's array are written by rank s when those rows have landed on r
     unsigned int* peer_done[kMaxWorld];      // optional (all null = the caller orders the epochs itself): every rank's [world] array of
                                              // "kernel finished" epochs; entry s of rank r's array is written by rank s
     unsigned int* exit_counter;              // with peer_done: zeroed device word, counts the CTAs that have left the kernel
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
+    int parts;                               // arrival flags per 256 gathered rows: 4 (comm CTAs, copy engines) or 16 (push warps)
+    int push_warps;                          // non-zero: every CTA of the kernel carries two extra warps that push this rank's rows
     // optional (comm_ctas == 0 only): a device word that counts completed steps.  The kernel waits for arrival epoch
     // *epoch_counter + 1 instead of `epoch`, and its last CTA to finish (exit_counter) adds one to the word.
     unsigned int* epoch_counter;

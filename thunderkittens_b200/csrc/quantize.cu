@@ -1,6 +1,7 @@
 // NVFP4 / MXFP8 quantize: IEEE arithmetic policies and host launchers.
 #include "quantize_impl.cuh"
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace tkb {
 
@@ -109,6 +110,82 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
 }
 
 
+// The same quantizer for large tensors, one 128 x 128 tile per CTA of 128 threads: the tile arrives as two TMA boxes of 128 rows x
+// 128 bytes (128-byte swizzle), thread t owns row t (4 blocks of 32 elements, no shuffles), the e4m3 codes go back into the first
+// half of the same buffer and leave as one TMA store, the 512-byte scale chunk as one coalesced store.  With ~33 KB of shared
+// memory and 128 threads per CTA six or seven CTAs share an SM, each with one bulk load or store in flight, and no load/store
+// instruction touches global memory except the scale chunk.  Chunk c (16 bytes) of row r of a box sits at r * 128 + ((c ^ (r & 7)) << 4):
+// a quarter-warp (8 consecutive rows) reads 8 different chunks, which covers all 32 banks once.
+constexpr int MXT_THREADS = 128;
+constexpr int MXT_SMEM = 2 * 128 * 128 + 1024;
+
+__global__ void __launch_bounds__(MXT_THREADS)
+mxfp8_quantize_tile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC, uint8_t* __restrict__ sc,
+                           int M, int K, int* status, long long limit) {
+    extern __shared__ uint8_t mx_smem_raw[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(16) uint32_t s_sc[128];
+    __shared__ int s_abort;
+    const uint32_t base = (smem_u32(mx_smem_raw) + 1023u) & ~1023u;
+    const int t = threadIdx.x;
+    const int tiles_n = K / 128;
+    const int row0 = (blockIdx.x / tiles_n) * 128, col0 = (blockIdx.x % tiles_n) * 128;
+    if (t == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(smem_u32(&bar), 2 * 128 * 128);
+        tma_load_2d(base, &tmA, smem_u32(&bar), col0, row0);
+        tma_load_2d(base + 128 * 128, &tmA, smem_u32(&bar), col0 + 64, row0);
+    }
+    __syncthreads();
+    WaitCtx wc{&s_abort, status, limit};
+    const bool ok = mbar_wait(wc, smem_u32(&bar), 0);
+    uint4 v[16];
+    const uint32_t row_base = base + uint32_t(t) * 128u;
+    const uint32_t sw = uint32_t(t & 7);
+#pragma unroll
+    for (int c = 0; c < 16; c++) {
+        const uint32_t a = row_base + uint32_t(c >> 3) * (128u * 128u) + ((uint32_t(c & 7) ^ sw) << 4);
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[c].x), "=r"(v[c].y), "=r"(v[c].z), "=r"(v[c].w) : "r"(a));
+    }
+    __syncthreads();                 // every row is in registers: the first half of the buffer becomes the output tile
+    if (!ok) return;                 // (uniform: the wait is on one barrier; a copy that never landed is not waited for twice)
+    uint32_t scales = 0;
+#pragma unroll
+    for (int kb = 0; kb < 4; kb++) {
+        float a = fmaxf(fmaxf(amax8(v[4 * kb]), amax8(v[4 * kb + 1])), fmaxf(amax8(v[4 * kb + 2]), amax8(v[4 * kb + 3])));
+        const float scale = fmaxf(__fmul_rn(a, 0.002232142857f), 0.000000000001f);
+        const uint32_t s8 = e8m0_round_up(scale);
+        scales |= s8 << (8 * kb);
+        const float inv = __uint_as_float(s8 == 254u ? 0x00400000u : (254u - s8) << 23);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {            // 16 codes = one 16-byte chunk of the output row
+            const uint32_t w[8] = {v[4 * kb + 2 * h].x, v[4 * kb + 2 * h].y, v[4 * kb + 2 * h].z, v[4 * kb + 2 * h].w,
+                                   v[4 * kb + 2 * h + 1].x, v[4 * kb + 2 * h + 1].y, v[4 * kb + 2 * h + 1].z, v[4 * kb + 2 * h + 1].w};
+            uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float2 f = bf16x2_to_f2(w[j]);
+                f.x = __fmul_rn(f.x, inv);
+                f.y = __fmul_rn(f.y, inv);
+                out[j >> 1] |= uint32_t(__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3)) << (16 * (j & 1));
+            }
+            st_shared_v4(row_base + ((uint32_t(2 * kb + h) ^ sw) << 4), out[0], out[1], out[2], out[3]);
+        }
+    }
+    s_sc[(t & 31) * 4 + (t >> 5)] = (row0 + t < M) ? scales : 0u;          // rows past M: scale 0
+    fence_proxy_async();
+    __syncthreads();
+    reinterpret_cast<uint32_t*>(sc + (int64_t(row0 / 128) * tiles_n + col0 / 128) * 512)[t] = s_sc[t];
+    if (t == 0) {
+        tma_store_2d(&tmC, base, col0, row0);         // rows past M are clipped
+        tma_store_commit();
+        tma_store_wait_read<0>();                     // the buffer must outlive the copy's reads
+    }
+}
+
+
 // fp32 <-> packed e2m1 helpers (nvfp4_utils::fp32_to_fp4x2_kernel / fp4x2_to_fp32_kernel,
 // nvfp4_b200_gemm.cu:568-583)
 __global__ void fp32_to_fp4x2_kernel(const float2* __restrict__ in, uint8_t* __restrict__ out, size_t n_pairs) {
@@ -158,6 +235,19 @@ cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64
     int grid = sm_count * per_sm < tiles ? sm_count * per_sm : tiles;
     mxfp8_quantize_kernel<<<grid < 1 ? 1 : grid, Q_THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(A), lda,
                                                                   static_cast<uint8_t*>(codes), ldc, static_cast<uint8_t*>(sc), M, K);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mxfp8_quantize_tiles(const CUtensorMap& tmA, const CUtensorMap& tmC, void* sc, int M, int K, int* status, long long limit,
+                                        cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(mxfp8_quantize_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MXT_SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int tiles = ((M + 127) / 128) * (K / 128);
+    mxfp8_quantize_tile_kernel<<<tiles, MXT_THREADS, MXT_SMEM, s>>>(tmA, tmC, static_cast<uint8_t*>(sc), M, K, status, limit);
     return cudaGetLastError();
 }
 

@@ -109,7 +109,7 @@ class AllGatherMatmulNVFP4:
     """
 
     def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None,
-                 copy_engines: bool = False, copy_streams: int = 3):
+                 copy_engines: bool = False, copy_streams: int = 3, push_warps: bool = False):
         self.arithmetic = arithmetic      # NVFP4 quantizer arithmetic (None = ops.default_nvfp4_arithmetic)
         if M % (256 * local_world_size):
             raise RuntimeError("M must be a multiple of 256 * world size")
@@ -125,7 +125,7 @@ class AllGatherMatmulNVFP4:
         # flags[0:world] = done (acknowledge) epochs; arrived[set] = arrival epochs of the row blocks, written by their owners
         self.flags = mk((local_world_size,), torch.int32)
         dev = self.flags.data_.device
-        self.arrived = [mk((M // 64,), torch.int32) for _ in range(2)]     # one arrival epoch per 64 gathered rows
+        self.arrived = [mk((M // 16,), torch.int32) for _ in range(2)]     # arrival epochs: 4 or (push warps) 16 per 256 gathered rows
         self.slots = [mk((local_world_size,), torch.int64) for _ in range(2)]   # (epoch, amax bits) per rank, see tkb_amax_allreduce
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -143,7 +143,8 @@ class AllGatherMatmulNVFP4:
             st.done[i] = self.flags.peer_ptr(i)
         st.amax, st.sg, st.exit_counter = self.amax.data_ptr(), self.sg.data_ptr(), self.exit_counter.data_ptr()
         st.epoch_counter = self.epoch_counter.data_ptr()
-        self.copy_engines = bool(copy_engines) and local_world_size > 1
+        self.copy_engines = bool(copy_engines) and local_world_size > 1 and not push_warps
+        self.push_warps = bool(push_warps) and local_world_size > 1      # two push warps in every CTA of the GEMM kernel
         self._copy = None
         self._graphs = []
         if self.copy_engines:
@@ -168,7 +169,7 @@ class AllGatherMatmulNVFP4:
         self.epoch += 1
         arith = ops._ARITH[self.arithmetic or ops.default_nvfp4_arithmetic]
         L.check(L.lib().tkb_ag_linear_nvfp4(C.byref(self._state), self.epoch, X_local.data_ptr(), W.data_ptr(), W_sc.data_ptr(), W_sg.data_ptr(),
-                                            D.data_ptr(), 0, n_local, -1 if self.copy_engines else self.num_comm_sms, arith, _stream()))
+                                            D.data_ptr(), 0, n_local, -2 if self.push_warps else (-1 if self.copy_engines else self.num_comm_sms), arith, _stream()))
 
     def capture(self, steps):
         """Records len(steps) consecutive calls as one CUDA graph (copy-engine gather only).  `steps` is a list of
@@ -214,7 +215,7 @@ class AllGatherMatmulNVFP4:
         ops.nvfp4_quantize(X_local, my_codes, my_scales, self.sg, False, self.arithmetic, amax=self.amax)
         L.check(lib.tkb_ag_gemm_nvfp4(codes.peer_ptr_array(), scales.peer_ptr_array(), self.sg.data_ptr(), W.data_ptr(), W_sc.data_ptr(),
                                       W_sg.data_ptr(), D.data_ptr(), 0, self.M, n_local, self.K, r, w, self.arrived[b].peer_ptr_array(),
-                                      None, None, e, self.num_comm_sms, s))
+                                      None, None, e, -2 if self.push_warps else self.num_comm_sms, s))
         if w > 1:
             L.check(lib.tkb_signal_peers(self.flags.peer_ptr_array(), w, r, r, e, 0, s))      # my kernel of epoch e is done
 
