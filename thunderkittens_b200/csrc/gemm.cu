@@ -405,6 +405,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __shared__ __align__(8) uint64_t bar_tmem_empty[2];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ unsigned int s_ag_all;      // all-gather mode: set by the CTA's spare warps once every remote row of the step has arrived
     __shared__ __align__(8) uint64_t bar_comm[MODE == MODE_MOE ? 32 : 1];   // comm CTAs of the MoE / all-gather modes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -434,6 +435,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         s_abort = 0;
+        s_ag_all = 0u;
         for (int s = 0; s < C::STAGES; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&bar_tmem_full[b]), 1);
@@ -491,7 +493,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if constexpr (AG) ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
             (void)ag_epoch;
             unsigned long long ag_seen = 0ull;      // all-gather mode: row blocks whose arrival this thread has already observed
-            (void)ag_seen;
+            bool ag_all = false;
+            (void)ag_seen; (void)ag_all;
             const long long t_begin = clock64();
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 int m_blk, n_blk;
@@ -509,8 +512,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const int src = m_blk / ag.blocks_per_rank;
                     if (src != ag.rank) {
                         const long long t0 = clock64();
-                        // a block that was seen complete stays complete for the rest of the step: one check per block and CTA
-                        if (m_blk >= 64 || !((ag_seen >> m_blk) & 1ull)) {
+                        // Once the CTA's spare warps have seen every remote row of the step arrive (s_ag_all, released at CTA scope
+                        // after their system-scope fence), nothing is left to check.  Before that: one check per block and CTA,
+                        // since a block that was seen complete stays complete for the rest of the step.
+                        if (!ag_all) {
+                            unsigned int v;
+                            asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(&s_ag_all)) : "memory");
+                            if (v) { ag_all = true; fence_proxy_async_all(); }
+                        }
+                        if (!ag_all && (m_blk >= 64 || !((ag_seen >> m_blk) & 1ull))) {
                             const unsigned int* fl = ag.peer_arrived[ag.rank] + m_blk * ag.parts;
                             // all flags of the block with independent (relaxed, system-scope) loads first; only a block that is
                             // not complete yet is waited for flag by flag.  The fence below turns the observation into an acquire.
@@ -757,10 +767,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else {
         // ------------------------------------------------------------- push warps (all-gather mode) ----
         if constexpr (AG) {
-            if (ag.push_warps && ag.world > 1) {
+            if (ag.world > 1 && !is_comm) {
                 asm volatile("griddepcontrol.wait;" ::: "memory");      // the rows come from the quantize kernel before this one
                 const unsigned int ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
-                ag_push_warps(ag, ag_epoch, int(blockIdx.x), int(gridDim.x), int(threadIdx.x) - C::THREADS, p.K / 2, (p.K / 64) * 512);
+                const int t = int(threadIdx.x) - C::THREADS;
+                if (ag.push_warps) ag_push_warps(ag, ag_epoch, int(blockIdx.x), int(gridDim.x), t, p.K / 2, (p.K / 64) * 512);
+                // Then these two warps watch the arrival flags of ALL remote rows (a few KB, 16 bytes per thread and round) and
+                // tell the producer thread through shared memory when the step's gather is complete, which takes the flag checks
+                // (a system-scope fence each) out of the producer's way for the rest of the step.  Bounded like every wait;
+                // giving up here reports nothing: the producer's own waits do.
+                const unsigned int* fl = ag.peer_arrived[ag.rank];
+                const int chunks = tiles_m * ag.parts / 4;                               // 4 flags per 16-byte chunk
+                const int own_lo = ag.rank * ag.blocks_per_rank * ag.parts / 4, own_hi = own_lo + ag.blocks_per_rank * ag.parts / 4;
+                const long long t0 = clock64();
+                while (true) {
+                    unsigned int mine = 1u;
+                    for (int c = t; c < chunks; c += 64) {
+                        if (c >= own_lo && c < own_hi) continue;                         // own rows raise no flags
+                        uint4 f;
+                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(f.x), "=r"(f.y), "=r"(f.z), "=r"(f.w) : "l"(fl + 4 * c) : "memory");
+                        if (int(f.x - ag_epoch) < 0 || int(f.y - ag_epoch) < 0 || int(f.z - ag_epoch) < 0 || int(f.w - ag_epoch) < 0) mine = 0u;
+                    }
+                    unsigned int all;
+                    asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.u32 pin, %1, 0;\n\tbar.red.and.pred pout, 2, 64, pin;\n\tselp.u32 %0, 1, 0, pout;\n\t}"
+                                 : "=r"(all) : "r"(mine) : "memory");
+                    if (all) {
+                        if (t == 0) {
+                            __threadfence_system();
+                            asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(&s_ag_all)), "r"(1u) : "memory");
+                        }
+                        break;
+                    }
+                    // giving up is decided together as well: every one of the 64 threads must take part in each barrier above
+                    const unsigned int quit = (s_abort || clock64() - t0 > p.wait_limit) ? 1u : 0u;
+                    unsigned int any_quit;
+                    asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.u32 pin, %1, 0;\n\tbar.red.or.pred pout, 2, 64, pin;\n\tselp.u32 %0, 1, 0, pout;\n\t}"
+                                 : "=r"(any_quit) : "r"(quit) : "memory");
+                    if (any_quit) break;
+                    __nanosleep(500);
+                }
             }
         }
     }
