@@ -241,13 +241,19 @@ class Dist:
 
 
 def gather_settings(args, world):
-    """--comm-sms: 0 or -2 = two push warps in every CTA of the GEMM kernel (default for N > 1), -1 = copy engines,
+    """--comm-sms: 0 = default (copy engines at N = 2, push warps from N = 3 on), -2 = two push warps in every CTA of the GEMM kernel, -1 = copy engines,
     k > 0 = k comm CTAs inside the GEMM kernel.  Returns (mode, comm CTAs)."""
     if world == 1:
         return "none", 0
     if args.comm_sms > 0:
         return "comm_ctas", args.comm_sms
-    return ("copy_engines", 0) if args.comm_sms == -1 else ("push_warps", 0)
+    if args.comm_sms == -1:
+        return "copy_engines", 0
+    if args.comm_sms == -2:
+        return "push_warps", 0
+    # default: with two ranks a step is one 19 MB peer copy, which the copy engines move while every warp of every SM
+    # multiplies (measured 0.394 against 0.414 ms); from three ranks on the copies get small and many, and the push warps win
+    return ("copy_engines", 0) if world == 2 else ("push_warps", 0)
 
 
 GATHER_TEXT = {"none": "none (one GPU)",
@@ -794,7 +800,7 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements (other kernels of the path) and the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "moe", "tp_timeline"],
                     help="auto: the tensor-parallel NVFP4 GEMM (plus the side measurements); moe: the MoE layer alone; tp_timeline: per-launch timing and wait counters of the tensor-parallel step (diagnostic)")
-    ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 or -2 = push warps in every CTA of the GEMM kernel, -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
+    ap.add_argument("--comm-sms", type=int, default=0, help="gather of the tensor-parallel GEMM at N > 1: 0 = default (copy engines at N = 2, push warps beyond), -2 = push warps in every CTA of the GEMM kernel, -1 = copy engines, k > 0 = k comm CTAs inside the GEMM kernel")
     ap.add_argument("--no-graph", action="store_true", help="tensor-parallel step at N > 1 with the copy-engine gather: issue every step call by call instead of replaying a CUDA graph")
     ap.add_argument("--copy-streams", type=int, default=3, help="streams the copy-engine gather spreads its peer copies over (1..4)")
     ap.add_argument("--moe-comm-sms", type=int, default=-1, help="k > 0: k CTAs of the MoE GEMM kernel pull the token rows; 0 (default): dispatch by the gather kernel on all SMs")

@@ -804,7 +804,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.u32 pin, %1, 0;\n\tbar.red.or.pred pout, 2, 64, pin;\n\tselp.u32 %0, 1, 0, pout;\n\t}"
                                  : "=r"(any_quit) : "r"(quit) : "memory");
                     if (any_quit) break;
-                    __nanosleep(500);
+                    __nanosleep(4000);                  // 148 CTAs re-reading a few KB of flags: rare enough not to show in the L2 traffic
                 }
             }
         }
