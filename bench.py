@@ -188,13 +188,18 @@ def synth(torch, dev, rows, cols, seed, std=1.0, outliers=0.0):
     return x.to(torch.bfloat16)
 
 
-def event_time(torch, fn, steps, cooldown=0.5, sampler=None, host=None):
+def event_time(torch, fn, steps, cooldown=0.5, sampler=None, host=None, barrier=None):
     """CUDA-event time per step on the current stream.  A 500 ms idle period precedes the timed loop, as in the
     reference's own protocol (kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:673-700), so the loop starts from the
-    same thermal/power state every time.  `host`, if given, receives the host time spent enqueueing one step."""
+    same thermal/power state every time.  `host`, if given, receives the host time spent enqueueing one step.
+    `barrier` (multi-rank runs) is called right before the start event, after the idle period: the ranks' sleeps and
+    set-up end milliseconds apart, and a rank that starts early would otherwise time its wait for the late ones as part
+    of its first step (at 8 ranks a step is ~0.2 ms, so a few ms of skew over 20 steps is as large as the steps)."""
     s = torch.cuda.Event(enable_timing=True); e = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     time.sleep(cooldown)
+    if barrier is not None:
+        barrier()
     s.record()
     t0 = time.perf_counter()
     for i in range(steps):
@@ -320,7 +325,7 @@ def measure_tp(args, D_) -> dict:
 
     cs = ClockSampler(D_.local_rank)
     host = []
-    dt = event_time(torch, lambda i: run_steps(args.steps) if i == 0 else None, args.steps, sampler=cs, host=host)
+    dt = event_time(torch, lambda i: run_steps(args.steps) if i == 0 else None, args.steps, sampler=cs, host=host, barrier=D_.barrier)
     clocks = cs.summary()
     status = _lib.device_status()
     dt = D_.max(dt)
@@ -353,7 +358,7 @@ def measure_tp(args, D_) -> dict:
     for i in range(2):
         e2e_step(i)
     D_.barrier()
-    dt_e2e = D_.max(event_time(torch, e2e_step, max(3, min(args.steps, 10))))
+    dt_e2e = D_.max(event_time(torch, e2e_step, max(3, min(args.steps, 10)), barrier=D_.barrier))
     status |= _lib.device_status()
     D_.barrier()
     op.close()
@@ -402,7 +407,7 @@ def measure_moe(args, D_, steps: int) -> dict:
     for i in range(3):
         step(i)
     D_.barrier()
-    dt = D_.max(event_time(torch, step, steps, cooldown=0.2))
+    dt = D_.max(event_time(torch, step, steps, cooldown=0.2, barrier=D_.barrier))
     st = _lib.device_status()
     rows = int(layer.num_blocks.item()) * 128
     D_.barrier()
@@ -736,7 +741,8 @@ def run_tp_timeline(args) -> None:
     med = lambda a: float(np.median(a))
     out = {"rank": rank, "n_gpus": world, "gather": mode if mode != "comm_ctas" else f"{ncomm} comm CTAs", "step_us_median_max": [med(per), float(per.max())],
            "cycles_of_last_step": {"mma_total": med(lead[:, 4]), "mma_waiting_for_operands": med(lead[:, 3]), "mma_waiting_for_drain": med(lead[:, 2]),
-                                   "producer_waiting_for_remote_rows_median_max": [med(lead[:, 7]), float(lead[:, 7].max())]},
+                                   "producer_waiting_for_remote_rows_median_max": [med(lead[:, 7]), float(lead[:, 7].max())],
+                                   "push_warps_busy_median_max": ([med(pr[:148, 1][pr[:148, 1] > 0]), float(pr[:148, 1].max())] if mode == "push_warps" and (pr[:148, 1] > 0).any() else None)},
            "device_status": L.device_status()}
     if rank in (0, world // 2):
         print(json.dumps(out), flush=True)

@@ -51,7 +51,8 @@ def test_nvfp4_golden(cuda, lib, tag, scale_2d):
     assert sg[0] == g["sg"][0]
 
 
-@pytest.mark.parametrize("M,K", [(128, 128), (1, 64), (16, 8192), (130, 192), (1024, 1024), (2048, 7168)])
+# the last two 1-D cases take the tile-per-CTA kernel (more than two 128 x 128 tiles per SM, K % 128 == 0), one with a ragged last row block
+@pytest.mark.parametrize("M,K", [(128, 128), (1, 64), (16, 8192), (130, 192), (1024, 1024), (2048, 7168), (2100, 4096)])
 @pytest.mark.parametrize("arith,assoc", [("spec", "spec"), ("kernel_ieee", "kernel")])
 @pytest.mark.parametrize("scale_2d", [False, True])
 def test_nvfp4_vs_oracle(cuda, lib, M, K, arith, assoc, scale_2d):
@@ -91,6 +92,25 @@ def test_nvfp4_repeated_calls_reuse_scratch_cleanly(cuda, lib):
     assert all(np.array_equal(x, y) for x, y in zip(a1, a2))
     rb = O.nvfp4_quantize(bf16_bits(B.cpu()))
     assert all(np.array_equal(x, y) for x, y in zip(b, rb))
+
+
+def test_nvfp4_tile_kernel_matches_register_tile_kernel(cuda, lib):
+    """Large tensors take the tile-per-CTA kernel; a sub-tensor view (row pitch larger than K) of the same data must give the
+    same bytes, and so must repeated calls (the scratch slot of the grid barrier is handed back clean)."""
+    big = randn_bf16((2304, 4352), seed=77, outlier_frac=0.01).to(cuda)
+    A = big[:, :4096]                                 # lda = 4352, K = 4096
+    ref = O.nvfp4_quantize(bf16_bits(A.cpu().contiguous()), False, "spec")
+    _ops()
+    for _ in range(3):
+        codes = torch.empty(2304, 2048, dtype=torch.uint8, device=cuda)
+        sc = torch.empty(18, 64, 512, dtype=torch.uint8, device=cuda)
+        sg = torch.empty(1, dtype=torch.float32, device=cuda)
+        from thunderkittens_b200 import _lib as L
+        L.check(L.lib().tkb_nvfp4_quantize(A.data_ptr(), 4352, codes.data_ptr(), sc.data_ptr(), sg.data_ptr(), 2304, 4096, 0, L.NVFP4_SPEC,
+                                           torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert L.device_status() == 0
+        assert np.array_equal(u8(codes), ref[0]) and np.array_equal(u8(sc), ref[1]) and float(sg.item()) == ref[2][0]
 
 
 def test_nvfp4_fast_mode_close_to_ieee(cuda, lib):

@@ -332,6 +332,27 @@ static int nvfp4_quantize_common(const void* A, int64_t lda, void* codes, void* 
     a.spin_limit = api_wait_limit();
     memset(&a.xch, 0, sizeof(a.xch));
     if (xch) a.xch = *xch;
+    // Large tensors in the operand layout: the tile-per-CTA kernel, fed and drained by TMA (the launcher keeps the register-tile
+    // kernels for tensors of at most two tiles per SM, which stay resident between the passes).
+    static const int tma_env = getenv("TKB_NVQ_TMA") ? atoi(getenv("TKB_NVQ_TMA")) : 1;      // tuning aid: 0 = register-tile kernels only
+    a.use_tiles = 0; a.wait_limit = api_wait_limit();
+    memset(&a.tmA, 0, sizeof(a.tmA)); memset(&a.tmC, 0, sizeof(a.tmC));
+    if (tma_env && !amax && !scale_2d && !sc_rowmajor && K % 128 == 0 && long((M + 127) / 128) * (K / 128) > 2L * c->sm_count) {
+        cuuint64_t dims[2] = {uint64_t(K), uint64_t(M)};
+        cuuint64_t strides[1] = {uint64_t(lda) * 2};
+        cuuint32_t box[2] = {64, 128};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode(&a.tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(nvfp4_quantize input) failed with CUresult %d", int(r));
+        cuuint64_t cdims[2] = {uint64_t(K / 2), uint64_t(M)};
+        cuuint64_t cstrides[1] = {uint64_t(K / 2)};
+        cuuint32_t cbox[2] = {64, 128};
+        r = g_encode(&a.tmC, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, codes, cdims, cstrides, cbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return api_fail(TKB_ERR_CUDA, "cuTensorMapEncodeTiled(nvfp4_quantize output) failed with CUresult %d", int(r));
+        a.use_tiles = 1;
+    }
     TKB_CUDA(launch_nvfp4_quantize_mode(a, arithmetic));
     return TKB_OK;
 }

@@ -193,8 +193,8 @@ __device__ __forceinline__ uint4 ld_nc_v4(const uint4* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+template <int UNROLL = 16>
 __device__ __forceinline__ void ag_copy_span(const uint8_t* src, uint8_t* dst, uint32_t bytes, int t, int nthr) {
-    constexpr int UNROLL = 16;
     const uint4* s4 = reinterpret_cast<const uint4*>(src);
     uint4* d4 = reinterpret_cast<uint4*>(dst);
     const uint32_t n = bytes / 16;
@@ -255,14 +255,37 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
 // is to use all the SMs a little instead of a few SMs entirely: 148 x 10 GB/s is twice what the links carry, and no SM is
 // taken from the GEMM.  Units are 16-row parts (ag.parts = 16) in the same consumption order as above.  No done-flag
 // wait: the caller's amax exchange orders the steps (see tkb_ag_linear_nvfp4).
+// Rolling copy for the push warps: U loads stay in flight per thread all the time (a register is reloaded right after its
+// store has been issued) instead of alternating between a round of loads and a round of stores.
+template <int U>
+__device__ __forceinline__ void ag_copy_rolling(const uint8_t* src, uint8_t* dst, uint32_t bytes, int t, int nthr) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src) + t;
+    uint4* d4 = reinterpret_cast<uint4*>(dst) + t;
+    const int n = (int(bytes / 16) - t + nthr - 1) / nthr;          // 16-byte pieces of this thread: t, t + nthr, ...
+    uint4 v[U];
+#pragma unroll
+    for (int i = 0; i < U; i++)
+        if (i < n) v[i] = ld_nc_v4(s4 + size_t(i) * nthr);
+    for (int base = 0; base < n; base += U) {
+#pragma unroll
+        for (int i = 0; i < U; i++) {
+            const int k = base + i;
+            if (k < n) {
+                d4[size_t(k) * nthr] = v[i];
+                if (k + U < n) v[i] = ld_nc_v4(s4 + size_t(k + U) * nthr);
+            }
+        }
+    }
+}
+
 __device__ void ag_push_warps(const AgParams& ag, unsigned int epoch, int cta, int n_ctas, int t, int k_bytes, int sc_bytes_per_mblock) {
     const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts};
     const int units = ag_units(geo);
     for (int u = cta; u < units; u += n_ctas) {
         const AgPiece codes = ag_piece(geo, AgCursor{u, 0, 0u}, 0xffffffffu);
         const AgPiece scales = ag_piece(geo, AgCursor{u, 1, 0u}, 0xffffffffu);
-        ag_copy_span(ag.codes + codes.off, const_cast<uint8_t*>(ag.peer_codes[codes.dst_rank]) + codes.off, codes.bytes, t, 64);
-        ag_copy_span(ag.scales + scales.off, const_cast<uint8_t*>(ag.peer_scales[scales.dst_rank]) + scales.off, scales.bytes, t, 64);
+        ag_copy_rolling<16>(ag.codes + codes.off, const_cast<uint8_t*>(ag.peer_codes[codes.dst_rank]) + codes.off, codes.bytes, t, 64);
+        ag_copy_rolling<16>(ag.scales + scales.off, const_cast<uint8_t*>(ag.peer_scales[scales.dst_rank]) + scales.off, scales.bytes, t, 64);
         asm volatile("bar.sync 2, 64;" ::: "memory");       // both push warps have issued the unit's stores
         if (t == 0) {
             __threadfence_system();                           // cumulative over the stores ordered before the barrier
@@ -573,7 +596,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            if (p.prof) { p.prof[blockIdx.x * 8 + 0] = waited; p.prof[blockIdx.x * 8 + 1] = clock64() - t_begin; p.prof[blockIdx.x * 8 + 7] = waited_flags; }
+            if (p.prof) {
+                p.prof[blockIdx.x * 8 + 0] = waited; p.prof[blockIdx.x * 8 + 7] = waited_flags;
+                bool pushing = false;
+                if constexpr (AG) pushing = ag.push_warps != 0;
+                if (!pushing) p.prof[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            }
             // tail: do not leave while stage releases from the MMA thread may still be in flight
             for (int s = 0; s < C::STAGES && ok; s++) {
                 ok = mbar_wait(wc, smem_u32(&bar_empty[stage]), phase ^ 1);
@@ -771,7 +799,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 asm volatile("griddepcontrol.wait;" ::: "memory");      // the rows come from the quantize kernel before this one
                 const unsigned int ag_epoch = ag.epoch_counter ? *reinterpret_cast<volatile unsigned int*>(ag.epoch_counter) + 1u : ag.epoch;
                 const int t = int(threadIdx.x) - C::THREADS;
-                if (ag.push_warps) ag_push_warps(ag, ag_epoch, int(blockIdx.x), int(gridDim.x), t, p.K / 2, (p.K / 64) * 512);
+                if (ag.push_warps) {
+                    const long long tp0 = clock64();
+                    ag_push_warps(ag, ag_epoch, int(blockIdx.x), int(gridDim.x), t, p.K / 2, (p.K / 64) * 512);
+                    if (p.prof && t == 0) p.prof[blockIdx.x * 8 + 1] = clock64() - tp0;      // push warps: slot 1 holds the cycles this CTA pushed for
+                }
                 // Then these two warps watch the arrival flags of ALL remote rows (a few KB, 16 bytes per thread and round) and
                 // tell the producer thread through shared memory when the step's gather is complete, which takes the flag checks
                 // (a system-scope fence each) out of the producer's way for the rest of the step.  Bounded like every wait;

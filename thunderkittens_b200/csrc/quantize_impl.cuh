@@ -23,6 +23,7 @@
 #include <cuda_fp4.h>
 #include <cuda_runtime.h>
 #include "quantize_types.h"
+#include "ptx.cuh"
 
 namespace tkb {
 
@@ -72,9 +73,10 @@ __device__ __forceinline__ void load_tile(const __nv_bfloat16* A, int64_t lda, i
 // ranks over NVLink (one posted 64-bit store per peer, then bounded polls of its own slots) before it
 // releases the grid, so a row-sharded tensor is quantized with the amax of the whole tensor in one launch.
 constexpr unsigned int kAmaxFailed = 0xffffffffu;      // never a maximum of bf16 magnitudes (NaNs are dropped)
+template <int THREADS = Q_THREADS>
 __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_amax, int* status, const QuantExchange& xch, long long spin_limit) {
     __shared__ float s_amax;
-    __shared__ float s_warp[Q_THREADS / 32];
+    __shared__ float s_warp[THREADS / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) block_amax = fmaxf(block_amax, __shfl_xor_sync(0xffffffffu, block_amax, o));
@@ -83,7 +85,7 @@ __device__ __forceinline__ float grid_amax_barrier(QuantWork* ws, float block_am
     if (threadIdx.x == 0) {
         float m = s_warp[0];
 #pragma unroll
-        for (int w = 1; w < Q_THREADS / 32; w++) m = fmaxf(m, s_warp[w]);
+        for (int w = 1; w < THREADS / 32; w++) m = fmaxf(m, s_warp[w]);
         atomicMax(&ws->amax_bits, __float_as_uint(m));
         __threadfence();
         const unsigned int prev = atomicAdd(&ws->arrived, 1u);
@@ -277,6 +279,154 @@ nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, uint8_t*
     }
 }
 
+
+// ------------------------------------------------------------------------------ NVFP4, tile per CTA, TMA in and out -----
+// Large tensors (two or more 128 x 128 tiles per SM, K % 128 == 0, chunked 1-D scales, fused amax): persistent CTAs of 128
+// threads with one 32 KB tile buffer each, as many as are resident at once (six per SM).  A tile arrives as two TMA boxes of
+// 128 rows x 128 bytes (128-byte swizzle); thread t owns row t.  Pass 1 takes the amax of the CTA's tiles; after the grid
+// barrier pass 2 walks them in reverse, so the tile that is still in shared memory needs no second load and the ones before it
+// are the part of the input most likely still in L2.  The codes of a tile (128 rows x 64 bytes) go into the front of the same
+// buffer (64-byte swizzle: a quarter-warp's 16-byte stores cover all banks) and leave as one TMA store, the two 512-byte scale
+// chunks as coalesced stores.  No load or store instruction touches the tensor itself, and six independent CTAs per SM keep
+// a bulk copy in flight while the others convert.
+constexpr int QTT_THREADS = 128;
+constexpr int QTT_SMEM = 2 * 128 * 128 + 1024;
+
+__device__ __forceinline__ void qtt_load_row(uint32_t base, int t, uint4 (&v)[16]) {
+    const uint32_t row_base = base + uint32_t(t) * 128u, sw = uint32_t(t & 7);
+#pragma unroll
+    for (int c = 0; c < 16; c++) {
+        const uint32_t a = row_base + uint32_t(c >> 3) * (128u * 128u) + ((uint32_t(c & 7) ^ sw) << 4);
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[c].x), "=r"(v[c].y), "=r"(v[c].z), "=r"(v[c].w) : "r"(a));
+    }
+}
+
+template <class Arith>
+__global__ void __launch_bounds__(QTT_THREADS, 5)
+nvfp4_quantize_tile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC, uint8_t* __restrict__ sc,
+                           float* __restrict__ sg, QuantWork* ws, int M, int K, int* status, const QuantExchange xch, long long spin_limit,
+                           long long wait_limit) {
+    extern __shared__ uint8_t qtt_smem_raw[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(16) uint32_t s_sc[2][128];
+    __shared__ int s_abort;
+    const uint32_t base = (smem_u32(qtt_smem_raw) + 1023u) & ~1023u;
+    const int t = threadIdx.x;
+    const int tiles_n = K / 128, tiles_m = (M + 127) / 128;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_chunks = K / 64;
+    const int n_mine = (num_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);      // the grid never exceeds the tiles
+    if (t == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_wait();
+    pdl_launch_dependents();
+    if (xch.stamp != nullptr && blockIdx.x == 0) {
+        const unsigned int epoch = xch.epoch_ptr ? *reinterpret_cast<const volatile unsigned int*>(xch.epoch_ptr) + 1u : xch.epoch;
+        for (int i = t; i < xch.stamp_count; i += QTT_THREADS) xch.stamp[i] = epoch;
+    }
+    WaitCtx wc{&s_abort, status, wait_limit};
+    uint32_t phase = 0;
+    auto issue = [&](int tile) {          // thread 0 only
+        const int row0 = (tile / tiles_n) * 128, col0 = (tile % tiles_n) * 128;
+        mbar_arrive_expect_tx(smem_u32(&bar), 2 * 128 * 128);
+        tma_load_2d(base, &tmA, smem_u32(&bar), col0, row0);
+        tma_load_2d(base + 128 * 128, &tmA, smem_u32(&bar), col0 + 64, row0);
+    };
+    // every thread of the CTA leaves a loop at the same iteration: the outcome of a wait is agreed on before it is acted on
+    auto arrived = [&]() -> bool {
+        const bool ok = mbar_wait(wc, smem_u32(&bar), phase);
+        const bool all = __syncthreads_and(ok ? 1 : 0) != 0;
+        if (!all) {
+            // giving up: the copy that was issued must still land before this CTA may exit (bounded, status already set)
+            if (t == 0) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait_sleep(smem_u32(&bar), phase, 20000u))
+                    if (clock64() - t0 > wait_limit) break;
+            }
+            __syncthreads();
+        }
+        phase ^= 1u;
+        return all;
+    };
+
+    // ---- pass 1: the amax of this CTA's tiles ----
+    uint4 v[16];
+    uint32_t m2 = 0u;                      // running maximum of |x| as packed bf16 pairs
+    bool ok = true;
+    for (int i = 0; i < n_mine && ok; i++) {
+        if (t == 0) issue(int(blockIdx.x) + i * int(gridDim.x));
+        ok = arrived();
+        if (!ok) break;
+        qtt_load_row(base, t, v);
+#pragma unroll
+        for (int c = 0; c < 16; c++) m2 = habs2_max(m2, habs2_max(habs2_max(v[c].x, v[c].y), habs2_max(v[c].z, v[c].w)));
+        if (i + 1 < n_mine) __syncthreads();          // every row is in registers before the next tile overwrites the buffer
+    }
+    __nv_bfloat162 mm = *reinterpret_cast<__nv_bfloat162*>(&m2);
+    const float local = __bfloat162float(__hmax(mm.x, mm.y));
+    const float amax = grid_amax_barrier<QTT_THREADS>(ws, local, status, xch, spin_limit);       // a CTA whose load failed still takes part
+    if (amax < 0.f || !ok) {
+        if (t == 0) grid_amax_depart(ws);
+        return;
+    }
+    float sg_dec, sg_enc;
+    Arith::global_scales(amax, sg_dec, sg_enc);
+    if (blockIdx.x == 0 && t == 0) *sg = sg_dec;
+
+    // ---- pass 2: quantize, last tile first (its rows are still in v) ----
+    const uint32_t row_out = base + uint32_t(t) * 64u, sw_out = uint32_t(t >> 1) & 3u;
+    for (int i = n_mine - 1; i >= 0; i--) {
+        const int tile = int(blockIdx.x) + i * int(gridDim.x);
+        const int row0 = (tile / tiles_n) * 128, col0 = (tile % tiles_n) * 128;
+        if (i != n_mine - 1) {
+            if (t == 0) issue(tile);
+            if (!arrived()) break;
+            qtt_load_row(base, t, v);
+        }
+        __syncthreads();                   // every row is in registers: the front of the buffer becomes the output tile
+        uint32_t scw[2] = {0u, 0u};
+#pragma unroll
+        for (int b = 0; b < 8; b++) {       // 16-value block b of this thread's row: chunks 2b and 2b + 1
+            const float a16 = fmaxf(amax8(v[2 * b]), amax8(v[2 * b + 1]));
+            const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(Arith::block_scale(a16, sg_enc), __NV_SATFINITE, __NV_E4M3);
+            scw[b >> 2] |= uint32_t(s8) << (8 * (b & 3));
+            const float s_enc = Arith::block_enc(e4m3_to_float(s8), sg_dec);
+            const uint32_t w[8] = {v[2 * b].x, v[2 * b].y, v[2 * b].z, v[2 * b].w, v[2 * b + 1].x, v[2 * b + 1].y, v[2 * b + 1].z, v[2 * b + 1].w};
+            uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float2 f = bf16x2_to_f2(w[j]);
+                f.x = Arith::scale_value(f.x, s_enc);
+                f.y = Arith::scale_value(f.y, s_enc);
+                packed[j >> 2] |= uint32_t(__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest)) << (8 * (j & 3));
+            }
+            // 8 bytes of codes at byte 8 b of the 64-byte output row: half of 16-byte chunk b / 2
+            const uint32_t a = row_out + (((uint32_t(b) >> 1) ^ sw_out) << 4) + (uint32_t(b) & 1u) * 8u;
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(packed[0]), "r"(packed[1]) : "memory");
+        }
+        // rows past M were loaded as zeros: their amax, scale byte and codes are 0, like the register-tile kernel writes them
+        s_sc[0][(t & 31) * 4 + (t >> 5)] = scw[0];
+        s_sc[1][(t & 31) * 4 + (t >> 5)] = scw[1];
+        fence_proxy_async();
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int kc = col0 / 64 + c;
+            if (kc < k_chunks) reinterpret_cast<uint32_t*>(sc + (int64_t(row0 / 128) * k_chunks + kc) * 512)[t] = s_sc[c][t];
+        }
+        if (t == 0) {
+            tma_store_2d(&tmC, base, col0 / 2, row0);         // rows past M are clipped
+            tma_store_commit();
+            tma_store_wait_read<0>();                         // before the next load (issued by this thread) overwrites the staging tile
+        }
+    }
+    if (t == 0) grid_amax_depart(ws);
+}
+
 } // namespace tkb
 
 // ------------------------------------------------------------------------------ host ------
@@ -431,8 +581,34 @@ inline bool nvfp4_quantize_skinny_ok(const NvQuantArgs& a) {
 }
 
 template <class Arith>
+inline cudaError_t launch_nvfp4_quantize_tiles(const NvQuantArgs& a) {
+    auto kern = nvfp4_quantize_tile_kernel<Arith>;
+    static int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QTT_SMEM);
+        if (e != cudaSuccess) return e;
+        int b = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, QTT_THREADS, QTT_SMEM);
+        if (e != cudaSuccess) return e;
+        blocks_per_sm = b < 1 ? 1 : b;
+    }
+    const int tiles = ((a.M + 127) / 128) * (a.K / 128);
+    static const int bps_env = getenv("TKB_NVQ_TILE_BLOCKS_PER_SM") ? atoi(getenv("TKB_NVQ_TILE_BLOCKS_PER_SM")) : 0;     // tuning aid; never above what is resident
+    int grid = a.sm_count * (bps_env > 0 && bps_env <= blocks_per_sm ? bps_env : blocks_per_sm);      // all resident at once: the grid barrier needs it
+    if (grid > tiles) grid = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(QTT_THREADS); cfg.dynamicSmemBytes = QTT_SMEM; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a.tmA, a.tmC, static_cast<uint8_t*>(a.sc), a.sg, a.ws, a.M, a.K, a.status, a.xch, a.spin_limit, a.wait_limit);
+}
+
+template <class Arith>
 inline cudaError_t launch_nvfp4_quantize(const NvQuantArgs& a) {
     if (nvfp4_quantize_skinny_ok(a)) return launch_nvfp4_quantize_skinny<Arith>(a);
+    if (a.use_tiles && a.amax_in == nullptr && !a.scale_2d && !a.sc_rowmajor && !nvfp4_quantize_resident_ok(a)) return launch_nvfp4_quantize_tiles<Arith>(a);
     const bool fused = a.amax_in == nullptr;
     const bool res = fused && nvfp4_quantize_resident_ok(a);
     if (a.scale_2d) {

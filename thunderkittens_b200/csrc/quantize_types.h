@@ -1,6 +1,7 @@
 // Host-visible types of the quantize kernels (shared by api.cu and the kernel translation units).
 #pragma once
 #include <cstdint>
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace tkb {
@@ -33,6 +34,10 @@ struct NvQuantArgs {
     int sc_rowmajor;   // 0: 512-byte chunk layout (GEMM operand); 1: plain scale rows of K/16 bytes, ldsc bytes apart
     int64_t ldsc;
     QuantExchange xch;
+    // optional (large tensors, K % 128 == 0): tensor maps of the input (bf16, box 64 x 128, 128-byte swizzle) and of the codes
+    // (bytes, box 64 x 128, 64-byte swizzle) for the tile-per-CTA kernel; use_tiles = 0 keeps the register-tile kernels
+    CUtensorMap tmA, tmC; int use_tiles;
+    long long wait_limit;   // clock cycles a wait for a TMA load may last
 };
 
 } // namespace tkb
