@@ -239,10 +239,10 @@ int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* di
  * from this rank; entry `rank` is local.  Each rank quantizes its M/world rows (with the all-reduced per-tensor
  * amax, so X_sg is the same everywhere) into its own slice of its own buffers; comm_ctas CTAs of the kernel push
  * that slice into every peer's buffers over NVLink while the rest multiply, own rows first.  peer_arrived[i]: rank
- * i's array of M/16 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own rows on every peer:
- * 4 per 256 gathered rows with comm CTAs or copy engines, 16 per 256 rows with push warps.
+ * i's array of M/8 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own rows on every peer:
+ * 4 per 256 gathered rows with comm CTAs or copy engines, 32 per 256 rows with push warps.
  * comm_ctas == TKB_AG_PUSH_WARPS: no CTA is set aside; every CTA of the kernel carries two extra warps that push a share of
- * the slice (16-row units) while its other warps multiply; peer_done must be NULL (the caller orders the steps).  Before a buffer set is reused every peer must have finished reading it:
+ * the slice (8-row units, one destination after the other in the order in which they need the rows) while its other warps multiply; peer_done must be NULL (the caller orders the steps).  Before a buffer set is reused every peer must have finished reading it:
  *   - peer_done == NULL: the caller sees to that itself (tkb_signal_peers / tkb_wait_flags);
  *   - else peer_done[i] is rank i's array of `world` 32-bit epochs and exit_counter a zeroed device word owned by
  *     this rank: the kernel's last CTA stores `epoch` into entry `rank` of every peer's array, and its comm CTAs
@@ -260,7 +260,8 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
  * destination rank, span (0 codes, 1 scales), byte offset in the gathered buffer, bytes, arrival-flag index, 1 if the
  * piece completes its unit.  Returns the number of pieces (even if larger than max_pieces), or -code on bad arguments. */
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces);
-/* The same with `parts` flagged parts per 256-row block: 4 (comm CTAs) or 16 (push warps: comm_ctas = CTAs of the kernel). */
+/* The same with `parts` flagged parts per 256-row block: 4 (comm CTAs) or 32 (push warps: comm_ctas = CTAs of the kernel, one
+ * destination at a time). */
 int tkb_debug_ag_schedule_parts(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, int parts, long long* out,
                                 int max_pieces);
 
@@ -282,7 +283,7 @@ typedef struct tkb_ag_state {
     int rank, world, M, K;
     void* codes[2][8];      /* [M, K/2] gathered codes */
     void* scales[2][8];     /* [M/128, K/64, 512] gathered scales */
-    void* arrived[2][8];    /* [M/16] arrival epochs (M/64 in use unless push warps gather) */
+    void* arrived[2][8];    /* [M/8] arrival epochs (M/64 in use unless push warps gather) */
     void* slots[2][8];      /* [world] 64-bit amax all-reduce slots */
     void* done[8];          /* [world] 32-bit "my kernel of epoch e is finished" flags */
     float* amax;            /* device scratch, 1 float */

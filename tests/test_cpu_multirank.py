@@ -132,7 +132,7 @@ def _worker(rank, world, port, q):
             ok = ok and st.codes[b][i] == op.codes[b].peer_ptr(i) and st.scales[b][i] == op.scales[b].peer_ptr(i)
             ok = ok and st.arrived[b][i] == op.arrived[b].peer_ptr(i) and st.slots[b][i] == op.slots[b].peer_ptr(i)
     ok = ok and all(st.done[i] == op.flags.peer_ptr(i) for i in range(world)) and st.exit_counter == op.exit_counter.data_ptr()
-    ok = ok and op.arrived[0].shape_ == (256 * world // 16,)
+    ok = ok and op.arrived[0].shape_ == (256 * world // 8,)
     Xl = torch.zeros(256, 256, dtype=torch.bfloat16); Wq = torch.zeros(128, 128, dtype=torch.uint8)
     Wsc = torch.zeros(1, 4, 512, dtype=torch.uint8); Wsg = torch.zeros(1); Dd = torch.zeros(256 * world, 128, dtype=torch.bfloat16)
     op(Xl, Wq, Wsc, Wsg, Dd); op(Xl, Wq, Wsc, Wsg, Dd)

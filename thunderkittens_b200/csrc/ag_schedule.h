@@ -14,18 +14,21 @@
 namespace tkb {
 
 constexpr int kAgPartsPerBlock = 4;          // comm CTAs / copy engines: a 256-row block travels as 4 independently flagged 64-row parts
-constexpr int kAgPartsPushWarps = 16;        // push warps in every CTA of the GEMM: 16-row parts, so that even 8 ranks' worth of units
-                                             // ((world - 1) * M / world / 16) is a few per CTA
-constexpr int kAgMaxParts = 16;              // the arrival arrays hold this many flags per 256 gathered rows
-constexpr int kAgFanOut = 4;                 // destinations served at the same time (one GPU pair alone did not fill the links:
-                                             // about 220 GB/s measured with every comm CTA writing to the same peer)
+constexpr int kAgPartsPushWarps = 32;        // push warps in every CTA of the GEMM: 8-row parts, so that ONE destination's share of the
+                                             // rows (M / world / 8 units) already occupies most of the kernel's CTAs
+constexpr int kAgMaxParts = 32;              // the arrival arrays hold this many flags per 256 gathered rows
+constexpr int kAgFanOut = 4;                 // comm CTAs: destinations served at the same time (a handful of CTAs writing to one peer did
+                                             // not fill the links: about 220 GB/s measured)
+constexpr int kAgFanOutPushWarps = 1;        // push warps: strictly in the order in which the destinations consume this rank's rows.  All
+                                             // SMs together push about as fast as one rank's rows are consumed, so each source arrives
+                                             // just before it is needed; interleaving four destinations made the first one four times late
 
-struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock, parts; };      // parts: flagged parts per 256-row block (4 or 16)
+struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock, parts, fan; };      // parts: flagged parts per 256-row block (4 or 32); fan: destinations served together
 struct AgCursor { int u; int span; uint32_t o; };                 // unit, span (0 = codes, 1 = scales), bytes done in the span
 struct AgPiece { size_t off; uint32_t bytes, span_len; int span, dst_rank, flag; };
 
 // A unit is one part (256 / parts rows) of one of this rank's 256-row blocks for one destination.  Destinations are taken in the
-// order in which they consume this rank's rows (rank-1 first), kAgFanOut of them at a time; inside such a group the
+// order in which they consume this rank's rows (rank-1 first), `fan` of them at a time; inside such a group the
 // units alternate between the destinations, so consecutive comm CTAs write to different peers.
 TKB_HD int ag_units(const AgGeometry& g) { return (g.world - 1) * g.blocks_per_rank * g.parts; }
 
@@ -35,8 +38,8 @@ TKB_HD AgPiece ag_piece(const AgGeometry& g, const AgCursor& c, uint32_t piece_b
     AgPiece pc;
     const int per_dst = g.blocks_per_rank * g.parts;
     const int part_rows = 256 / g.parts;
-    const int first = (c.u / (kAgFanOut * per_dst)) * kAgFanOut;          // first destination (consumption order) of the unit's group
-    const int gsize = g.world - 1 - first < kAgFanOut ? g.world - 1 - first : kAgFanOut;
+    const int first = (c.u / (g.fan * per_dst)) * g.fan;                  // first destination (consumption order) of the unit's group
+    const int gsize = g.world - 1 - first < g.fan ? g.world - 1 - first : g.fan;
     const int v = c.u - first * per_dst;                                  // unit inside the group
     pc.dst_rank = (g.rank + g.world - 1 - (first + v % gsize)) % g.world;
     const int in_dst = v / gsize, b = in_dst / g.parts, part = in_dst % g.parts;

@@ -405,7 +405,7 @@ int tkb_debug_ag_schedule_parts(int M, int K, int rank, int world, int comm_ctas
     if ((parts != kAgPartsPerBlock && parts != kAgPartsPushWarps) || world < 2 || world > kMaxWorld || rank < 0 || rank >= world || M < 1 || M % (256 * world) || K < 64 || K % 64 || comm_ctas < 1 ||
         comm_idx < 0 || comm_idx >= comm_ctas || piece_bytes < 16 || piece_bytes % 16 || (!out && max_pieces > 0))
         return -api_fail(TKB_ERR_INVALID_ARG, "debug_ag_schedule: bad arguments");
-    const AgGeometry geo{rank, world, M / world / 256, K / 2, (K / 64) * 512, parts};
+    const AgGeometry geo{rank, world, M / world / 256, K / 2, (K / 64) * 512, parts, parts == kAgPartsPerBlock ? kAgFanOut : kAgFanOutPushWarps};
     const int units = ag_units(geo);
     AgCursor c{comm_idx, 0, 0u};
     int n = 0;

@@ -213,7 +213,7 @@ __device__ __forceinline__ void ag_copy_span(const uint8_t* src, uint8_t* dst, u
     }
 }
 __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_bytes_per_mblock, const WaitCtx& wc, unsigned long long* prof) {
-    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts};
+    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts, kAgFanOut};
     const int units = ag_units(geo);
     const unsigned int* done = ag.peer_done[ag.rank];
     const int tid = threadIdx.x, nthr = int(blockDim.x) - 32;
@@ -252,8 +252,8 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
 // The same push spread over EVERY CTA of the kernel: two extra warps per CTA (threads t = 0..63 of them) move units
 // cta, cta + n_ctas, ... while the CTA's other warps multiply.  What limits SM-issued stores to a peer is a per-SM bound
 // (about 10 GB/s, whether 2 or 8 warps issue them and whether they are plain or bulk stores), so the way to fill the links
-// is to use all the SMs a little instead of a few SMs entirely: 148 x 10 GB/s is twice what the links carry, and no SM is
-// taken from the GEMM.  Units are 16-row parts (ag.parts = 16) in the same consumption order as above.  No done-flag
+// is to use all the SMs a little instead of a few SMs entirely, and no SM is taken from the GEMM.  Units are 8-row parts
+// (ag.parts = 32), one destination after the other in the order in which the destinations consume this rank's rows.  No done-flag
 // wait: the caller's amax exchange orders the steps (see tkb_ag_linear_nvfp4).
 // Rolling copy for the push warps: U loads stay in flight per thread all the time (a register is reloaded right after its
 // store has been issued) instead of alternating between a round of loads and a round of stores.
@@ -279,7 +279,7 @@ __device__ __forceinline__ void ag_copy_rolling(const uint8_t* src, uint8_t* dst
 }
 
 __device__ void ag_push_warps(const AgParams& ag, unsigned int epoch, int cta, int n_ctas, int t, int k_bytes, int sc_bytes_per_mblock) {
-    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts};
+    const AgGeometry geo{ag.rank, ag.world, ag.blocks_per_rank, k_bytes, sc_bytes_per_mblock, ag.parts, kAgFanOutPushWarps};
     const int units = ag_units(geo);
     for (int u = cta; u < units; u += n_ctas) {
         const AgPiece codes = ag_piece(geo, AgCursor{u, 0, 0u}, 0xffffffffu);

@@ -30,14 +30,14 @@ struct AgParams {
     const uint8_t* peer_codes[kMaxWorld];    // base of every rank's gathered-codes buffer [M, K/2] (own entry = local)
     const uint8_t* peer_scales[kMaxWorld];   // base of every rank's gathered-scales buffer [M/128, K/64, 512]
     uint8_t* codes; uint8_t* scales;         // this rank's buffers (same as peer_*[rank], writable)
-    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs, `parts` per 256 gathered rows ([M / 16] words allocated); the entries of
+    unsigned int* peer_arrived[kMaxWorld];   // every rank's arrival epochs, `parts` per 256 gathered rows ([M / 8] words allocated); the entries of
                                              // rank s's rows in rank r's array are written by rank s when those rows have landed on r
     unsigned int* peer_done[kMaxWorld];      // optional (all null = the caller orders the epochs itself): every rank's [world] array of
                                              // "kernel finished" epochs; entry s of rank r's array is written by rank s
     unsigned int* exit_counter;              // with peer_done: zeroed device word, counts the CTAs that have left the kernel
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
-    int parts;                               // arrival flags per 256 gathered rows: 4 (comm CTAs, copy engines) or 16 (push warps)
+    int parts;                               // arrival flags per 256 gathered rows: 4 (comm CTAs, copy engines) or 32 (push warps)
     int push_warps;                          // non-zero: every CTA of the kernel carries two extra warps that push this rank's rows
     // optional (comm_ctas == 0 only): a device word that counts completed steps.  The kernel waits for arrival epoch
     // *epoch_counter + 1 instead of `epoch`, and its last CTA to finish (exit_counter) adds one to the word.

@@ -302,7 +302,7 @@ __device__ __forceinline__ void qtt_load_row(uint32_t base, int t, uint4 (&v)[16
 }
 
 template <class Arith>
-__global__ void __launch_bounds__(QTT_THREADS, 5)
+__global__ void __launch_bounds__(QTT_THREADS, 6)
 nvfp4_quantize_tile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC, uint8_t* __restrict__ sc,
                            float* __restrict__ sg, QuantWork* ws, int M, int K, int* status, const QuantExchange xch, long long spin_limit,
                            long long wait_limit) {
