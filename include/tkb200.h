@@ -240,9 +240,9 @@ int tkb_all_to_all_4d(void* const* peer_out, const void* in, const long long* di
  * amax, so X_sg is the same everywhere) into its own slice of its own buffers; comm_ctas CTAs of the kernel push
  * that slice into every peer's buffers over NVLink while the rest multiply, own rows first.  peer_arrived[i]: rank
  * i's array of M/8 32-bit arrival epochs (entry `rank` local); a rank writes the entries of its own rows on every peer:
- * 4 per 256 gathered rows with comm CTAs or copy engines, 32 per 256 rows with push warps.
+ * 4 per 256 gathered rows with comm CTAs or copy engines, 16 per 256 rows with push warps.
  * comm_ctas == TKB_AG_PUSH_WARPS: no CTA is set aside; every CTA of the kernel carries two extra warps that push a share of
- * the slice (8-row units, one destination after the other in the order in which they need the rows) while its other warps multiply; peer_done must be NULL (the caller orders the steps).  Before a buffer set is reused every peer must have finished reading it:
+ * the slice (16-row units, destinations in the order in which they need the rows, four at a time) while its other warps multiply; peer_done must be NULL (the caller orders the steps).  Before a buffer set is reused every peer must have finished reading it:
  *   - peer_done == NULL: the caller sees to that itself (tkb_signal_peers / tkb_wait_flags);
  *   - else peer_done[i] is rank i's array of `world` 32-bit epochs and exit_counter a zeroed device word owned by
  *     this rank: the kernel's last CTA stores `epoch` into entry `rank` of every peer's array, and its comm CTAs
@@ -260,8 +260,7 @@ int tkb_ag_gemm_nvfp4(void* const* peer_codes, void* const* peer_scales, const f
  * destination rank, span (0 codes, 1 scales), byte offset in the gathered buffer, bytes, arrival-flag index, 1 if the
  * piece completes its unit.  Returns the number of pieces (even if larger than max_pieces), or -code on bad arguments. */
 int tkb_debug_ag_schedule(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, long long* out, int max_pieces);
-/* The same with `parts` flagged parts per 256-row block: 4 (comm CTAs) or 32 (push warps: comm_ctas = CTAs of the kernel, one
- * destination at a time). */
+/* The same with `parts` flagged parts per 256-row block: 4 (comm CTAs) or 16 (push warps: comm_ctas = CTAs of the kernel). */
 int tkb_debug_ag_schedule_parts(int M, int K, int rank, int world, int comm_ctas, int comm_idx, int piece_bytes, int parts, long long* out,
                                 int max_pieces);
 

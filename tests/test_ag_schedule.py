@@ -20,12 +20,11 @@ def _enumerate(lib, M, K, rank, world, comm_ctas, comm_idx, piece, parts=4):
     return np.frombuffer(buf, dtype=np.int64)[:6 * n].reshape(n, 6)
 
 
-# parts = 4: dedicated comm CTAs, four destinations at a time; parts = 32: the push warps of every CTA of the kernel (148 CTAs on a
-# B200), one destination after the other
+# parts = 4: dedicated comm CTAs; parts = 16: the push warps of every CTA of the kernel (148 CTAs on a B200)
 @pytest.mark.parametrize("M,K,world,comm_ctas,parts", [(1024, 1024, 2, 4, 4), (2048, 1024, 4, 4, 4), (4096, 256, 8, 6, 4), (8192, 8192, 8, 16, 4),
                                                        (8192, 8192, 4, 8, 4), (8192, 8192, 2, 30, 4), (512, 64, 2, 2, 4),
-                                                       (8192, 8192, 8, 148, 32), (8192, 1024, 4, 148, 32), (1024, 1024, 2, 148, 32),
-                                                       (512, 64, 2, 148, 32), (2048, 256, 8, 18, 32)])
+                                                       (8192, 8192, 8, 148, 16), (8192, 1024, 4, 148, 16), (1024, 1024, 2, 148, 16),
+                                                       (512, 64, 2, 148, 16), (2048, 256, 8, 18, 16)])
 @pytest.mark.parametrize("piece", [16384, 1 << 30])        # the kernel moves whole spans (piece >= span)
 def test_push_schedule_covers_every_byte_once(lib, M, K, world, comm_ctas, parts, piece):
     part_rows = 256 // parts
@@ -66,7 +65,7 @@ def test_push_schedule_covers_every_byte_once(lib, M, K, world, comm_ctas, parts
             assert np.array_equal(flags[d], mine), "every part of the slice raises its flag exactly once per destination"
         # the first round of units serves the destinations that consume this rank's rows first (rank-1, rank-2, ...),
         # four of them at a time, alternating between them
-        fan = min(4 if parts == 4 else 1, world - 1)
+        fan = min(4, world - 1)
         expect = [(rank + world - 1 - (ci % fan)) % world for ci in range(min(comm_ctas, fan * (rows // 256) * parts))]
         assert first_unit_dst[:len(expect)] == expect
 
@@ -75,4 +74,4 @@ def test_schedule_rejects_bad_arguments(lib):
     assert lib.tkb_debug_ag_schedule(1000, 1024, 0, 2, 4, 0, 16384, None, 0) < 0       # M not a multiple of 256 * world
     assert lib.tkb_debug_ag_schedule(1024, 1024, 0, 2, 4, 4, 16384, None, 0) < 0       # comm_idx out of range
     assert lib.tkb_debug_ag_schedule(1024, 1024, 0, 2, 4, 0, 100, None, 0) < 0         # piece size not a multiple of 16
-    assert lib.tkb_debug_ag_schedule_parts(1024, 1024, 0, 2, 4, 0, 16384, 8, None, 0) < 0   # parts other than 4 or 32
+    assert lib.tkb_debug_ag_schedule_parts(1024, 1024, 0, 2, 4, 0, 16384, 8, None, 0) < 0   # parts other than 4 or 16

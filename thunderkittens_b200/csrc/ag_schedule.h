@@ -14,16 +14,15 @@
 namespace tkb {
 
 constexpr int kAgPartsPerBlock = 4;          // comm CTAs / copy engines: a 256-row block travels as 4 independently flagged 64-row parts
-constexpr int kAgPartsPushWarps = 32;        // push warps in every CTA of the GEMM: 8-row parts, so that ONE destination's share of the
-                                             // rows (M / world / 8 units) already occupies most of the kernel's CTAs
+constexpr int kAgPartsPushWarps = 16;        // push warps in every CTA of the GEMM: 16-row parts, so that even 8 ranks' worth of units
+                                             // ((world - 1) * M / world / 16) is a few per CTA
 constexpr int kAgMaxParts = 32;              // the arrival arrays hold this many flags per 256 gathered rows
-constexpr int kAgFanOut = 4;                 // comm CTAs: destinations served at the same time (a handful of CTAs writing to one peer did
-                                             // not fill the links: about 220 GB/s measured)
-constexpr int kAgFanOutPushWarps = 1;        // push warps: strictly in the order in which the destinations consume this rank's rows.  All
-                                             // SMs together push about as fast as one rank's rows are consumed, so each source arrives
-                                             // just before it is needed; interleaving four destinations made the first one four times late
+constexpr int kAgFanOut = 4;                 // destinations served at the same time.  SM-issued stores to ONE peer stop at about
+                                             // 220-250 GB/s however many SMs issue them (measured with 20 comm CTAs and with the push
+                                             // warps of all 148), so one destination at a time cannot fill the links; four can
+constexpr int kAgFanOutPushWarps = 4;        // measured at 8 GPUs, M=8192 N=28672 K=8192: 195 us per step with 4, 234 us with 1
 
-struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock, parts, fan; };      // parts: flagged parts per 256-row block (4 or 32); fan: destinations served together
+struct AgGeometry { int rank, world, blocks_per_rank, k_bytes, sc_bytes_per_mblock, parts, fan; };      // parts: flagged parts per 256-row block (4 or 16); fan: destinations served together
 struct AgCursor { int u; int span; uint32_t o; };                 // unit, span (0 = codes, 1 = scales), bytes done in the span
 struct AgPiece { size_t off; uint32_t bytes, span_len; int span, dst_rank, flag; };
 

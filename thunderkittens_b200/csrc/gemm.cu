@@ -252,8 +252,8 @@ __device__ void ag_push(const AgParams& ag, int comm_idx, int k_bytes, int sc_by
 // The same push spread over EVERY CTA of the kernel: two extra warps per CTA (threads t = 0..63 of them) move units
 // cta, cta + n_ctas, ... while the CTA's other warps multiply.  What limits SM-issued stores to a peer is a per-SM bound
 // (about 10 GB/s, whether 2 or 8 warps issue them and whether they are plain or bulk stores), so the way to fill the links
-// is to use all the SMs a little instead of a few SMs entirely, and no SM is taken from the GEMM.  Units are 8-row parts
-// (ag.parts = 32), one destination after the other in the order in which the destinations consume this rank's rows.  No done-flag
+// is to use all the SMs a little instead of a few SMs entirely, and no SM is taken from the GEMM.  Units are 16-row parts
+// (ag.parts = 16) in the same consumption order as above, four destinations at a time.  No done-flag
 // wait: the caller's amax exchange orders the steps (see tkb_ag_linear_nvfp4).
 // Rolling copy for the push warps: U loads stay in flight per thread all the time (a register is reloaded right after its
 // store has been issued) instead of alternating between a round of loads and a round of stores.

@@ -37,7 +37,7 @@ struct AgParams {
     unsigned int* exit_counter;              // with peer_done: zeroed device word, counts the CTAs that have left the kernel
     unsigned int epoch;
     int rank, world, blocks_per_rank, comm_ctas;
-    int parts;                               // arrival flags per 256 gathered rows: 4 (comm CTAs, copy engines) or 32 (push warps)
+    int parts;                               // arrival flags per 256 gathered rows: 4 (comm CTAs, copy engines) or 16 (push warps)
     int push_warps;                          // non-zero: every CTA of the kernel carries two extra warps that push this rank's rows
     // optional (comm_ctas == 0 only): a device word that counts completed steps.  The kernel waits for arrival epoch
     // *epoch_counter + 1 instead of `epoch`, and its last CTA to finish (exit_counter) adds one to the word.

@@ -125,7 +125,7 @@ class AllGatherMatmulNVFP4:
         # flags[0:world] = done (acknowledge) epochs; arrived[set] = arrival epochs of the row blocks, written by their owners
         self.flags = mk((local_world_size,), torch.int32)
         dev = self.flags.data_.device
-        self.arrived = [mk((M // 8,), torch.int32) for _ in range(2)]      # arrival epochs: 4 or (push warps) 32 per 256 gathered rows
+        self.arrived = [mk((M // 8,), torch.int32) for _ in range(2)]      # arrival epochs: 4 or (push warps) 16 per 256 gathered rows in use
         self.slots = [mk((local_world_size,), torch.int64) for _ in range(2)]   # (epoch, amax bits) per rank, see tkb_amax_allreduce
         self.amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sg = torch.zeros(1, dtype=torch.float32, device=dev)
