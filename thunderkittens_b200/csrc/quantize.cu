@@ -240,12 +240,7 @@ cudaError_t launch_mxfp8_quantize(const void* A, int64_t lda, void* codes, int64
 
 cudaError_t launch_mxfp8_quantize_tiles(const CUtensorMap& tmA, const CUtensorMap& tmC, void* sc, int M, int K, int* status, long long limit,
                                         cudaStream_t s) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(mxfp8_quantize_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MXT_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static_assert(MXT_SMEM <= 48 * 1024, "no opt-in needed for the dynamic shared memory");
     const int tiles = ((M + 127) / 128) * (K / 128);
     mxfp8_quantize_tile_kernel<<<tiles, MXT_THREADS, MXT_SMEM, s>>>(tmA, tmC, static_cast<uint8_t*>(sc), M, K, status, limit);
     return cudaGetLastError();

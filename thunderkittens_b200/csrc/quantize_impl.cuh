@@ -585,10 +585,9 @@ inline cudaError_t launch_nvfp4_quantize_tiles(const NvQuantArgs& a) {
     auto kern = nvfp4_quantize_tile_kernel<Arith>;
     static int blocks_per_sm = 0;
     if (blocks_per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QTT_SMEM);
-        if (e != cudaSuccess) return e;
+        static_assert(QTT_SMEM <= 48 * 1024, "no opt-in needed for the dynamic shared memory");
         int b = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, QTT_THREADS, QTT_SMEM);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, kern, QTT_THREADS, QTT_SMEM);
         if (e != cudaSuccess) return e;
         blocks_per_sm = b < 1 ? 1 : b;
     }
