@@ -149,8 +149,16 @@ mxfp8_quantize_tile_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         const uint32_t a = row_base + uint32_t(c >> 3) * (128u * 128u) + ((uint32_t(c & 7) ^ sw) << 4);
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[c].x), "=r"(v[c].y), "=r"(v[c].z), "=r"(v[c].w) : "r"(a));
     }
-    __syncthreads();                 // every row is in registers: the first half of the buffer becomes the output tile
-    if (!ok) return;                 // (uniform: the wait is on one barrier; a copy that never landed is not waited for twice)
+    // every row is in registers: the first half of the buffer becomes the output tile.  The outcome of the wait is agreed on
+    // by the whole CTA, so that all of its threads leave together if it ran out
+    if (!__syncthreads_and(ok ? 1 : 0)) {
+        if (t == 0) {                // the copy that was issued must still land before this CTA may exit (bounded)
+            const long long t0 = clock64();
+            while (!mbar_try_wait_sleep(smem_u32(&bar), 0, 20000u))
+                if (clock64() - t0 > limit) break;
+        }
+        return;
+    }
     uint32_t scales = 0;
 #pragma unroll
     for (int kb = 0; kb < 4; kb++) {
