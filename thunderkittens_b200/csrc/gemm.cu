@@ -124,9 +124,10 @@ __device__ __forceinline__ uint8_t quant_block16(const uint32_t (&w)[8], float s
 
 // All-gather mode (tensor-parallel GEMM): the A operand is row-sharded over `world` GPUs.  Every rank
 // keeps a full-size buffer for the gathered codes and scales and quantizes its own shard into its own
-// slice; `comm_ctas` CTAs of this kernel push that slice into every peer's buffers over NVLink (plain
-// loads and stores, no multicast) while the remaining CTAs multiply, own rows first, then the other
-// shards in the order in which they arrive.
+// slice.  That slice reaches every peer's buffers over NVLink (plain loads and stores, no multicast) in one
+// of three ways: two extra "push warps" in every CTA of this kernel, `comm_ctas` CTAs of this kernel set
+// aside for it, or copy engines driven by the host (the kernel then only waits on the arrival flags).  The
+// CTAs multiply meanwhile, own rows first, then the other shards in the order in which they arrive.
 
 // tile index -> (row block, column block).  `group` row-blocks share a sweep over the columns (L2
 // reuse); `rot` rotates the row-block order (all-gather mode starts with the rank's own rows).

@@ -102,10 +102,13 @@ def _stream() -> int:
 class AllGatherMatmulNVFP4:
     """Column-parallel linear layer with NVFP4 operands: every rank owns M/world activation rows (bf16) and
     N_local = N/world weight rows (already NVFP4).  One call =
-        amax(X_local) -> all-reduce(max) -> quantize into this rank's slice of the gathered buffers ->
-        fused kernel (a few CTAs push the slice into every peer's buffers over NVLink, the rest multiply).
-    Two buffer sets alternate between calls; a set is written again only after every peer has acknowledged
-    that its kernel finished with the previous contents.
+        quantize into this rank's slice of the gathered buffers (the per-tensor amax is max-reduced over NVLink
+        inside the quantize kernel) -> fused kernel that gathers the other ranks' slices while it multiplies.
+    The gather is one of: `push_warps=True` — two extra warps in EVERY CTA of the GEMM kernel push a share of the slice
+    (best from 3 ranks on); `copy_engines=True` — peer copies on library-owned streams, replayable as a CUDA graph
+    (`capture` / `replay`; best at 2 ranks); otherwise `num_comm_sms` CTAs of the GEMM kernel push (the reference's
+    scheme).  Two buffer sets alternate between calls; a set is written again only after every peer has finished
+    with its previous contents (acknowledgement flags, or the amax exchange of the following step).
     """
 
     def __init__(self, M: int, K: int, local_rank: int, local_world_size: int, num_comm_sms: int = 8, group=None, arithmetic: str | None = None,
