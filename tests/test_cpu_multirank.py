@@ -137,6 +137,11 @@ def _worker(rank, world, port, q):
     Wsc = torch.zeros(1, 4, 512, dtype=torch.uint8); Wsg = torch.zeros(1); Dd = torch.zeros(256 * world, 128, dtype=torch.bfloat16)
     op(Xl, Wq, Wsc, Wsg, Dd); op(Xl, Wq, Wsc, Wsg, Dd)
     res["ag_calls"] = [c for c in fake.calls if c[0] == "ag_linear"]
+    # the gather with push warps in every CTA of the GEMM travels as comm = -2, and needs no copy context
+    op_push = parallel.AllGatherMatmulNVFP4(256 * world, 256, rank, world, push_warps=True)
+    op_push(Xl, Wq, Wsc, Wsg, Dd)
+    last = [c for c in fake.calls if c[0] == "ag_linear"][-1]
+    res["ag_push"] = last[1] == 1 and last[3] == (-2 if world > 1 else 0) and op_push._copy is None and not op_push.copy_engines
     try:
         op(Xl[:100], Wq, Wsc, Wsg, Dd)
         ok = False
@@ -174,7 +179,7 @@ def test_world2_host_logic_gloo():
         assert p.exitcode == 0
     for r in range(world):
         res = results[r]
-        for key in ("tp_codes", "tp_scales", "tp_sg", "moe_route_consistent", "moe_cover_once", "moe_map", "moe_padding", "ag_state", "moe_state"):
+        for key in ("tp_codes", "tp_scales", "tp_sg", "moe_route_consistent", "moe_cover_once", "moe_map", "moe_padding", "ag_state", "ag_push", "moe_state"):
             assert res[key], (r, key)
         assert [c[1] for c in res["ag_calls"]] == [1, 2] and all(c[2:4] == (128, 4) for c in res["ag_calls"])      # epochs grow by one per call
         assert [c[1] for c in res["moe_calls"]] == [1] and res["moe_calls"][0][2] == 6
