@@ -76,7 +76,7 @@ int tkb_device_status(void* stream, int* status);
 int tkb_set_wait_limit_cycles(long long cycles);
 
 /* Diagnostics (no counterpart in the reference): when set to a device buffer of 8 x uint64 per launched CTA,
- * GEMM kernels record per-CTA wait cycles: [0] producer waiting for a free stage, [1] producer total,
+ * GEMM kernels record per-CTA wait cycles: [0] producer waiting for a free stage, [1] producer total (all-gather mode with push warps: cycles the CTA's push warps were busy),
  * [2] MMA thread waiting for the accumulator to be drained, [3] MMA thread waiting for operands, [4] MMA total,
  * [5] epilogue waiting for the accumulator, [6] epilogue drain, [7] producer waiting for rows of other ranks (all-gather
  * mode; its comm CTAs record [0] total, [1] waiting for peers' done flags, [2] fences and flag stores).  The skinny-M kernel
